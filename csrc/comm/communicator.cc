@@ -1,0 +1,533 @@
+#include "communicator.h"
+
+#include <algorithm>
+#include <cstdio>
+#include <cstring>
+
+#include "../core/env.h"
+#include "../kernels/launch.h"
+#include "topology.h"
+
+namespace yali {
+
+namespace {
+uint64_t RoundUp(uint64_t a, uint64_t b) { return (a + b - 1) / b * b; }
+bool Aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+}  // namespace
+
+bool MakeHeapLayout(int world, uint64_t requested_total, uint64_t granularity, HeapLayout* out) {
+    HeapLayout l;
+    std::memset(&l, 0, sizeof(l));
+    const uint64_t MiB = 1ull << 20;
+    uint64_t off = 0;
+    l.flags_off = off;
+    off += kFlagRegionBytes;
+    if (world > 1) {
+        l.flash_cap = world == 2 ? 64 * MiB : (world <= 4 ? 16 * MiB : 8 * MiB);
+        l.flash_off = off;
+        off += 2ull * (world - 1) * l.flash_cap;
+        l.ring_off = off;
+        l.ring_bytes = 256 * MiB;
+        off += l.ring_bytes;
+        l.nvls_off = off;
+        l.nvls_cap = 64 * MiB;
+        off += 2 * l.nvls_cap;
+        l.gemm_off = off;
+        l.gemm_cap = 4 * MiB;
+        off += 2ull * world * l.gemm_cap;
+    }
+    l.user_off = off;
+    uint64_t total = requested_total ? requested_total : off + 256 * MiB;
+    if (granularity) total = RoundUp(total, granularity);
+    if (total < off + MiB) return false;
+    l.user_bytes = total - off;
+    l.total_bytes = total;
+    *out = l;
+    return true;
+}
+
+Result Communicator::CreateSingleProcess(const std::vector<int>& devices, const CommOptions& opt,
+                                         std::unique_ptr<Communicator>* out, std::string* err) {
+    std::vector<int> u(devices);
+    std::sort(u.begin(), u.end());
+    if (devices.empty() || devices.size() > static_cast<size_t>(kMaxRanks) ||
+        std::adjacent_find(u.begin(), u.end()) != u.end()) {
+        if (err) *err = "need 1.." + std::to_string(kMaxRanks) + " distinct GPUs";
+        return Result::InvalidArg;
+    }
+    int ndev = 0;
+    if (cudaGetDeviceCount(&ndev) != cudaSuccess || u.back() >= ndev || u.front() < 0) {
+        (void)cudaGetLastError();
+        if (err) *err = "GPU index out of range";
+        return Result::InvalidArg;
+    }
+    // User buffers from cudaMalloc must be reachable from every GPU of the group.
+    if (!EnableAllPairsP2P(devices)) {
+        if (err) *err = "peer access could not be enabled between all GPUs";
+        return Result::PeerAccessFailed;
+    }
+    std::unique_ptr<Communicator> c(new Communicator());
+    c->world_ = static_cast<int>(devices.size());
+    c->single_process_ = true;
+    c->local_.resize(devices.size());
+    for (size_t i = 0; i < devices.size(); ++i) {
+        c->local_[i].rank = static_cast<int>(i);
+        c->local_[i].device = devices[i];
+    }
+    Result r = c->Init(opt, err);
+    if (r != Result::Success) return r;
+    *out = std::move(c);
+    return Result::Success;
+}
+
+Result Communicator::CreateEmulated(int world, int device, const CommOptions& opt, std::unique_ptr<Communicator>* out,
+                                    std::string* err) {
+    if (world < 1 || world > kMaxRanks) {
+        if (err) *err = "world size out of range";
+        return Result::InvalidArg;
+    }
+    std::unique_ptr<Communicator> c(new Communicator());
+    c->world_ = world;
+    c->single_process_ = true;
+    c->emulated_ = true;
+    c->local_.resize(world);
+    for (int i = 0; i < world; ++i) {
+        c->local_[i].rank = i;
+        c->local_[i].device = device;
+    }
+    Result r = c->Init(opt, err);
+    if (r != Result::Success) return r;
+    *out = std::move(c);
+    return Result::Success;
+}
+
+Result Communicator::CreateMultiProcess(std::unique_ptr<Bootstrap> bs, int device, const CommOptions& opt,
+                                        std::unique_ptr<Communicator>* out, std::string* err) {
+    if (!bs) {
+        if (err) *err = "no bootstrap";
+        return Result::InvalidArg;
+    }
+    std::unique_ptr<Communicator> c(new Communicator());
+    c->world_ = bs->world();
+    c->local_.resize(1);
+    c->local_[0].rank = bs->rank();
+    c->local_[0].device = device;
+    c->bs_ = std::move(bs);
+    Result r = c->Init(opt, err);
+    // Whether or not this rank succeeded, all ranks must agree before anyone launches.
+    char ok = r == Result::Success;
+    std::vector<char> all(c->world_);
+    if (c->bs_->allgather(&ok, all.data(), 1) != Result::Success) {
+        if (err && r == Result::Success) *err = c->bs_->last_error();
+        return r == Result::Success ? Result::BootstrapError : r;
+    }
+    if (r != Result::Success) return r;
+    if (!std::all_of(all.begin(), all.end(), [](char x) { return x != 0; })) {
+        if (err) *err = "another rank failed to create its communicator";
+        return Result::BootstrapError;
+    }
+    *out = std::move(c);
+    return Result::Success;
+}
+
+Result Communicator::Init(const CommOptions& opt, std::string* err) {
+    const int dev0 = local_[0].device;
+    if (cudaSetDevice(dev0) != cudaSuccess) {
+        (void)cudaGetLastError();
+        if (err) *err = "cudaSetDevice(" + std::to_string(dev0) + ") failed";
+        return Result::CudaError;
+    }
+    uint64_t want = opt.heap_bytes ? opt.heap_bytes : static_cast<uint64_t>(env::HeapBytes());
+    const bool want_mc = opt.want_multicast && !emulated_ && world_ > 1;
+    HeapLayout probe;
+    if (!MakeHeapLayout(world_, want, 0, &probe)) {
+        if (err) *err = "heap size too small for the fixed regions of a " + std::to_string(world_) + "-rank group";
+        return Result::InvalidArg;
+    }
+    Result r;
+    if (bs_) {
+        r = SymmHeapSet::CreateShared(*bs_, dev0, probe.total_bytes, want_mc, &heaps_, err);
+    } else {
+        std::vector<int> devs;
+        for (const Local& l : local_) devs.push_back(l.device);
+        r = SymmHeapSet::CreateLocal(devs, probe.total_bytes, want_mc, &heaps_, err);
+    }
+    if (r != Result::Success) return r;
+    MakeHeapLayout(world_, heaps_->bytes(), 0, &lay_);
+
+    const long long tmo = opt.timeout_ms >= 0 ? opt.timeout_ms : env::TimeoutMs();
+    timeout_ns_ = static_cast<uint64_t>(std::max<long long>(tmo, 1)) * 1000000ull;
+
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, dev0) != cudaSuccess) {
+        if (err) *err = "cudaGetDeviceProperties failed";
+        return Result::CudaError;
+    }
+    // Emulated ranks share one GPU and run in one cooperative launch: every CTA of every
+    // rank must be resident (two 512-thread CTAs per SM are guaranteed by the launch bounds).
+    max_ctas_ = emulated_ ? std::max(1, prop.multiProcessorCount * 2 / world_) : prop.multiProcessorCount * 8;
+
+    for (Local& l : local_) {
+        if (cudaSetDevice(l.device) != cudaSuccess || cudaStreamCreate(&l.stream) != cudaSuccess ||
+            cudaHostAlloc(reinterpret_cast<void**>(&l.status), sizeof(DeviceStatus), cudaHostAllocMapped |
+                                                                                         cudaHostAllocPortable) !=
+                cudaSuccess) {
+            (void)cudaGetLastError();
+            if (err) *err = "stream / status allocation failed on GPU " + std::to_string(l.device);
+            return Result::CudaError;
+        }
+        std::memset(l.status, 0, sizeof(DeviceStatus));
+    }
+    cudaSetDevice(dev0);
+    if (env::DebugLevel() > 0 && local_[0].rank == 0)
+        std::fprintf(stderr, "[yali] world=%d nlocal=%d heap=%s %.0f MiB multicast=%d emulated=%d\n", world_, nlocal(),
+                     heaps_->kind(), lay_.total_bytes / 1048576.0, has_multicast() ? 1 : 0, emulated_ ? 1 : 0);
+    return Result::Success;
+}
+
+Communicator::~Communicator() {
+    for (Local& l : local_) {
+        if (cudaSetDevice(l.device) == cudaSuccess) cudaDeviceSynchronize();
+    }
+    // Nobody unmaps or unbinds while a peer may still touch this rank's heap.
+    if (bs_) bs_->barrier();
+    for (void* p : ipc_opened_) cudaIpcCloseMemHandle(p);
+    heaps_.reset();
+    for (Local& l : local_) {
+        if (cudaSetDevice(l.device) != cudaSuccess) continue;
+        if (l.status) cudaFreeHost(l.status);
+        if (l.stream) cudaStreamDestroy(l.stream);
+    }
+    (void)cudaGetLastError();
+}
+
+CommView Communicator::View(int i) const {
+    CommView v;
+    std::memset(&v, 0, sizeof(v));
+    for (int q = 0; q < world_; ++q) v.heap[q] = heaps_->base(q);
+    v.mc_heap = heaps_->mc_base();
+    v.lay = lay_;
+    v.status = local_[i].status;
+    v.timeout_ns = timeout_ns_;
+    v.rank = local_[i].rank;
+    v.world = world_;
+    return v;
+}
+
+uint32_t Communicator::TakeBarrierEpochs(uint32_t n) {
+    uint32_t e = bar_epoch_;
+    bar_epoch_ += n;
+    return e;
+}
+
+bool Communicator::IsSymmetric(int i, const void* p, uint64_t bytes) const {
+    const char* base = heaps_->base(local_[i].rank);
+    const char* c = static_cast<const char*>(p);
+    return c >= base + lay_.user_off && c + bytes <= base + lay_.total_bytes;
+}
+
+Result Communicator::SymmAlloc(uint64_t bytes, std::vector<void*>* ptrs) {
+    const uint64_t need = RoundUp(std::max<uint64_t>(bytes, 1), 256);
+    if (user_bump_ + need > lay_.user_bytes)
+        return Fail(Result::InvalidArg, "symmetric heap exhausted: " + std::to_string(lay_.user_bytes - user_bump_) +
+                                            " bytes left, " + std::to_string(need) +
+                                            " requested (raise YALI_HEAP_BYTES)");
+    ptrs->clear();
+    for (const Local& l : local_) ptrs->push_back(heaps_->base(l.rank) + lay_.user_off + user_bump_);
+    user_bump_ += need;
+    return Result::Success;
+}
+
+// Fills the peer tables.  Single process: every rank's pointers are known and
+// addressable.  Multi process: only heap buffers (same offset on every rank) are.
+Result Communicator::ResolvePeers(const void* const* send, void* const* recv, uint64_t send_bytes, uint64_t recv_bytes,
+                                  bool /*stable*/, CollArgs* args, bool* peer_recv, bool* symmetric) {
+    bool all_sym = true;
+    for (int i = 0; i < nlocal(); ++i) {
+        if (!IsSymmetric(i, send[i], send_bytes) || !IsSymmetric(i, recv[i], recv_bytes)) all_sym = false;
+    }
+    if (all_sym && nlocal() > 1) {
+        // Equal offsets on all local ranks?
+        const uint64_t so = static_cast<const char*>(send[0]) - heaps_->base(local_[0].rank);
+        const uint64_t ro = static_cast<const char*>(recv[0]) - heaps_->base(local_[0].rank);
+        for (int i = 1; i < nlocal(); ++i) {
+            if (static_cast<uint64_t>(static_cast<const char*>(send[i]) - heaps_->base(local_[i].rank)) != so ||
+                static_cast<uint64_t>(static_cast<const char*>(recv[i]) - heaps_->base(local_[i].rank)) != ro)
+                all_sym = false;
+        }
+    }
+    *symmetric = all_sym;
+    *peer_recv = false;
+    for (int i = 0; i < nlocal(); ++i) {
+        for (int q = 0; q < kMaxRanks; ++q) {
+            args[i].peer_send[q] = nullptr;
+            args[i].peer_recv[q] = nullptr;
+        }
+    }
+    if (single_process_) {
+        for (int i = 0; i < nlocal(); ++i) {
+            for (int j = 0; j < nlocal(); ++j) {
+                args[i].peer_send[local_[j].rank] = send[j];
+                args[i].peer_recv[local_[j].rank] = recv[j];
+            }
+        }
+        *peer_recv = true;
+    } else if (all_sym) {
+        const uint64_t so = static_cast<const char*>(send[0]) - heaps_->base(local_[0].rank);
+        const uint64_t ro = static_cast<const char*>(recv[0]) - heaps_->base(local_[0].rank);
+        for (int q = 0; q < world_; ++q) {
+            args[0].peer_send[q] = heaps_->base(q) + so;
+            args[0].peer_recv[q] = heaps_->base(q) + ro;
+        }
+        *peer_recv = true;
+    }
+    return Result::Success;
+}
+
+Result Communicator::Launch(const Plan& plan, Dtype in, Dtype out, int epilogue, CollArgs* args,
+                            const cudaStream_t* streams) {
+    const void* fn = nullptr;
+    int threads = 0;
+    switch (plan.variant) {
+        case Variant::Flash:
+            fn = FlashKernelFor(in, out, epilogue, world_, emulated_);
+            threads = kFlashThreads;
+            break;
+        case Variant::Stream:
+            fn = StreamKernelFor(in, out, epilogue, world_, emulated_);
+            threads = kStreamThreads;
+            break;
+        case Variant::NvlsOneShot:
+        case Variant::NvlsTwoShot:
+            if (emulated_) return Fail(Result::Unsupported, "multicast kernels cannot run on emulated ranks");
+            fn = NvlsKernelFor(in, world_, plan.variant == Variant::NvlsTwoShot);
+            threads = kNvlsThreads;
+            break;
+    }
+    if (!fn) return Fail(Result::Unsupported, "no kernel for this dtype / epilogue combination");
+    if (epilogue == kEpiResidualRmsNorm) {
+        // One thread handles up to four 16-byte vectors of a row.
+        const int vec = 16 / static_cast<int>(DtypeSize(in));
+        const int vec_per_row = args[0].ep.hidden / vec;
+        threads = std::min(kFlashThreads, std::max(32, (vec_per_row + 31) / 32 * 32));
+    }
+    if (emulated_) {
+        EmuArgs e;
+        std::memset(&e, 0, sizeof(e));
+        for (int i = 0; i < nlocal(); ++i) e.r[local_[i].rank] = args[i];
+        cudaStream_t s = streams && streams[0] ? streams[0] : local_[0].stream;
+        void* params[] = {&e};
+        cudaError_t ce = cudaLaunchCooperativeKernel(fn, dim3(plan.ctas, world_), dim3(threads), params, 0, s);
+        if (ce != cudaSuccess) {
+            (void)cudaGetLastError();
+            return Fail(Result::CudaError, std::string("cooperative launch failed: ") + cudaGetErrorString(ce));
+        }
+        last_.launches += 1;
+        return Result::Success;
+    }
+    for (int i = 0; i < nlocal(); ++i) {
+        if (nlocal() > 1 && cudaSetDevice(local_[i].device) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return Fail(Result::CudaError, "cudaSetDevice failed");
+        }
+        cudaStream_t s = streams && streams[i] ? streams[i] : local_[i].stream;
+        void* params[] = {&args[i]};
+        cudaError_t ce = cudaLaunchKernel(fn, dim3(plan.ctas), dim3(threads), params, 0, s);
+        if (ce != cudaSuccess) {
+            (void)cudaGetLastError();
+            return Fail(Result::CudaError, std::string("kernel launch failed: ") + cudaGetErrorString(ce));
+        }
+        last_.launches += 1;
+    }
+    return Result::Success;
+}
+
+Result Communicator::Collective(const void* const* send, void* const* recv, uint64_t count, Dtype in, Dtype out,
+                                const OpOptions& opt, const cudaStream_t* streams, uint32_t extra_flags) {
+    if (poisoned_) return Fail(Result::Timeout, "communicator is poisoned by an earlier timeout; call Reset()");
+    if (!send || !recv) return Fail(Result::InvalidArg, "null buffer table");
+    if (count == 0) return Result::Success;
+    for (int i = 0; i < nlocal(); ++i)
+        if (!send[i] || !recv[i]) return Fail(Result::InvalidArg, "null buffer");
+    if (count > (1ull << 40)) return Fail(Result::InvalidArg, "count too large");
+
+    const bool rs_only = extra_flags & kFlagReduceScatterOnly, ag_only = extra_flags & kFlagAllGatherOnly;
+    const uint64_t shard = ShardElems(count, world_);
+    const uint64_t send_elems = ag_only ? shard : count, recv_elems = rs_only ? shard : count;
+    const uint64_t send_bytes = send_elems * DtypeSize(in), recv_bytes = recv_elems * DtypeSize(out);
+
+    std::vector<CollArgs> args(nlocal());
+    std::memset(args.data(), 0, sizeof(CollArgs) * args.size());
+    bool peer_recv = false, symmetric = false;
+    Result r = ResolvePeers(send, recv, send_bytes, recv_bytes, opt.buffers_stable, args.data(), &peer_recv, &symmetric);
+    if (r != Result::Success) return r;
+
+    PlanCaps caps;
+    caps.flash_cap = lay_.flash_cap;
+    caps.ring_bytes = lay_.ring_bytes;
+    caps.nvls_cap = lay_.nvls_cap;
+    caps.has_multicast = has_multicast();
+    caps.symmetric = symmetric;
+    caps.peer_recv = peer_recv && !rs_only;
+    caps.max_ctas = max_ctas_;
+    caps.vec_ok = true;
+    for (int i = 0; i < nlocal(); ++i) caps.vec_ok = caps.vec_ok && Aligned16(send[i]) && Aligned16(recv[i]);
+
+    KernelMode mode = opt.mode;
+    if (mode == KernelMode::Auto) mode = env::ForcedKernelMode();
+    if (rs_only || ag_only) mode = KernelMode::Stream;
+    Plan plan;
+    std::string why;
+    r = MakePlan(world_, count, in, out, opt.epilogue, mode, caps, EnvTuningTable(), &plan, &why);
+    if (r != Result::Success) return Fail(r, why);
+    if (opt.ctas > 0) {
+        const uint32_t lim = plan.variant == Variant::Stream ? kMaxLanes
+                                                             : (plan.variant == Variant::Flash ? kMaxFlashCtas : kBarSlots);
+        plan.ctas = std::min<uint32_t>(std::min<uint32_t>(opt.ctas, max_ctas_), lim);
+    }
+    if (world_ == 1 && plan.variant != Variant::Flash)
+        return Fail(Result::Unsupported, "a single rank only runs the one-shot kernel");
+
+    EpilogueParams ep;
+    std::memset(&ep, 0, sizeof(ep));
+    ep.scale = opt.epilogue == kEpiScaleCast ? opt.scale : 1.0f;
+    if (opt.epilogue == kEpiResidualRmsNorm) {
+        const int vec = 16 / static_cast<int>(DtypeSize(in));
+        if (in != out || opt.hidden <= 0 || count % opt.hidden != 0 || opt.hidden % vec != 0 ||
+            opt.hidden / vec > 4 * kFlashThreads || !opt.weight || !caps.vec_ok)
+            return Fail(Result::Unsupported,
+                        "fused RMSNorm needs equal in/out dtype, count a multiple of hidden, hidden a multiple of "
+                        "16 bytes and at most 4*512 vectors, 16-byte aligned buffers and a weight");
+        plan.ctas = static_cast<uint32_t>(std::min<uint64_t>(plan.ctas, count / opt.hidden));
+        ep.eps = opt.eps;
+        ep.hidden = opt.hidden;
+    }
+
+    uint32_t epoch = 0, seq_base = 0;
+    switch (plan.variant) {
+        case Variant::Flash: epoch = ++flash_epoch_; break;
+        case Variant::Stream:
+            seq_base = stream_seq_;
+            stream_seq_ += plan.max_iters;
+            break;
+        default: epoch = TakeBarrierEpochs(2); break;
+    }
+    plan.flags |= extra_flags;
+    for (int i = 0; i < nlocal(); ++i) {
+        CollArgs& a = args[i];
+        a.cv = View(i);
+        a.send = send[i];
+        a.recv = recv[i];
+        a.count = count;
+        a.epoch = epoch;
+        a.seq_base = seq_base;
+        a.ctas = plan.ctas;
+        a.slot_bytes = plan.slot_bytes;
+        a.shard_elems = plan.shard_elems;
+        a.flags = plan.flags;
+        // Alignment is a per-rank property: it selects the vector or the scalar code path only.
+        if (!(Aligned16(send[i]) && Aligned16(recv[i]))) a.flags &= ~static_cast<uint32_t>(kFlagVecOk);
+        else a.flags |= kFlagVecOk;
+        if (opt.skip_rank >= 0 && local_[i].rank == opt.skip_rank) a.flags |= kFlagSkipRank;
+        a.ep = ep;
+        if (opt.epilogue == kEpiResidualRmsNorm) {
+            a.ep.residual = opt.residual ? opt.residual[i] : nullptr;
+            a.ep.residual_out = opt.residual_out ? opt.residual_out[i] : nullptr;
+            a.ep.weight = opt.weight[i];
+        }
+    }
+    last_.variant = plan.variant;
+    last_.ctas = plan.ctas;
+    last_.slot_bytes = plan.slot_bytes;
+    last_.flags = plan.flags;
+    if (env::DebugLevel() > 1 && local_[0].rank == 0)
+        std::fprintf(stderr, "[yali] %s count=%llu ctas=%u slot=%u flags=0x%x epoch=%u seq=%u\n",
+                     VariantName(plan.variant), static_cast<unsigned long long>(count), plan.ctas, plan.slot_bytes,
+                     plan.flags, epoch, seq_base);
+    return Launch(plan, in, out, opt.epilogue, args.data(), streams);
+}
+
+Result Communicator::AllReduce(const void* const* send, void* const* recv, uint64_t count, Dtype in, Dtype out,
+                               const OpOptions& opt, const cudaStream_t* streams) {
+    return Collective(send, recv, count, in, out, opt, streams, 0);
+}
+
+Result Communicator::ReduceScatter(const void* const* send, void* const* recv, uint64_t count, Dtype dt,
+                                   const OpOptions& opt, const cudaStream_t* streams) {
+    if (world_ == 1) return Collective(send, recv, count, dt, dt, opt, streams, 0);
+    return Collective(send, recv, count, dt, dt, opt, streams, kFlagReduceScatterOnly);
+}
+
+Result Communicator::AllGather(const void* const* send, void* const* recv, uint64_t count, Dtype dt,
+                               const OpOptions& opt, const cudaStream_t* streams) {
+    if (world_ == 1) return Collective(send, recv, count, dt, dt, opt, streams, 0);
+    return Collective(send, recv, count, dt, dt, opt, streams, kFlagAllGatherOnly);
+}
+
+Result Communicator::Check() {
+    for (const Local& l : local_) {
+        if (l.status && *reinterpret_cast<volatile uint32_t*>(&l.status->code) != 0) {
+            poisoned_ = true;
+            return Fail(Result::Timeout, DescribeStatus());
+        }
+    }
+    return Result::Success;
+}
+
+Result Communicator::Sync(const cudaStream_t* streams) {
+    for (int i = 0; i < nlocal(); ++i) {
+        if (nlocal() > 1) cudaSetDevice(local_[i].device);
+        cudaStream_t s = streams && streams[i] ? streams[i] : local_[i].stream;
+        cudaError_t e = cudaStreamSynchronize(s);
+        if (e != cudaSuccess) {
+            (void)cudaGetLastError();
+            return Fail(Result::CudaError, std::string("cudaStreamSynchronize: ") + cudaGetErrorString(e));
+        }
+        if (emulated_) break;  // one launch served every rank
+    }
+    return Check();
+}
+
+std::string Communicator::DescribeStatus() const {
+    static const char* const sites[] = {"none",          "one-shot arrival", "ring credit", "reduce-scatter slot",
+                                        "all-gather slot", "ring drain",       "CTA barrier", "GEMM partials",
+                                        "GEMM done",     "mbarrier"};
+    for (const Local& l : local_) {
+        const DeviceStatus s = *l.status;
+        if (s.code == 0) continue;
+        char buf[256];
+        std::snprintf(buf, sizeof(buf),
+                      "rank %u gave up waiting for rank %u at '%s' (cta/lane %u): wanted %u, saw %u", s.rank, s.peer,
+                      s.code < 10 ? sites[s.code] : "?", s.cta, s.wanted, s.observed);
+        return buf;
+    }
+    return "";
+}
+
+Result Communicator::Barrier() {
+    for (const Local& l : local_) {
+        cudaSetDevice(l.device);
+        cudaError_t e = cudaDeviceSynchronize();
+        if (e != cudaSuccess) return Fail(Result::CudaError, cudaGetErrorString(e));
+    }
+    if (bs_ && bs_->barrier() != Result::Success) return Fail(Result::BootstrapError, bs_->last_error());
+    return Result::Success;
+}
+
+Result Communicator::Reset() {
+    Result r = Barrier();
+    if (r != Result::Success) return r;
+    for (const Local& l : local_) {
+        cudaSetDevice(l.device);
+        if (cudaMemset(heaps_->base(l.rank) + lay_.flags_off, 0, kFlagRegionBytes) != cudaSuccess ||
+            cudaDeviceSynchronize() != cudaSuccess)
+            return Fail(Result::CudaError, "clearing the flag region failed");
+        std::memset(l.status, 0, sizeof(DeviceStatus));
+    }
+    flash_epoch_ = bar_epoch_ = stream_seq_ = gemm_epoch_ = 0;
+    poisoned_ = false;
+    if (bs_ && bs_->barrier() != Result::Success) return Fail(Result::BootstrapError, bs_->last_error());
+    return Result::Success;
+}
+
+}  // namespace yali

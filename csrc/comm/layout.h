@@ -1,0 +1,137 @@
+// Layout of the symmetric heap and the by-value argument blocks of the kernels.
+// Shared by host and device code.
+//
+// Parity: the reference passes one YaliLaunchArgs per lane through a device array
+// that is memcpy'd before every launch (src/include/yali_launch.h:16-58,
+// src/ops/allreduce.cuh:753-761) and allocates three cudaMalloc blocks per lane
+// for the ring (allreduce.cuh:388-458).  Here each rank owns ONE allocation (the
+// heap) that is mapped on every peer; flags, one-shot staging, ring slots, NVLS
+// staging and user-visible symmetric buffers live at fixed offsets in it, and
+// kernels receive everything they need as a parameter struct.
+#pragma once
+
+#include <stdint.h>
+
+#include "../core/status.h"
+
+namespace yali {
+
+// ---- control words (uint32 indices into the flag region; zero-initialised, monotone) ----
+constexpr int kMaxFlashCtas = 2048;  // one flag row per CTA of the one-shot kernel
+constexpr int kMaxLanes = 256;       // lanes (CTAs) of the two-shot ring kernel
+constexpr int kBarSlots = 1024;      // per-CTA cross-rank barriers (NVLS and fused kernels)
+constexpr int kGemmRowBlocks = 256;  // arrival counters of the fused GEMM, one per 128-row block
+
+constexpr uint32_t kFlashFlagOff = 0;                                        // [kMaxFlashCtas][kMaxRanks]
+constexpr uint32_t kRsSeqOff = kFlashFlagOff + kMaxFlashCtas * kMaxRanks;    // [kMaxLanes][kMaxRanks]
+constexpr uint32_t kAgSeqOff = kRsSeqOff + kMaxLanes * kMaxRanks;            // [kMaxLanes][kMaxRanks]
+constexpr uint32_t kCreditOff = kAgSeqOff + kMaxLanes * kMaxRanks;           // [kMaxLanes][kMaxRanks]
+constexpr uint32_t kBarOff = kCreditOff + kMaxLanes * kMaxRanks;             // [kBarSlots][kMaxRanks]
+constexpr uint32_t kGemmCntOff = kBarOff + kBarSlots * kMaxRanks;            // [kGemmRowBlocks][kMaxRanks]
+constexpr uint32_t kGemmDoneOff = kGemmCntOff + kGemmRowBlocks * kMaxRanks;  // [kGemmRowBlocks][kMaxRanks]
+constexpr uint32_t kStatusCntOff = kGemmDoneOff + kGemmRowBlocks * kMaxRanks;  // [1] timeouts seen by this rank
+constexpr uint32_t kFlagWords = kStatusCntOff + 8;
+constexpr uint64_t kFlagRegionBytes = 1ull << 20;
+static_assert(kFlagWords * 4ull <= kFlagRegionBytes, "flag region too small");
+
+constexpr int kRingCap = 4;  // slots per (lane, source) ring
+
+struct HeapLayout {
+    uint64_t total_bytes;
+    uint64_t flags_off;    // kFlagRegionBytes of uint32 control words
+    uint64_t flash_off;    // one-shot staging: [2 parities][world-1 sources][flash_cap]
+    uint64_t flash_cap;    // largest one-shot message in bytes
+    uint64_t ring_off;     // two-shot rings: [lane][world-1 sources][kRingCap][2 (RS, AG)][slot]
+    uint64_t ring_bytes;
+    uint64_t nvls_off;     // staging for multimem kernels when user buffers are not in the heap: [2][nvls_cap]
+    uint64_t nvls_cap;
+    uint64_t gemm_off;     // partial-sum landing zone of the fused GEMM: [2][world][gemm_cap]
+    uint64_t gemm_cap;
+    uint64_t user_off;     // symmetric allocations handed to the user
+    uint64_t user_bytes;
+};
+
+// Default sizing for a world size; `requested_total` of 0 picks the default.
+// Returns false when the request is too small to hold the fixed regions.
+bool MakeHeapLayout(int world, uint64_t requested_total, uint64_t granularity, HeapLayout* out);
+
+// Index of source rank `src` in the per-destination arrays that skip the owner.
+__host__ __device__ inline int SrcSlot(int src, int owner) { return src < owner ? src : src - 1; }
+
+// What a device-side wait writes when it gives up.  Lives in pinned host memory
+// that the device can write, one block per rank.
+enum WaitSite : uint32_t {
+    kSiteNone = 0,
+    kSiteFlashArrive = 1,
+    kSiteStreamCredit = 2,
+    kSiteStreamRs = 3,
+    kSiteStreamAg = 4,
+    kSiteStreamDrain = 5,
+    kSiteBarrier = 6,
+    kSiteGemmPartials = 7,
+    kSiteGemmDone = 8,
+    kSiteMbar = 9,
+};
+struct DeviceStatus {
+    uint32_t code;      // 0 = ok, otherwise a WaitSite
+    uint32_t rank;
+    uint32_t peer;
+    uint32_t cta;
+    uint32_t wanted;
+    uint32_t observed;
+    uint32_t pad[2];
+};
+
+// One rank's view of the communicator.
+struct CommView {
+    char* heap[kMaxRanks];  // heap base of every rank as mapped for this device
+    char* mc_heap;          // multicast mapping of the heaps, nullptr without NVLS
+    HeapLayout lay;
+    DeviceStatus* status;
+    uint64_t timeout_ns;
+    int rank;
+    int world;
+};
+
+enum EpilogueKind : int { kEpiIdentity = 0, kEpiScaleCast = 1, kEpiResidualRmsNorm = 2 };
+
+struct EpilogueParams {
+    float scale;            // kEpiScaleCast: out = cast(sum * scale)
+    float eps;              // kEpiResidualRmsNorm
+    int hidden;             // row length of the RMSNorm
+    const void* residual;   // [rows, hidden], output dtype; may be nullptr
+    void* residual_out;     // optional: sum + residual before normalisation
+    const void* weight;     // [hidden], output dtype
+};
+
+struct CollArgs {
+    CommView cv;
+    const void* send;                   // this rank's input
+    void* recv;                         // this rank's output
+    const void* peer_send[kMaxRanks];   // inputs of all ranks when they are peer-addressable, else nullptr
+    void* peer_recv[kMaxRanks];         // outputs of all ranks when they are peer-addressable, else nullptr
+    uint64_t count;                     // elements
+    uint32_t epoch;                     // one-shot / barrier epoch of this call
+    uint32_t seq_base;                  // two-shot: sequence number before this call
+    uint32_t ctas;                      // CTAs (one-shot, NVLS) or lanes (two-shot) per rank
+    uint32_t slot_bytes;                // two-shot ring slot size
+    uint64_t shard_elems;               // two-shot / NVLS: elements owned by each rank
+    uint32_t flags;                     // CollFlags
+    EpilogueParams ep;
+};
+
+enum CollFlags : uint32_t {
+    kFlagVecOk = 1u << 0,       // pointers 16-byte aligned: vector path
+    kFlagDirectAg = 1u << 1,    // all-gather writes straight into peer_recv
+    kFlagSymmetric = 1u << 2,   // NVLS: send/recv live in the heap at cv offsets (zero copy)
+    kFlagReduceScatterOnly = 1u << 3,
+    kFlagAllGatherOnly = 1u << 4,
+    kFlagSkipRank = 1u << 5,    // this rank leaves at once (models a rank that never launched; tests of the timeouts)
+};
+
+// All ranks of an emulated communicator in one launch (ranks = blockIdx.y).
+struct EmuArgs {
+    CollArgs r[kMaxRanks];
+};
+
+}  // namespace yali

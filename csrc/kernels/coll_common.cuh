@@ -1,0 +1,102 @@
+// Device helpers shared by the collective kernels: addressing of the heap
+// regions, bounded waits that record where they gave up, and the per-CTA
+// cross-rank barrier.
+//
+// Parity: src/kernels/ring.cuh:103-128 (wait_for_credit / wait_for_slot spin
+// without limit, thread 0 only).  Here one thread per peer waits, every wait has
+// a deadline, and a wait that runs out records {site, rank, peer, cta, wanted,
+// observed} in the rank's status block and makes the whole CTA leave normally.
+#pragma once
+
+#include "../comm/layout.h"
+#include "../core/ptx.cuh"
+#include "type_ops.cuh"
+
+namespace yali {
+
+__device__ __forceinline__ uint32_t* flag_word(const CommView& cv, int on_rank, uint32_t word) {
+    return reinterpret_cast<uint32_t*>(cv.heap[on_rank] + cv.lay.flags_off) + word;
+}
+
+// One-shot staging: where source rank `src` deposits its copy on rank `on_rank`.
+__device__ __forceinline__ char* flash_stage(const CommView& cv, int on_rank, int src, uint32_t parity) {
+    return cv.heap[on_rank] + cv.lay.flash_off +
+           (static_cast<uint64_t>(parity) * (cv.world - 1) + SrcSlot(src, on_rank)) * cv.lay.flash_cap;
+}
+
+// Two-shot ring slot on rank `on_rank` filled by `src`: which = 0 reduce-scatter, 1 all-gather.
+__device__ __forceinline__ char* ring_slot(const CommView& cv, int on_rank, int src, uint32_t lane, uint32_t slot,
+                                           uint32_t which, uint32_t slot_bytes) {
+    uint64_t idx = ((static_cast<uint64_t>(lane) * (cv.world - 1) + SrcSlot(src, on_rank)) * kRingCap + slot) * 2 + which;
+    return cv.heap[on_rank] + cv.lay.ring_off + idx * slot_bytes;
+}
+
+// Records the first wait of this rank that gave up.  The status block is pinned
+// host memory (read by the host without a copy), written with plain stores; the
+// election of the first reporter uses a counter in this rank's own heap.
+__device__ __forceinline__ void report_timeout(const CommView& cv, uint32_t site, uint32_t peer, uint32_t cta,
+                                               uint32_t wanted, uint32_t observed) {
+    volatile DeviceStatus* st = cv.status;
+    if (!st) return;
+    uint32_t prev = atomicAdd(flag_word(cv, cv.rank, kStatusCntOff), 1u);
+    if (prev == 0) {
+        st->rank = cv.rank;
+        st->peer = peer;
+        st->cta = cta;
+        st->wanted = wanted;
+        st->observed = observed;
+        __threadfence_system();
+        st->code = site;
+        __threadfence_system();
+    }
+}
+
+// Threads 0..world-1 (except `rank`) each wait for the flag that peer `tid`
+// writes into this rank's heap at `word_base + tid`.  Returns, on every thread of
+// the CTA, whether all flags arrived.  Contains two CTA barriers.
+__device__ __forceinline__ bool wait_peers(const CommView& cv, uint32_t word_base, uint32_t wanted,
+                                           uint64_t deadline_ns, uint32_t site, uint32_t cta, int* s_abort) {
+    const int tid = threadIdx.x;
+    if (tid < cv.world && tid != cv.rank) {
+        uint32_t seen;
+        if (!ptx::wait_flag_reached(flag_word(cv, cv.rank, word_base + tid), wanted, deadline_ns, &seen)) {
+            report_timeout(cv, site, tid, cta, wanted, seen);
+            *s_abort = 1;
+        }
+    }
+    __syncthreads();
+    return *s_abort == 0;
+}
+
+// After a CTA barrier: threads 0..world-1 (except `rank`) publish `value` into
+// word `word_base + rank` of every peer's flag region with release semantics, so
+// that everything the CTA wrote before the barrier is visible to whoever
+// acquires the flag.
+__device__ __forceinline__ void signal_peers(const CommView& cv, uint32_t word_base, uint32_t value) {
+    const int tid = threadIdx.x;
+    if (tid < cv.world && tid != cv.rank) ptx::st_release_sys(flag_word(cv, tid, word_base + cv.rank), value);
+}
+
+// Cross-rank barrier among the CTAs with index `cta` of all ranks.
+__device__ __forceinline__ bool cta_barrier_all_ranks(const CommView& cv, uint32_t cta, uint32_t epoch,
+                                                      uint64_t deadline_ns, int* s_abort) {
+    __syncthreads();
+    signal_peers(cv, kBarOff + cta * kMaxRanks, epoch);
+    return wait_peers(cv, kBarOff + cta * kMaxRanks, epoch, deadline_ns, kSiteBarrier, cta, s_abort);
+}
+
+// Block-wide sum of one float per thread (all threads get the result).
+__device__ __forceinline__ float block_sum(float v, float* s_red /* >= 32 floats */) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = (blockDim.x + 31) >> 5;
+    __syncthreads();  // protect s_red from the previous use
+    if (lane == 0) s_red[warp] = v;
+    __syncthreads();
+    float t = (lane < nwarps) ? s_red[lane] : 0.f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+    return t;
+}
+
+}  // namespace yali

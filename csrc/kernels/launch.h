@@ -1,0 +1,27 @@
+// Host-side entry points of the kernel translation units.  Each returns the
+// __global__ function for a (dtype, epilogue, world) combination so that the
+// dispatcher can launch it with cudaLaunchKernel (one rank per launch) or, for
+// an emulated communicator whose ranks share one GPU, with a cooperative launch
+// of the *_emu twin (ranks = blockIdx.y), which guarantees that all CTAs that
+// wait on one another are resident together.
+//
+// Parity: src/all_reduce/kernels.cuh:41-55 (LaunchFlashKernel) and the
+// extern "C" YaliKernel symbols of src/kernels/stream.cu:104-111.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include "../comm/layout.h"
+
+namespace yali {
+
+constexpr int kFlashThreads = 512;
+constexpr int kStreamThreads = 512;
+constexpr int kNvlsThreads = 512;
+
+// nullptr when the combination is not built.
+const void* FlashKernelFor(Dtype in, Dtype out, int epilogue, int world, bool emu);
+const void* StreamKernelFor(Dtype in, Dtype out, int epilogue, int world, bool emu);
+const void* NvlsKernelFor(Dtype dt, int world, bool two_shot);
+
+}  // namespace yali

@@ -1,0 +1,154 @@
+// Buffer utilities: seeded fills, conversion to fp32 and on-device validation of
+// an all-reduce result against the sum recomputed from the generators in fp64.
+//
+// Parity: seed_buffer_kernel / SeedBufferSync / ZeroBuffer / AllocAndSeed
+// (src/common/buffer_ops.cuh:16-59) fill with one constant per rank, and
+// convert_to_float_kernel / VerifyAllReduceSum / ValidateRankResult
+// (src/common/validation.cuh:18-115) copy the result to the host and expect
+// N(N+1)/2 everywhere.  Constant fills are kept; in addition a counter-based
+// generator (Philox4x32-10, identical on host and device) gives every element of
+// every rank its own U(-1,1) or N(0,1) value, so a missing, duplicated or
+// misplaced contribution changes the numbers.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "../ops/buffer_ops.h"
+#include "type_ops.cuh"
+
+namespace yali {
+
+namespace {
+
+template <typename T>
+__global__ void fill_constant_kernel(T* p, uint64_t n, float v) {
+    const T x = from_f32<T>(v);
+    for (uint64_t i = blockIdx.x * static_cast<uint64_t>(blockDim.x) + threadIdx.x; i < n;
+         i += static_cast<uint64_t>(gridDim.x) * blockDim.x)
+        p[i] = x;
+}
+
+template <typename T>
+__global__ void fill_random_kernel(T* p, uint64_t n, int dist, uint64_t seed) {
+    for (uint64_t i = blockIdx.x * static_cast<uint64_t>(blockDim.x) + threadIdx.x; i < n;
+         i += static_cast<uint64_t>(gridDim.x) * blockDim.x)
+        p[i] = from_f32<T>(RandomValue(dist, seed, i));
+}
+
+template <typename T>
+__global__ void to_float_kernel(const T* src, float* dst, uint64_t n) {
+    for (uint64_t i = blockIdx.x * static_cast<uint64_t>(blockDim.x) + threadIdx.x; i < n;
+         i += static_cast<uint64_t>(gridDim.x) * blockDim.x)
+        dst[i] = to_f32<T>(src[i]);
+}
+
+// expected[i] = scale * sum_r round_to_Tin(gen(seed_base + r, i)) in fp64.
+template <typename Tin, typename Tout>
+__global__ void validate_sum_kernel(const Tout* out, uint64_t n, uint64_t index_offset, int dist, uint64_t seed_base,
+                                    int world, float scale, double rtol, double atol, ValidateReport* rep) {
+    unsigned long long bad = 0;
+    double worst = 0.0;
+    unsigned long long first = ~0ull;
+    for (uint64_t i = blockIdx.x * static_cast<uint64_t>(blockDim.x) + threadIdx.x; i < n;
+         i += static_cast<uint64_t>(gridDim.x) * blockDim.x) {
+        double e = 0.0;
+        for (int r = 0; r < world; ++r)
+            e += static_cast<double>(to_f32<Tin>(from_f32<Tin>(RandomValue(dist, seed_base + r, index_offset + i))));
+        e *= static_cast<double>(scale);
+        const double got = static_cast<double>(to_f32<Tout>(out[i]));
+        const double err = fabs(got - e);
+        if (!(err <= atol + rtol * fabs(e))) {
+            ++bad;
+            if (i < first) first = i;
+        }
+        if (err > worst || err != err) worst = (err != err) ? 1e300 : err;
+    }
+    if (bad) {
+        atomicAdd(&rep->mismatches, bad);
+        atomicMin(&rep->first_mismatch, first);
+    }
+    // max of non-negative doubles == max of their bit patterns
+    atomicMax(reinterpret_cast<unsigned long long*>(&rep->max_abs_err),
+              static_cast<unsigned long long>(__double_as_longlong(worst)));
+}
+
+int GridFor(uint64_t n) {
+    uint64_t b = (n + 255) / 256;
+    if (b < 1) b = 1;
+    if (b > 148 * 8) b = 148 * 8;
+    return static_cast<int>(b);
+}
+
+template <typename Tin>
+cudaError_t ValidateOut(const void* out, Dtype out_dt, uint64_t n, uint64_t off, int dist, uint64_t seed, int world,
+                        float scale, double rtol, double atol, ValidateReport* d_rep, cudaStream_t s) {
+    switch (out_dt) {
+        case Dtype::FP32:
+            validate_sum_kernel<Tin, float><<<GridFor(n), 256, 0, s>>>(static_cast<const float*>(out), n, off, dist,
+                                                                       seed, world, scale, rtol, atol, d_rep);
+            break;
+        case Dtype::FP16:
+            validate_sum_kernel<Tin, __half><<<GridFor(n), 256, 0, s>>>(static_cast<const __half*>(out), n, off, dist,
+                                                                        seed, world, scale, rtol, atol, d_rep);
+            break;
+        case Dtype::BF16:
+            validate_sum_kernel<Tin, __nv_bfloat16><<<GridFor(n), 256, 0, s>>>(
+                static_cast<const __nv_bfloat16*>(out), n, off, dist, seed, world, scale, rtol, atol, d_rep);
+            break;
+    }
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t FillConstant(void* p, uint64_t n, Dtype dt, float v, cudaStream_t s) {
+    if (n == 0) return cudaSuccess;
+    switch (dt) {
+        case Dtype::FP32: fill_constant_kernel<<<GridFor(n), 256, 0, s>>>(static_cast<float*>(p), n, v); break;
+        case Dtype::FP16: fill_constant_kernel<<<GridFor(n), 256, 0, s>>>(static_cast<__half*>(p), n, v); break;
+        case Dtype::BF16: fill_constant_kernel<<<GridFor(n), 256, 0, s>>>(static_cast<__nv_bfloat16*>(p), n, v); break;
+    }
+    return cudaGetLastError();
+}
+
+cudaError_t FillRandom(void* p, uint64_t n, Dtype dt, int dist, uint64_t seed, cudaStream_t s) {
+    if (n == 0) return cudaSuccess;
+    switch (dt) {
+        case Dtype::FP32: fill_random_kernel<<<GridFor(n), 256, 0, s>>>(static_cast<float*>(p), n, dist, seed); break;
+        case Dtype::FP16: fill_random_kernel<<<GridFor(n), 256, 0, s>>>(static_cast<__half*>(p), n, dist, seed); break;
+        case Dtype::BF16:
+            fill_random_kernel<<<GridFor(n), 256, 0, s>>>(static_cast<__nv_bfloat16*>(p), n, dist, seed);
+            break;
+    }
+    return cudaGetLastError();
+}
+
+cudaError_t ConvertToFloat(const void* src, float* dst, uint64_t n, Dtype dt, cudaStream_t s) {
+    if (n == 0) return cudaSuccess;
+    switch (dt) {
+        case Dtype::FP32: to_float_kernel<<<GridFor(n), 256, 0, s>>>(static_cast<const float*>(src), dst, n); break;
+        case Dtype::FP16: to_float_kernel<<<GridFor(n), 256, 0, s>>>(static_cast<const __half*>(src), dst, n); break;
+        case Dtype::BF16:
+            to_float_kernel<<<GridFor(n), 256, 0, s>>>(static_cast<const __nv_bfloat16*>(src), dst, n);
+            break;
+    }
+    return cudaGetLastError();
+}
+
+cudaError_t ValidateSumAsync(const void* out, uint64_t n, uint64_t index_offset, Dtype in_dt, Dtype out_dt, int dist,
+                             uint64_t seed_base, int world, float scale, double rtol, double atol,
+                             ValidateReport* d_rep, cudaStream_t s) {
+    if (n == 0) return cudaSuccess;
+    switch (in_dt) {
+        case Dtype::FP32:
+            return ValidateOut<float>(out, out_dt, n, index_offset, dist, seed_base, world, scale, rtol, atol, d_rep, s);
+        case Dtype::FP16:
+            return ValidateOut<__half>(out, out_dt, n, index_offset, dist, seed_base, world, scale, rtol, atol, d_rep,
+                                       s);
+        case Dtype::BF16:
+            return ValidateOut<__nv_bfloat16>(out, out_dt, n, index_offset, dist, seed_base, world, scale, rtol, atol,
+                                              d_rep, s);
+    }
+    return cudaErrorInvalidValue;
+}
+
+}  // namespace yali

@@ -1,0 +1,319 @@
+#include "tuning.h"
+
+#include <algorithm>
+#include <cctype>
+#include <cstdio>
+#include <cstdlib>
+#include <fstream>
+#include <mutex>
+#include <sstream>
+
+#include "../core/env.h"
+
+namespace yali {
+
+const char* VariantName(Variant v) {
+    switch (v) {
+        case Variant::Flash: return "flash";
+        case Variant::Stream: return "stream";
+        case Variant::NvlsOneShot: return "nvls1";
+        case Variant::NvlsTwoShot: return "nvls2";
+    }
+    return "?";
+}
+
+namespace {
+uint64_t CeilDiv(uint64_t a, uint64_t b) { return (a + b - 1) / b; }
+uint64_t RoundUp(uint64_t a, uint64_t b) { return CeilDiv(a, b) * b; }
+}  // namespace
+
+// One-shot sends (N-1)*S per rank, two-shot 2(N-1)/N*S: at N=2 they tie and the
+// one-shot wins on latency up to its staging capacity; at larger N the one-shot
+// only pays off while the message is latency-bound.
+uint64_t FlashCrossoverBytes(Dtype /*dt*/, int world) {
+    if (world <= 2) return 64ull << 20;
+    if (world <= 4) return 1ull << 20;
+    return 256ull << 10;
+}
+
+int FlashLanePreset(uint64_t bytes, Dtype /*dt*/, int /*world*/) {
+    // About 8 KiB per CTA (one 16-byte vector per thread) while the message is
+    // small, then 32 KiB per CTA, capped by the flag rows.
+    if (bytes <= (8ull << 10)) return 1;
+    if (bytes <= (2ull << 20)) return static_cast<int>(std::min<uint64_t>(CeilDiv(bytes, 8ull << 10), 256));
+    return static_cast<int>(std::min<uint64_t>(std::max<uint64_t>(CeilDiv(bytes, 32ull << 10), 256), kMaxFlashCtas));
+}
+
+int StreamLanePreset(uint64_t bytes, Dtype /*dt*/, int /*world*/) {
+    if (bytes >= (64ull << 20)) return 148;
+    if (bytes >= (8ull << 20)) return 128;
+    if (bytes >= (1ull << 20)) return 64;
+    return 16;
+}
+
+uint64_t AutoSlotBytes(uint64_t bytes, int world) {
+    // Slot = one rank's piece of one shard.  Keep at least ~2 pieces per lane so
+    // the three pipeline stages overlap, and at most 256 KiB.
+    const uint64_t shard = CeilDiv(bytes, static_cast<uint64_t>(std::max(world, 1)));
+    uint64_t s = 256ull << 10;
+    while (s > (8ull << 10) && shard / s < 256) s >>= 1;
+    return s;
+}
+
+uint64_t ClampSlotBytes(uint64_t slot_bytes, uint64_t max_bytes) {
+    uint64_t s = std::max<uint64_t>(256, std::min(slot_bytes, max_bytes));
+    s = std::min<uint64_t>(s, 1ull << 30);
+    return s / 256 * 256;
+}
+
+int AutoCtasPerLane(bool use_flash, int lanes, uint64_t max_lane_elems, uint64_t tile_elems) {
+    if (!use_flash || lanes <= 0 || max_lane_elems == 0) return 1;
+    if (tile_elems == 0) tile_elems = 1;
+    return static_cast<int>(std::min<uint64_t>(std::max<uint64_t>(CeilDiv(max_lane_elems, tile_elems), 1), 32));
+}
+
+uint64_t ShardElems(uint64_t count, int world) {
+    return RoundUp(CeilDiv(count, static_cast<uint64_t>(std::max(world, 1))), 16);
+}
+
+// ------------------------------------------------------------------ tuning table
+namespace {
+
+struct Cursor {
+    const std::string& s;
+    size_t i = 0;
+    void ws() {
+        while (i < s.size() && std::isspace(static_cast<unsigned char>(s[i]))) ++i;
+    }
+    bool eat(char c) {
+        ws();
+        if (i < s.size() && s[i] == c) {
+            ++i;
+            return true;
+        }
+        return false;
+    }
+    bool str(std::string* out) {
+        ws();
+        if (i >= s.size() || s[i] != '"') return false;
+        size_t j = s.find('"', i + 1);
+        if (j == std::string::npos) return false;
+        *out = s.substr(i + 1, j - i - 1);
+        i = j + 1;
+        return true;
+    }
+    bool num(double* out) {
+        ws();
+        char* end = nullptr;
+        *out = std::strtod(s.c_str() + i, &end);
+        if (end == s.c_str() + i) return false;
+        i = static_cast<size_t>(end - s.c_str());
+        return true;
+    }
+};
+
+bool ParseVariant(const std::string& v, Variant* out) {
+    if (v == "flash") *out = Variant::Flash;
+    else if (v == "stream") *out = Variant::Stream;
+    else if (v == "nvls1") *out = Variant::NvlsOneShot;
+    else if (v == "nvls2") *out = Variant::NvlsTwoShot;
+    else return false;
+    return true;
+}
+
+}  // namespace
+
+void TuningTable::Add(const TuningRow& r) {
+    rows_.push_back(r);
+    std::stable_sort(rows_.begin(), rows_.end(), [](const TuningRow& a, const TuningRow& b) {
+        if (a.world != b.world) return a.world < b.world;
+        if (a.elem_bytes != b.elem_bytes) return a.elem_bytes > b.elem_bytes;  // specific before wildcard 0
+        return a.max_bytes < b.max_bytes;
+    });
+}
+
+bool TuningTable::Parse(const std::string& json, TuningTable* out, std::string* err) {
+    Cursor c{json};
+    auto fail = [&](const char* m) {
+        if (err) *err = std::string("tuning table: ") + m + " at offset " + std::to_string(c.i);
+        return false;
+    };
+    if (!c.eat('{')) return fail("expected '{'");
+    std::string key;
+    if (!c.str(&key) || key != "rows" || !c.eat(':') || !c.eat('[')) return fail("expected \"rows\": [");
+    TuningTable t;
+    if (!c.eat(']')) {
+        do {
+            if (!c.eat('{')) return fail("expected '{' of a row");
+            TuningRow row;
+            bool have_variant = false;
+            if (!c.eat('}')) {
+                do {
+                    if (!c.str(&key) || !c.eat(':')) return fail("expected \"key\":");
+                    if (key == "variant") {
+                        std::string v;
+                        if (!c.str(&v) || !ParseVariant(v, &row.variant)) return fail("bad variant");
+                        have_variant = true;
+                    } else {
+                        double x;
+                        if (!c.num(&x) || x < 0) return fail("expected a non-negative number");
+                        if (key == "world") row.world = static_cast<int>(x);
+                        else if (key == "elem_bytes") row.elem_bytes = static_cast<int>(x);
+                        else if (key == "max_bytes") row.max_bytes = static_cast<uint64_t>(x);
+                        else if (key == "ctas") row.ctas = static_cast<uint32_t>(x);
+                        else if (key == "slot_bytes") row.slot_bytes = static_cast<uint32_t>(x);
+                        // unknown numeric keys (measurements kept for the record) are ignored
+                    }
+                } while (c.eat(','));
+                if (!c.eat('}')) return fail("expected '}' of a row");
+            }
+            if (!have_variant || row.world < 1 || row.world > kMaxRanks || row.max_bytes == 0)
+                return fail("row needs world, max_bytes and variant");
+            t.Add(row);
+        } while (c.eat(','));
+        if (!c.eat(']')) return fail("expected ']'");
+    }
+    *out = t;
+    return true;
+}
+
+bool TuningTable::Load(const std::string& path, TuningTable* out, std::string* err) {
+    std::ifstream f(path);
+    if (!f) {
+        if (err) *err = "cannot open " + path;
+        return false;
+    }
+    std::stringstream ss;
+    ss << f.rdbuf();
+    return Parse(ss.str(), out, err);
+}
+
+const TuningRow* TuningTable::Find(int world, int elem_bytes, uint64_t bytes) const {
+    for (const TuningRow& r : rows_) {
+        if (r.world != world) continue;
+        if (r.elem_bytes != 0 && r.elem_bytes != elem_bytes) continue;
+        if (bytes <= r.max_bytes) return &r;
+    }
+    return nullptr;
+}
+
+const TuningTable* EnvTuningTable() {
+    static TuningTable table;
+    static bool ok = false;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        std::string path = env::TuningFile();
+        if (path.empty()) return;
+        std::string err;
+        ok = TuningTable::Load(path, &table, &err);
+        if (!ok && env::DebugLevel() > 0) std::fprintf(stderr, "[yali] %s\n", err.c_str());
+    });
+    return ok ? &table : nullptr;
+}
+
+// ------------------------------------------------------------------ the plan
+Result MakePlan(int world, uint64_t count, Dtype in, Dtype out, int epilogue, KernelMode forced, const PlanCaps& caps,
+                const TuningTable* table, Plan* plan, std::string* why) {
+    if (world < 1 || world > kMaxRanks) {
+        if (why) *why = "world size out of range";
+        return Result::InvalidArg;
+    }
+    const uint64_t in_b = DtypeSize(in), out_b = DtypeSize(out);
+    const uint64_t bytes = count * in_b;
+    const uint32_t max_ctas = std::max<uint32_t>(1, caps.max_ctas);
+    Plan p;
+    if (caps.vec_ok) p.flags |= kFlagVecOk;
+
+    // Which variants can run this call at all.
+    const bool rows = epilogue == kEpiResidualRmsNorm;
+    const bool flash_ok = bytes <= caps.flash_cap || world == 1;
+    const bool stream_ok = !rows && world > 1 && caps.ring_bytes > 0;
+    const bool nvls_ok = !rows && world > 1 && caps.has_multicast && in == out && caps.vec_ok &&
+                         (bytes % 16 == 0) && (caps.symmetric || bytes <= caps.nvls_cap);
+
+    Variant v;
+    const TuningRow* row = (table && forced == KernelMode::Auto) ? table->Find(world, static_cast<int>(in_b), bytes)
+                                                                 : nullptr;
+    if (forced == KernelMode::Flash) v = Variant::Flash;
+    else if (forced == KernelMode::Stream) v = Variant::Stream;
+    else if (forced == KernelMode::NVLS) v = bytes <= (128ull << 10) ? Variant::NvlsOneShot : Variant::NvlsTwoShot;
+    else if (row) v = row->variant;
+    else if (bytes <= FlashCrossoverBytes(in, world)) v = Variant::Flash;
+    else if (nvls_ok && world > 2) v = Variant::NvlsTwoShot;
+    else v = Variant::Stream;
+
+    // Fall back when the chosen variant cannot run; a forced mode that cannot run is an error.
+    auto runnable = [&](Variant x) {
+        switch (x) {
+            case Variant::Flash: return flash_ok;
+            case Variant::Stream: return stream_ok;
+            default: return nvls_ok;
+        }
+    };
+    if (!runnable(v)) {
+        if (forced != KernelMode::Auto) {
+            if (why)
+                *why = std::string("kernel mode '") + KernelModeName(forced) +
+                       "' cannot run this call (size, alignment, epilogue or missing multicast)";
+            return Result::Unsupported;
+        }
+        if (stream_ok) v = Variant::Stream;
+        else if (flash_ok) v = Variant::Flash;
+        else {
+            if (why) *why = "message exceeds the one-shot staging capacity and no two-shot path is available";
+            return Result::Unsupported;
+        }
+    }
+    p.variant = v;
+
+    const int dev_ctas = env::DevCtas(), dev_lanes = env::DevLanes();
+    const long long dev_slot = env::DevSlotBytes();
+    switch (v) {
+        case Variant::Flash: {
+            uint32_t c = row && row->ctas ? row->ctas : static_cast<uint32_t>(FlashLanePreset(bytes, in, world));
+            if (dev_ctas > 0) c = dev_ctas;
+            p.ctas = std::max<uint32_t>(1, std::min<uint32_t>(std::min<uint32_t>(c, max_ctas), kMaxFlashCtas));
+            break;
+        }
+        case Variant::Stream: {
+            const uint64_t elem = std::max(in_b, out_b);
+            p.shard_elems = ShardElems(count, world);
+            uint64_t slot = row && row->slot_bytes ? row->slot_bytes : AutoSlotBytes(count * elem, world);
+            if (dev_slot > 0) slot = static_cast<uint64_t>(dev_slot);
+            uint32_t lanes = row && row->ctas ? row->ctas : static_cast<uint32_t>(StreamLanePreset(bytes, in, world));
+            if (dev_lanes > 0) lanes = dev_lanes;
+            lanes = std::max<uint32_t>(1, std::min<uint32_t>(std::min<uint32_t>(lanes, max_ctas), kMaxLanes));
+            // The rings of all lanes must fit: lanes * (world-1) * kRingCap * 2 * slot <= ring_bytes.
+            const uint64_t per_lane_slots = static_cast<uint64_t>(world - 1) * kRingCap * 2;
+            slot = ClampSlotBytes(slot, std::max<uint64_t>(256, caps.ring_bytes / (per_lane_slots * lanes)));
+            if (slot * per_lane_slots * lanes > caps.ring_bytes) {
+                lanes = static_cast<uint32_t>(std::max<uint64_t>(1, caps.ring_bytes / (per_lane_slots * slot)));
+            }
+            const uint64_t piece = slot / elem;
+            const uint64_t n_pieces = CeilDiv(p.shard_elems, std::max<uint64_t>(piece, 1));
+            lanes = static_cast<uint32_t>(std::min<uint64_t>(lanes, std::max<uint64_t>(n_pieces, 1)));
+            p.ctas = lanes;
+            p.slot_bytes = static_cast<uint32_t>(slot);
+            p.max_iters = static_cast<uint32_t>(CeilDiv(n_pieces, lanes));
+            if (caps.peer_recv) p.flags |= kFlagDirectAg;
+            break;
+        }
+        case Variant::NvlsOneShot:
+        case Variant::NvlsTwoShot: {
+            p.shard_elems = ShardElems(count, world);
+            uint32_t c = row && row->ctas ? row->ctas
+                                          : static_cast<uint32_t>(std::min<uint64_t>(
+                                                std::max<uint64_t>(CeilDiv(bytes, 32ull << 10), 1), 148));
+            if (v == Variant::NvlsTwoShot)
+                c = static_cast<uint32_t>(std::min<uint64_t>(c, std::max<uint64_t>(CeilDiv(bytes / world, 8192), 1)));
+            if (dev_ctas > 0) c = dev_ctas;
+            p.ctas = std::max<uint32_t>(1, std::min<uint32_t>(std::min<uint32_t>(c, max_ctas), kBarSlots));
+            if (caps.symmetric) p.flags |= kFlagSymmetric;
+            break;
+        }
+    }
+    *plan = p;
+    return Result::Success;
+}
+
+}  // namespace yali

@@ -1,0 +1,332 @@
+// Host-thread model of the kernels' cross-rank protocols (see yali_c.h,
+// yali_c_simulate).  One host thread plays one CTA (a lane of the two-shot ring
+// kernel or a CTA of the one-shot kernel) of one rank; all "device memory" is host
+// memory and flags are std::atomic with release/acquire ordering, which is what
+// st.release.sys / ld.acquire.sys give the device code.  Calls follow one another
+// without any barrier between ranks; lanes of one rank meet between calls, as
+// kernels of one stream do.  Every slot and staging slice carries a FULL/FREE stamp
+// that is NOT part of the protocol: a producer that finds FULL, or a consumer that
+// finds a stamp of the wrong iteration, has caught the protocol reusing memory too
+// early, which the real kernels could only show as silent corruption.
+//
+// Parity: the reference has no such model; its protocol is described in comments
+// only (src/kernels/ring.cuh:18-34, src/kernels/stream.cuh:8-37,140-145).
+#include <algorithm>
+#include <atomic>
+#include <chrono>
+#include <cmath>
+#include <condition_variable>
+#include <cstring>
+#include <memory>
+#include <mutex>
+#include <thread>
+#include <vector>
+
+#include "../capi/yali_c.h"
+#include "../comm/layout.h"
+#include "../ops/buffer_ops.h"
+#include "../ops/host_oracle.h"
+#include "../ops/tuning.h"
+
+namespace {
+
+using Clock = std::chrono::steady_clock;
+
+struct Barrier {
+    std::mutex m;
+    std::condition_variable cv;
+    int count, waiting = 0, gen = 0;
+    explicit Barrier(int n) : count(n) {}
+    void wait() {
+        std::unique_lock<std::mutex> l(m);
+        int g = gen;
+        if (++waiting == count) {
+            waiting = 0;
+            ++gen;
+            cv.notify_all();
+        } else {
+            cv.wait(l, [&] { return g != gen; });
+        }
+    }
+};
+
+struct Shared {
+    YaliSimConfig cfg;
+    int W, L;
+    // flags[rank][kind][lane][src]
+    std::vector<std::unique_ptr<std::atomic<uint32_t>[]>> flags;
+    // slots[rank][lane][srcslot][cap][which] -> data + stamp
+    std::vector<std::vector<float>> ring;          // per rank
+    std::vector<std::unique_ptr<std::atomic<uint64_t>[]>> ring_stamp;  // per rank, one per slot; 0 = FREE
+    std::vector<std::vector<float>> stage;         // one-shot staging per rank: [2][W-1][count]
+    std::vector<std::unique_ptr<std::atomic<uint64_t>[]>> stage_stamp;  // [2][W-1][ctas]
+    std::vector<std::vector<float>> send, recv;
+    std::vector<std::unique_ptr<Barrier>> rank_barrier;
+    std::unique_ptr<std::atomic<int>[]> rank_abort;  // agreed between the lanes of a rank at the barrier
+    std::atomic<uint64_t> timeouts{0}, violations{0}, flag_writes{0}, max_outstanding{0};
+    std::atomic<int> t_rank{-1}, t_peer{-1}, t_site{0};
+    std::atomic<bool> abort{false};
+    int dropped = 0;
+    std::mutex drop_m;
+};
+
+enum Kind { kRs = 0, kAg = 1, kCr = 2, kFlash = 3, kKinds = 4 };
+
+std::atomic<uint32_t>& Flag(Shared& s, int on_rank, int kind, int lane, int src) {
+    return s.flags[on_rank][(static_cast<size_t>(kind) * s.L + lane) * yali::kMaxRanks + src];
+}
+
+bool SeqReached(uint32_t seen, uint32_t wanted) { return static_cast<int32_t>(seen - wanted) >= 0; }
+
+// Waits for the flags of all peers; false on timeout or global abort.
+bool WaitPeers(Shared& s, int rank, int kind, int lane, uint32_t wanted, int site) {
+    auto deadline = Clock::now() + std::chrono::milliseconds(s.cfg.timeout_ms);
+    for (int p = 0; p < s.W; ++p) {
+        if (p == rank) continue;
+        uint32_t spins = 0;
+        while (!SeqReached(Flag(s, rank, kind, lane, p).load(std::memory_order_acquire), wanted)) {
+            if ((++spins & 255u) == 0) {
+                if (s.abort.load() || Clock::now() > deadline) {
+                    if (s.timeouts.fetch_add(1) == 0) {
+                        s.t_rank = rank;
+                        s.t_peer = p;
+                        s.t_site = site;
+                    }
+                    s.abort = true;
+                    return false;
+                }
+                std::this_thread::yield();
+            }
+        }
+    }
+    return true;
+}
+
+void SignalPeers(Shared& s, int rank, int kind, int lane, uint32_t value, int call) {
+    for (int p = 0; p < s.W; ++p) {
+        if (p == rank) continue;
+        if (s.cfg.fault == 2 && rank == s.cfg.fault_rank && call == s.cfg.fault_call) {
+            std::lock_guard<std::mutex> l(s.drop_m);
+            if (s.dropped == 0) {
+                s.dropped = 1;
+                continue;  // this publication is lost
+            }
+        }
+        Flag(s, p, kind, lane, rank).store(value, std::memory_order_release);
+        s.flag_writes.fetch_add(1, std::memory_order_relaxed);
+    }
+}
+
+size_t SlotIndex(const Shared& s, int on_rank, int src, int lane, int slot, int which) {
+    return ((static_cast<size_t>(lane) * (s.W - 1) + yali::SrcSlot(src, on_rank)) * yali::kRingCap + slot) * 2 + which;
+}
+
+void ProducerStamp(Shared& s, int on_rank, size_t idx, uint64_t stamp) {
+    uint64_t expect = 0;
+    if (!s.ring_stamp[on_rank][idx].compare_exchange_strong(expect, stamp)) s.violations.fetch_add(1);
+}
+void ConsumerCheck(Shared& s, int on_rank, size_t idx, uint64_t stamp) {
+    uint64_t expect = stamp;
+    if (!s.ring_stamp[on_rank][idx].compare_exchange_strong(expect, 0)) s.violations.fetch_add(1);
+}
+
+void StreamLane(Shared& s, int r, int lane) {
+    const YaliSimConfig& c = s.cfg;
+    const int W = s.W;
+    const uint64_t shard = yali::ShardElems(c.count, W);
+    const uint64_t piece = c.slot_elems;
+    uint32_t seq_base = 0;
+    const uint64_t n_pieces = (shard + piece - 1) / piece;
+    const uint32_t max_iters = static_cast<uint32_t>((n_pieces + s.L - 1) / s.L);
+    for (int call = 0; call < c.calls; ++call) {
+        if (c.fault == 1 && r == c.fault_rank && call >= c.fault_call) return;  // this rank never launches
+        const uint32_t n_it = yali::oracle::StreamIters(shard, piece, s.L, lane);
+        const float* send = s.send[r].data();
+        float* recv = s.recv[r].data();
+        bool ok = true;
+        for (uint32_t step = 0; ok && step < n_it + 2; ++step) {
+            if (step < n_it) {  // stage A
+                const uint32_t i = step, slot = i % yali::kRingCap;
+                if (i >= yali::kRingCap) ok = WaitPeers(s, r, kCr, lane, seq_base + (i - yali::kRingCap) + 1, 2);
+                if (!ok) break;
+                for (int k = 1; k < W; ++k) {
+                    const int p = (r + k) % W;
+                    uint64_t eb, ee;
+                    yali::oracle::StreamPiece(c.count, shard, piece, s.L, lane, i, p, &eb, &ee);
+                    const size_t idx = SlotIndex(s, p, r, lane, slot, 0);
+                    ProducerStamp(s, p, idx, (static_cast<uint64_t>(call + 1) << 32) | (i + 1));
+                    std::memcpy(&s.ring[p][idx * piece], send + eb, (ee - eb) * sizeof(float));
+                }
+                SignalPeers(s, r, kRs, lane, seq_base + i + 1, call);
+            }
+            if (step >= 1 && step - 1 < n_it) {  // stage B
+                const uint32_t i = step - 1, slot = i % yali::kRingCap;
+                ok = WaitPeers(s, r, kRs, lane, seq_base + i + 1, 3);
+                if (!ok) break;
+                uint64_t eb, ee;
+                yali::oracle::StreamPiece(c.count, shard, piece, s.L, lane, i, r, &eb, &ee);
+                std::vector<float> red(ee - eb);
+                for (uint64_t e = 0; e < ee - eb; ++e) {
+                    float acc = 0.f;
+                    for (int q = 0; q < W; ++q)
+                        acc += (q == r) ? send[eb + e] : s.ring[r][SlotIndex(s, r, q, lane, slot, 0) * piece + e];
+                    red[e] = acc;
+                }
+                for (int q = 0; q < W; ++q)
+                    if (q != r)
+                        ConsumerCheck(s, r, SlotIndex(s, r, q, lane, slot, 0),
+                                      (static_cast<uint64_t>(call + 1) << 32) | (i + 1));
+                std::memcpy(recv + eb, red.data(), red.size() * sizeof(float));
+                for (int k = 1; k < W; ++k) {
+                    const int p = (r + k) % W;
+                    if (c.direct_ag) {
+                        std::memcpy(s.recv[p].data() + eb, red.data(), red.size() * sizeof(float));
+                    } else {
+                        const size_t idx = SlotIndex(s, p, r, lane, slot, 1);
+                        ProducerStamp(s, p, idx, (static_cast<uint64_t>(call + 1) << 32) | (i + 1));
+                        std::memcpy(&s.ring[p][idx * piece], red.data(), red.size() * sizeof(float));
+                    }
+                }
+                SignalPeers(s, r, kAg, lane, seq_base + i + 1, call);
+                if (c.direct_ag) SignalPeers(s, r, kCr, lane, seq_base + i + 1, call);
+            }
+            if (!c.direct_ag && step >= 2 && step - 2 < n_it) {  // stage C
+                const uint32_t i = step - 2, slot = i % yali::kRingCap;
+                ok = WaitPeers(s, r, kAg, lane, seq_base + i + 1, 4);
+                if (!ok) break;
+                for (int k = 1; k < W; ++k) {
+                    const int q = (r + k) % W;
+                    uint64_t eb, ee;
+                    yali::oracle::StreamPiece(c.count, shard, piece, s.L, lane, i, q, &eb, &ee);
+                    const size_t idx = SlotIndex(s, r, q, lane, slot, 1);
+                    std::memcpy(recv + eb, &s.ring[r][idx * piece], (ee - eb) * sizeof(float));
+                    ConsumerCheck(s, r, idx, (static_cast<uint64_t>(call + 1) << 32) | (i + 1));
+                }
+                SignalPeers(s, r, kCr, lane, seq_base + i + 1, call);
+            }
+        }
+        if (ok && c.direct_ag && n_it > 0) ok = WaitPeers(s, r, kAg, lane, seq_base + n_it, 5);
+        if (!ok) {
+            s.abort = true;
+        }
+        seq_base += max_iters;
+        // Stream order: the next kernel of this rank starts when all CTAs of this one are done.
+        if (s.abort.load()) s.rank_abort[r].store(1);
+        s.rank_barrier[r]->wait();
+        if (s.rank_abort[r].load()) return;
+    }
+}
+
+void FlashCta(Shared& s, int r, int cta) {
+    const YaliSimConfig& c = s.cfg;
+    const int W = s.W;
+    for (int call = 0; call < c.calls; ++call) {
+        if (c.fault == 1 && r == c.fault_rank && call >= c.fault_call) return;
+        const uint32_t epoch = call + 1, parity = epoch & 1u;
+        uint64_t vb, ve, tb, te;
+        yali::oracle::FlashSlice(c.count, 4, s.L, cta, true, &vb, &ve, &tb, &te);
+        const uint64_t eb = vb * 4, ee = (cta == s.L - 1) ? c.count : ve * 4;
+        const float* send = s.send[r].data();
+        for (int k = 1; k < W; ++k) {
+            const int p = (r + k) % W;
+            const size_t sidx = (static_cast<size_t>(parity) * (W - 1) + yali::SrcSlot(r, p));
+            uint64_t expect = 0;
+            if (!s.stage_stamp[p][sidx * s.L + cta].compare_exchange_strong(expect, epoch)) s.violations.fetch_add(1);
+            std::memcpy(&s.stage[p][sidx * c.count + eb], send + eb, (ee - eb) * sizeof(float));
+        }
+        SignalPeers(s, r, kFlash, cta, epoch, call);
+        bool ok = WaitPeers(s, r, kFlash, cta, epoch, 1);
+        if (ok) {
+            float* recv = s.recv[r].data();
+            for (uint64_t e = eb; e < ee; ++e) {
+                float acc = 0.f;
+                for (int q = 0; q < W; ++q) {
+                    if (q == r) acc += send[e];
+                    else acc += s.stage[r][(static_cast<size_t>(parity) * (W - 1) + yali::SrcSlot(q, r)) * c.count + e];
+                }
+                recv[e] = acc;
+            }
+            for (int q = 0; q < W; ++q) {
+                if (q == r) continue;
+                const size_t sidx = (static_cast<size_t>(parity) * (W - 1) + yali::SrcSlot(q, r));
+                uint64_t expect = epoch;
+                if (!s.stage_stamp[r][sidx * s.L + cta].compare_exchange_strong(expect, 0)) s.violations.fetch_add(1);
+            }
+        } else {
+            s.abort = true;
+        }
+        if (s.abort.load()) s.rank_abort[r].store(1);
+        s.rank_barrier[r]->wait();
+        if (s.rank_abort[r].load()) return;
+    }
+}
+
+}  // namespace
+
+extern "C" int yali_c_simulate(const YaliSimConfig* cfg, YaliSimReport* rep) {
+    std::memset(rep, 0, sizeof(*rep));
+    rep->timeout_rank = rep->timeout_peer = -1;
+    if (!cfg || cfg->world < 2 || cfg->world > yali::kMaxRanks || cfg->lanes < 1 || cfg->lanes > 64 ||
+        cfg->count == 0 || cfg->calls < 1 || (cfg->mode == 1 && (cfg->slot_elems == 0 || cfg->slot_elems % 4)))
+        return -1;
+    Shared s;
+    s.cfg = *cfg;
+    s.W = cfg->world;
+    s.L = cfg->lanes;
+    const int W = s.W;
+    const size_t nflags = static_cast<size_t>(kKinds) * s.L * yali::kMaxRanks;
+    const size_t nslots = static_cast<size_t>(s.L) * (W - 1) * yali::kRingCap * 2;
+    for (int r = 0; r < W; ++r) {
+        s.flags.emplace_back(new std::atomic<uint32_t>[nflags]);
+        for (size_t i = 0; i < nflags; ++i) s.flags[r][i].store(0);
+        s.send.emplace_back(cfg->count);
+        s.recv.emplace_back(cfg->count, -12345.f);
+        for (uint64_t i = 0; i < cfg->count; ++i)
+            s.send[r][i] = yali::RandomValue(yali::kDistNormal, cfg->seed + r, i);
+        if (cfg->mode == 1) {
+            s.ring.emplace_back(nslots * cfg->slot_elems);
+            s.ring_stamp.emplace_back(new std::atomic<uint64_t>[nslots]);
+            for (size_t i = 0; i < nslots; ++i) s.ring_stamp[r][i].store(0);
+        } else {
+            s.stage.emplace_back(2ull * (W - 1) * cfg->count);
+            s.stage_stamp.emplace_back(new std::atomic<uint64_t>[2ull * (W - 1) * s.L]);
+            for (size_t i = 0; i < 2ull * (W - 1) * s.L; ++i) s.stage_stamp[r][i].store(0);
+        }
+        s.rank_barrier.emplace_back(new Barrier(s.L));
+    }
+    s.rank_abort.reset(new std::atomic<int>[W]);
+    for (int r = 0; r < W; ++r) s.rank_abort[r].store(0);
+    std::vector<std::thread> threads;
+    for (int r = 0; r < W; ++r)
+        for (int l = 0; l < s.L; ++l)
+            threads.emplace_back(cfg->mode == 1 ? StreamLane : FlashCta, std::ref(s), r, l);
+    // A rank that stops launching leaves its lanes' barrier short-handed only for itself.
+    for (auto& t : threads) t.join();
+
+    rep->timeouts = s.timeouts.load();
+    rep->flag_writes = s.flag_writes.load();
+    rep->timeout_rank = s.t_rank.load();
+    rep->timeout_peer = s.t_peer.load();
+    rep->timeout_site = s.t_site.load();
+    if (s.violations.load()) {
+        rep->mismatches = s.violations.load();
+        rep->status = 3;
+        return 3;
+    }
+    if (rep->timeouts) {
+        rep->status = 2;
+        return 2;
+    }
+    // Oracle: fp64 sum; fp32 rank-order accumulation differs from it by rounding only.
+    uint64_t bad = 0;
+    for (int r = 0; r < W; ++r) {
+        for (uint64_t i = 0; i < cfg->count; ++i) {
+            double e = 0.0;
+            for (int q = 0; q < W; ++q) e += s.send[q][i];
+            if (!(std::fabs(s.recv[r][i] - e) <= 1e-5 * W + 1e-5 * std::fabs(e))) ++bad;
+        }
+    }
+    rep->mismatches = bad;
+    rep->status = bad ? 1 : 0;
+    return rep->status;
+}

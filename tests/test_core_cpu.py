@@ -1,0 +1,245 @@
+"""Host-only logic: enums and names, tuning functions, the planner, the heap layout,
+partition arithmetic (property tests), the generator and the CPU oracles.
+
+Reference counterparts: tests/unit/test_all_reduce_interface.cu (enum names, config
+defaults), tests/unit/test_all_reduce_correctness.cu:165-208 (tuning ranges),
+tests/unit/test_validation.cu:13-59 (VerifyAllReduceSum)."""
+import ctypes
+import json
+
+import numpy as np
+import pytest
+
+from yali_b200 import _native
+from yali_b200._native import Plan, PlanCaps
+
+FP32, FP16, BF16 = 0, 1, 2
+MiB = 1 << 20
+
+
+def caps(world, **kw):
+    c = PlanCaps(flash_cap=(64 if world == 2 else 16 if world <= 4 else 8) * MiB, ring_bytes=256 * MiB,
+                 nvls_cap=64 * MiB, has_multicast=0, symmetric=0, peer_recv=0, vec_ok=1, max_ctas=1184)
+    for k, v in kw.items():
+        setattr(c, k, v)
+    return c
+
+
+def make_plan(lib, world, count, in_dt=FP32, out_dt=None, epi=0, mode=0, cp=None, table=None):
+    plan = Plan()
+    err = ctypes.create_string_buffer(256)
+    c = cp or caps(world)
+    rc = lib.yali_c_make_plan(world, count, in_dt, in_dt if out_dt is None else out_dt, epi, mode, ctypes.byref(c),
+                              table.encode() if table else None, ctypes.byref(plan), err, 256)
+    return rc, plan, err.value.decode()
+
+
+def test_version_and_errors(native_lib):
+    assert b"yali" in native_lib.yali_c_version()
+    names = [native_lib.yali_c_error_string(i).decode() for i in range(8)]
+    assert names[0] == "Success" and "timed out" in names[5] and len(set(names)) == 8
+
+
+def test_tuning_functions_sane(native_lib):
+    lib = native_lib
+    for world in (2, 4, 8):
+        cross = lib.yali_c_flash_crossover_bytes(FP32, world)
+        assert 64 * 1024 <= cross <= 64 * MiB
+        prev = 0
+        for shift in range(10, 32):
+            b = 1 << shift
+            lanes = lib.yali_c_flash_lane_preset(b, FP32, world)
+            assert 1 <= lanes <= 2048
+            assert lanes >= prev  # more data never means fewer CTAs
+            prev = lanes
+            s_lanes = lib.yali_c_stream_lane_preset(b, BF16, world)
+            assert 1 <= s_lanes <= 256
+            slot = lib.yali_c_auto_slot_bytes(b, world)
+            assert 8 * 1024 <= slot <= 256 * 1024 and slot % 256 == 0
+    assert lib.yali_c_flash_crossover_bytes(FP32, 2) == 64 * MiB  # same crossover as the reference at two ranks
+    assert lib.yali_c_clamp_slot_bytes(100, 1 << 20) == 256
+    assert lib.yali_c_clamp_slot_bytes(1 << 30, 1 << 16) == 1 << 16
+    assert lib.yali_c_auto_ctas_per_lane(0, 16, 1 << 20, 2048) == 1
+    assert 1 <= lib.yali_c_auto_ctas_per_lane(1, 16, 1 << 20, 2048) <= 32
+    assert lib.yali_c_auto_ctas_per_lane(1, 16, 0, 2048) == 1
+
+
+def test_shard_elems(native_lib):
+    for world in range(1, 9):
+        for count in (1, 7, 31, 32, 33, 1000, 262144, (1 << 29) + 3):
+            s = native_lib.yali_c_shard_elems(count, world)
+            assert s % 16 == 0 and s * world >= count and (s - 16) * world < count
+
+
+def test_heap_layout(native_lib):
+    f = (ctypes.c_uint64 * 12)()
+    for world in (1, 2, 4, 8):
+        assert native_lib.yali_c_heap_layout(world, 0, f) == 0
+        total, flags_off, flash_off, flash_cap, ring_off, ring_bytes, nvls_off, nvls_cap, gemm_off, gemm_cap, \
+            user_off, user_bytes = list(f)
+        assert flags_off == 0 and user_off + user_bytes == total and user_bytes >= 256 * MiB
+        if world > 1:
+            assert flash_off >= 1 * MiB
+            assert ring_off == flash_off + 2 * (world - 1) * flash_cap
+            assert nvls_off == ring_off + ring_bytes
+            assert gemm_off == nvls_off + 2 * nvls_cap
+            assert user_off == gemm_off + 2 * world * gemm_cap
+    assert native_lib.yali_c_heap_layout(8, 1 * MiB, f) != 0  # too small for the fixed regions
+
+
+def test_plan_auto_selection(native_lib):
+    lib = native_lib
+    rc, p, _ = make_plan(lib, 2, 262144)  # 1 MiB fp32 at two ranks: one-shot
+    assert rc == 0 and p.variant == 0 and p.ctas >= 32
+    rc, p, _ = make_plan(lib, 2, 64 * MiB)  # 256 MiB: two-shot
+    assert rc == 0 and p.variant == 1 and p.slot_bytes % 256 == 0 and p.max_iters >= 1
+    assert p.ctas * (2 - 1) * 4 * 2 * p.slot_bytes <= 256 * MiB
+    rc, p, _ = make_plan(lib, 8, 64 * MiB, cp=caps(8, has_multicast=1, symmetric=1))
+    assert rc == 0 and p.variant == 3  # NVLS two-shot when multicast is there
+    rc, p, _ = make_plan(lib, 8, 64 * MiB, cp=caps(8, has_multicast=1, symmetric=0))
+    assert rc == 0 and p.variant == 1  # 256 MiB does not fit the NVLS staging: ring kernel
+    rc, p, _ = make_plan(lib, 8, 1024)
+    assert rc == 0 and p.variant == 0 and p.ctas == 1
+
+
+def test_plan_forced_modes_and_errors(native_lib):
+    lib = native_lib
+    rc, p, _ = make_plan(lib, 4, 1 << 20, mode=2)
+    assert rc == 0 and p.variant == 1
+    rc, p, msg = make_plan(lib, 4, 1 << 20, mode=3)  # NVLS forced without multicast
+    assert rc == 6 and "cannot run" in msg
+    rc, p, msg = make_plan(lib, 2, 128 * MiB, mode=1)  # one-shot forced beyond its staging
+    assert rc == 6
+    rc, p, _ = make_plan(lib, 2, 4096 * 64, in_dt=BF16, epi=2)  # row-wise epilogue: one-shot only
+    assert rc == 0 and p.variant == 0
+    rc, p, _ = make_plan(lib, 9, 10)
+    assert rc == 1
+
+
+def test_plan_respects_max_ctas(native_lib):
+    rc, p, _ = make_plan(native_lib, 8, 1 << 22, cp=caps(8, max_ctas=37))
+    assert rc == 0 and p.ctas <= 37
+    rc, p, _ = make_plan(native_lib, 8, 1 << 16, cp=caps(8, max_ctas=37))
+    assert rc == 0 and p.ctas <= 37
+
+
+def test_tuning_table_override(native_lib):
+    table = json.dumps({"rows": [
+        {"world": 2, "elem_bytes": 4, "max_bytes": 65536, "variant": "stream", "ctas": 8, "slot_bytes": 4096},
+        {"world": 2, "elem_bytes": 0, "max_bytes": 1 << 40, "variant": "flash", "ctas": 77, "busbw": 123.4},
+    ]})
+    rc, p, _ = make_plan(native_lib, 2, 4096, table=table)  # 16 KiB fp32 -> first row
+    assert rc == 0 and p.variant == 1 and p.slot_bytes == 4096 and p.ctas <= 8
+    rc, p, _ = make_plan(native_lib, 2, 1 << 20, table=table)  # 4 MiB -> wildcard row
+    assert rc == 0 and p.variant == 0 and p.ctas == 77
+    rc, p, msg = make_plan(native_lib, 2, 4096, table='{"rows": [{"world": 2}]}')
+    assert rc == 1 and "tuning table" in msg
+
+
+@pytest.mark.parametrize("count", [0, 1, 7, 31, 32, 33, 4099, 262144, 1000003])
+@pytest.mark.parametrize("ctas", [1, 3, 8, 37, 256])
+@pytest.mark.parametrize("vec", [4, 8])
+def test_flash_slices_partition_the_message(native_lib, count, ctas, vec):
+    for vec_ok in (1, 0):
+        covered = np.zeros(count, dtype=np.int32)
+        o = (ctypes.c_uint64 * 4)()
+        for cta in range(ctas):
+            native_lib.yali_c_flash_slice(count, vec, ctas, cta, vec_ok, o)
+            vb, ve, tb, te = list(o)
+            assert vb <= ve and tb <= te
+            covered[vb * vec:ve * vec] += 1
+            covered[tb:te] += 1
+        assert (covered == 1).all()
+
+
+@pytest.mark.parametrize("world", [2, 3, 4, 8])
+@pytest.mark.parametrize("count", [1, 17, 4099, 100000])
+@pytest.mark.parametrize("lanes,piece", [(1, 16), (3, 64), (7, 1024)])
+def test_stream_pieces_partition_the_message(native_lib, world, count, lanes, piece):
+    shard = native_lib.yali_c_shard_elems(count, world)
+    covered = np.zeros(count, dtype=np.int32)
+    o = (ctypes.c_uint64 * 2)()
+    for q in range(world):
+        for lane in range(lanes):
+            iters = native_lib.yali_c_stream_iters(shard, piece, lanes, lane)
+            for it in range(iters):
+                native_lib.yali_c_stream_piece(count, shard, piece, lanes, lane, it, q, o)
+                eb, ee = list(o)
+                assert eb <= ee <= count and ee - eb <= piece
+                assert eb % 16 == 0 or eb == count  # vector paths start on 16-element boundaries
+                covered[eb:ee] += 1
+    assert (covered == 1).all()
+    # every rank runs the same number of iterations per lane (the sequence numbers rely on it)
+    total = sum(native_lib.yali_c_stream_iters(shard, piece, lanes, lane) for lane in range(lanes))
+    assert total == -(-shard // piece)
+
+
+def test_philox_reference_vector_and_determinism(native_lib):
+    o = (ctypes.c_uint32 * 4)()
+    # Known-answer test of Philox4x32-10 (counter 0, key 0) from the Random123 distribution.
+    native_lib.yali_c_philox(0, 0, o)
+    assert [hex(x) for x in o] == ["0x6627e8d5", "0xe169c58d", "0xbc57ac4c", "0x9b00dbd8"]
+    a = [native_lib.yali_c_random_value(0, 1234, i) for i in range(1000)]
+    b = [native_lib.yali_c_random_value(0, 1234, i) for i in range(1000)]
+    c = [native_lib.yali_c_random_value(0, 1235, i) for i in range(1000)]
+    assert a == b and a != c and all(-1.0 < x < 1.0 for x in a)
+    n = np.array([native_lib.yali_c_random_value(1, 99, i) for i in range(20000)])
+    assert abs(n.mean()) < 0.03 and abs(n.std() - 1.0) < 0.03
+
+
+def test_rounding_helpers_match_torch(native_lib):
+    import torch
+    xs = np.concatenate([np.random.default_rng(0).normal(size=2000).astype(np.float32) * 10,
+                         np.array([0.0, 1.0, -1.0, 65504.0, 1e-7, 3.1415927], dtype=np.float32)])
+    t = torch.from_numpy(xs)
+    bf = t.to(torch.bfloat16).to(torch.float32).numpy()
+    hf = t.to(torch.float16).to(torch.float32).numpy()
+    for x, eb, eh in zip(xs, bf, hf):
+        assert native_lib.yali_c_round_bf16(float(x)) == eb
+        assert native_lib.yali_c_round_fp16(float(x)) == eh
+
+
+def test_oracles(native_lib):
+    rng = np.random.default_rng(1)
+    world, n = 4, 1000
+    ins = [rng.normal(size=n).astype(np.float32) for _ in range(world)]
+    ptrs = (ctypes.c_void_p * world)(*[x.ctypes.data for x in ins])
+    out = np.zeros(n, dtype=np.float64)
+    native_lib.yali_c_oracle_allreduce(ptrs, world, n, 0.25, out.ctypes.data)
+    np.testing.assert_allclose(out, 0.25 * np.sum(np.stack(ins).astype(np.float64), axis=0), rtol=1e-12)
+
+    rows, hidden = 5, 64
+    s = rng.normal(size=(rows, hidden))
+    res = rng.normal(size=(rows, hidden)).astype(np.float32)
+    w = rng.normal(size=hidden).astype(np.float32)
+    y = np.zeros((rows, hidden))
+    pre = np.zeros((rows, hidden))
+    native_lib.yali_c_oracle_residual_rmsnorm(s.ctypes.data, res.ctypes.data, w.ctypes.data, rows, hidden, 1e-5,
+                                              y.ctypes.data, pre.ctypes.data)
+    exp_pre = s + res
+    exp = exp_pre / np.sqrt((exp_pre ** 2).mean(axis=1, keepdims=True) + 1e-5) * w
+    np.testing.assert_allclose(pre, exp_pre, rtol=1e-12)
+    np.testing.assert_allclose(y, exp, rtol=1e-10)
+
+    a = rng.normal(size=(3, 8)).astype(np.float32)
+    b = rng.normal(size=(8, 5)).astype(np.float32)
+    c = np.zeros((3, 5))
+    native_lib.yali_c_oracle_gemm(a.ctypes.data, b.ctypes.data, 3, 5, 8, c.ctypes.data)
+    np.testing.assert_allclose(c, a.astype(np.float64) @ b.astype(np.float64), rtol=1e-12)
+
+
+def test_verify_allreduce_sum(native_lib):
+    first, count = ctypes.c_size_t(), ctypes.c_size_t()
+    good = np.full(100, 3.0, dtype=np.float32)
+    assert native_lib.yali_c_verify_allreduce_sum(good.ctypes.data, 100, 3.0, 1e-3, ctypes.byref(first),
+                                                  ctypes.byref(count)) == 1 and count.value == 0
+    bad = good.copy()
+    bad[17] = 2.0
+    bad[50] = float("nan")
+    assert native_lib.yali_c_verify_allreduce_sum(bad.ctypes.data, 100, 3.0, 1e-3, ctypes.byref(first),
+                                                  ctypes.byref(count)) == 0
+    assert first.value == 17 and count.value == 2
+    near = np.full(10, 3.0005, dtype=np.float32)
+    assert native_lib.yali_c_verify_allreduce_sum(near.ctypes.data, 10, 3.0, 1e-3, None, None) == 1
+    assert native_lib.yali_c_verify_allreduce_sum(near.ctypes.data, 10, 3.0, 1e-4, None, None) == 0
+    assert native_lib.yali_c_verify_allreduce_sum(None, 0, 3.0, 1e-4, None, None) == 1

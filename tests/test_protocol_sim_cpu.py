@@ -1,0 +1,71 @@
+"""The cross-rank flag protocols of the one-shot and the two-shot ring kernel, run
+by host threads on host memory (one thread per CTA): correctness of back-to-back
+calls without any barrier, slot reuse (a producer that overwrites a slot before its
+consumer is done is reported as an invariant violation), and fault injection on the
+host: a rank that never launches must make its peers time out, not hang."""
+import ctypes
+
+import pytest
+
+from yali_b200 import _native
+from yali_b200._native import SimConfig, SimReport
+
+
+def simulate(**kw):
+    cfg = SimConfig(mode=1, world=2, lanes=2, calls=2, count=10000, slot_elems=64, direct_ag=0, fault=0, fault_rank=0,
+                    fault_call=0, timeout_ms=5000, seed=1234)
+    for k, v in kw.items():
+        setattr(cfg, k, v)
+    rep = SimReport()
+    rc = _native.lib().yali_c_simulate(ctypes.byref(cfg), ctypes.byref(rep))
+    return rc, rep
+
+
+@pytest.mark.parametrize("world", [2, 3, 4, 8])
+@pytest.mark.parametrize("direct_ag", [0, 1])
+def test_ring_protocol_many_iterations(world, direct_ag):
+    # 50001 elements, 128-element slots, 3 lanes: dozens of iterations per lane, so every
+    # slot of the 4-deep rings is reused many times and the credits matter.
+    rc, rep = simulate(world=world, lanes=3, calls=3, count=50001, slot_elems=128, direct_ag=direct_ag)
+    assert rc == 0 and rep.mismatches == 0 and rep.timeouts == 0
+    assert rep.flag_writes > 0
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_ring_protocol_tiny_and_ragged(world):
+    for count, slot, lanes in [(1, 4, 1), (17, 4, 2), (4099, 16, 5), (1000, 1024, 4)]:
+        rc, rep = simulate(world=world, lanes=lanes, calls=2, count=count, slot_elems=slot)
+        assert rc == 0, (count, slot, lanes, rep.status, rep.mismatches)
+
+
+@pytest.mark.parametrize("world", [2, 3, 4, 8])
+def test_one_shot_protocol_back_to_back(world):
+    rc, rep = simulate(mode=0, world=world, lanes=4, calls=6, count=4099)
+    assert rc == 0 and rep.mismatches == 0
+
+
+def test_rank_that_never_launches_times_out_ring():
+    rc, rep = simulate(world=4, fault=1, fault_rank=2, fault_call=1, calls=3, timeout_ms=300)
+    assert rc == 2 and rep.timeouts >= 1 and rep.timeout_peer == 2 and rep.timeout_rank != 2
+    assert rep.timeout_site in (2, 3, 4, 5)
+
+
+def test_rank_that_never_launches_times_out_one_shot():
+    rc, rep = simulate(mode=0, world=2, fault=1, fault_rank=0, fault_call=0, calls=1, timeout_ms=300)
+    assert rc == 2 and rep.timeout_peer == 0 and rep.timeout_site == 1
+
+
+def test_dropped_flag_write_is_survived_or_times_out():
+    # Counters are monotone: a lost publication is healed by the next one of the same lane;
+    # when it was the last one the waiter times out.  Never a wrong result.
+    for world in (2, 4):
+        rc, rep = simulate(world=world, lanes=2, calls=2, count=20000, slot_elems=64, fault=2, fault_rank=1,
+                           fault_call=0, timeout_ms=300)
+        assert rc in (0, 2) and (rc != 0 or rep.mismatches == 0)
+
+
+def test_bad_configs_are_rejected():
+    assert simulate(world=1)[0] == -1
+    assert simulate(world=9)[0] == -1
+    assert simulate(slot_elems=6)[0] == -1
+    assert simulate(count=0)[0] == -1

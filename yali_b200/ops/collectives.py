@@ -1,0 +1,36 @@
+"""Functional collectives on the default communicator (or an explicit one).
+
+CUDA tensors run the native kernels; CPU tensors go through `GlooComm`.  The same
+functions back the `torch.ops.yali.*` operators (see `registry.py`)."""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from ..parallel import comm as _comm
+
+
+def _pick(comm):
+    return comm if comm is not None else _comm.get_default_comm()
+
+
+def all_reduce(x: torch.Tensor, *, comm=None, out: Optional[torch.Tensor] = None, scale: Optional[float] = None,
+               out_dtype: Optional[torch.dtype] = None, mode: str = "auto") -> torch.Tensor:
+    """Sum over all ranks (optionally scaled and cast)."""
+    return _pick(comm).all_reduce(x, out, mode=mode, scale=scale, out_dtype=out_dtype)
+
+
+def all_reduce_rmsnorm(x: torch.Tensor, weight: torch.Tensor, residual: Optional[torch.Tensor] = None, *,
+                       eps: float = 1e-5, comm=None, out: Optional[torch.Tensor] = None,
+                       residual_out: Optional[torch.Tensor] = None, mode: str = "auto") -> torch.Tensor:
+    """RMSNorm(sum over ranks of x + residual) * weight in one kernel."""
+    return _pick(comm).all_reduce_rmsnorm(x, weight, residual, eps=eps, out=out, residual_out=residual_out, mode=mode)
+
+
+def reduce_scatter(x: torch.Tensor, *, comm=None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    return _pick(comm).reduce_scatter(x, out)
+
+
+def all_gather(shard: torch.Tensor, count: int, *, comm=None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    return _pick(comm).all_gather(shard, count, out)
