@@ -1,0 +1,325 @@
+#!/usr/bin/env python
+"""Headline benchmark: all-reduce bus bandwidth (NCCL convention, bytes*2(n-1)/n/t).
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference]
+
+One step = one sum all-reduce of a 128 MiB fp32 message per rank (inputs larger
+than the 126 MB L2) between pre-allocated symmetric buffers.  N > 1 runs one rank
+per GPU (torchrun exports RANK / LOCAL_RANK / WORLD_SIZE / MASTER_*); N = 1 has no
+peer, so two ranks are emulated on the one GPU by a single cooperative launch of
+the same kernels (HBM-bound, no NVLink) and the line says so.  Timing: CUDA events
+per step on the launching stream after W warm-up steps, barrier + synchronize on
+both sides, max over ranks.  The line also carries p50/p99 latency of a 1 MiB
+all-reduce (rotating over buffers that together exceed L2), the end-to-end number
+(pinned host -> device copy of the step's input, all-reduce through the public
+API, device -> host copy of the result) and the clocks sampled during the timed
+region.
+
+`--impl reference` runs the unmodified reference (its own benchmark_yali binary and
+an end-to-end harness around its yali::allreduce, built by
+baseline/build_reference.sh into baseline/_ref/) for the same message.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+# 2x A100 NV4, 128 MB fp32, the reference's published bus bandwidth (its README.md:124,273).
+BASELINE_GBPS_128MB = 79.2
+MESSAGE_BYTES = 128 << 20
+
+
+def bus_factor(n: int) -> float:
+    return 2.0 * (n - 1) / n if n > 1 else 1.0
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int = 0) -> None:
+        self.gpu = gpu_index
+        self.proc = None
+        self.lines = []
+        self.thread = None
+
+    def start(self) -> None:
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-i", str(self.gpu), "-lms", "100"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self) -> None:
+        for ln in self.proc.stdout:
+            self.lines.append(ln.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def gather_max(comm, value: float) -> float:
+    """Max over ranks of a host float (control plane, outside any timed region)."""
+    import struct
+    if comm.nlocal != 1 or comm.world == 1:
+        return value
+    parts = comm.allgather_object_bytes(struct.pack("d", value))
+    return max(struct.unpack("d", p)[0] for p in parts)
+
+
+def time_steps(comm, torch, fn, steps: int, warmup: int):
+    """Runs fn(i) warmup+steps times; returns (total_ms max over ranks, per-step ms list of this rank)."""
+    for i in range(warmup):
+        fn(i)
+    comm.barrier()
+    torch.cuda.synchronize()
+    evs = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+    launches0 = comm.launches
+    evs[0].record()
+    for i in range(steps):
+        fn(warmup + i)
+        evs[i + 1].record()
+    torch.cuda.synchronize()
+    comm.barrier()
+    comm.check()
+    per = [evs[i].elapsed_time(evs[i + 1]) for i in range(steps)]
+    total = evs[0].elapsed_time(evs[steps])
+    time_steps.launches = comm.launches - launches0  # kernels this process launched inside the timed region
+    return gather_max(comm, total), per
+
+
+def percentile(xs, q):
+    s = sorted(xs)
+    if not s:
+        return None
+    k = min(len(s) - 1, max(0, int(round(q / 100.0 * (len(s) - 1)))))
+    return s[k]
+
+
+def run_own(args) -> dict:
+    import torch
+
+    import yali_b200 as yali
+    from yali_b200 import _native
+
+    n_gpus = args.gpus
+    world_env = int(os.environ.get("WORLD_SIZE", "1"))
+    elems = MESSAGE_BYTES // 4
+    heap = 3 << 30
+    emulated = n_gpus == 1
+    if emulated:
+        comm = yali.Comm.emulated(2, device=0, heap_bytes=heap)
+        ranks = 2
+    else:
+        if world_env != n_gpus:
+            raise SystemExit(f"--gpus {n_gpus} needs a launcher that starts {n_gpus} ranks (WORLD_SIZE={world_env})")
+        comm = yali.Comm.from_env(heap_bytes=heap)
+        ranks = n_gpus
+    rank = comm.rank
+    ext = _native.ext()
+    aslist = (lambda t: t if isinstance(t, list) else [t])
+
+    send = comm.symm_empty(elems, torch.float32)
+    recv = comm.symm_empty(elems, torch.float32)
+    for i, t in enumerate(aslist(send)):
+        ext.fill_random(t, 0, 1234 + (i if emulated else rank))
+
+    # ---- headline: 128 MiB fp32, device-timed ----
+    sampler = ClockSampler(comm.device)
+
+    def step(_i):
+        comm.all_reduce(send, recv)
+
+    if rank == 0:
+        sampler.start()
+    total_ms, per = time_steps(comm, torch, step, args.steps, args.warmup)
+    launches = time_steps.launches * (1 if emulated else ranks)  # every rank launches the same count
+    clocks = sampler.stop() if rank == 0 else {}
+    variant = comm.last_call()
+    ok = all(ext.validate_sum(t, torch.float32, 0, 1234, ranks)["mismatches"] == 0 for t in aslist(recv))
+    ms_per_step = total_ms / args.steps
+    busbw = MESSAGE_BYTES * bus_factor(ranks) / (ms_per_step * 1e-3) / 1e9
+
+    # ---- latency at 1 MiB: rotate over 160 buffer pairs (320 MiB touched > L2) ----
+    small = (1 << 20) // 4
+    nbuf = 160
+    pool_s = comm.symm_empty(small * nbuf, torch.float32)
+    pool_r = comm.symm_empty(small * nbuf, torch.float32)
+    views_s = [[t[k * small:(k + 1) * small] for t in aslist(pool_s)] for k in range(nbuf)]
+    views_r = [[t[k * small:(k + 1) * small] for t in aslist(pool_r)] for k in range(nbuf)]
+    unwrap = (lambda v: v if emulated else v[0])
+
+    def small_step(i):
+        comm.all_reduce(unwrap(views_s[i % nbuf]), unwrap(views_r[i % nbuf]))
+
+    lat_steps = max(args.steps, 200)
+    _, lat = time_steps(comm, torch, small_step, lat_steps, max(args.warmup, 20))
+    p50, p99 = percentile(lat, 50), percentile(lat, 99)
+    p50 = gather_max(comm, p50)
+    p99 = gather_max(comm, p99)
+
+    # ---- end to end through the public API: pinned H2D, all-reduce, D2H of the result ----
+    n_local = len(aslist(send))
+    h_in = [torch.empty(elems, dtype=torch.float32).pin_memory() for _ in range(n_local)]
+    h_out = [torch.empty(elems, dtype=torch.float32).pin_memory() for _ in range(n_local)]
+    for h, t in zip(h_in, aslist(send)):
+        h.copy_(t)
+
+    def e2e_step(_i):
+        for h, t in zip(h_in, aslist(send)):
+            t.copy_(h, non_blocking=True)
+        comm.all_reduce(send, recv)
+        for h, t in zip(h_out, aslist(recv)):
+            h.copy_(t, non_blocking=True)
+
+    e2e_steps = max(3, min(args.steps, 20))
+    e2e_ms, _ = time_steps(comm, torch, e2e_step, e2e_steps, 3)
+    e2e_busbw = MESSAGE_BYTES * bus_factor(ranks) / (e2e_ms / e2e_steps * 1e-3) / 1e9
+    ok = ok and bool(torch.equal(h_out[0], aslist(recv)[0].cpu()))
+    comm.close()
+
+    return {
+        "metric": "allreduce_busbw_GBps_128MiB_fp32",
+        "value": round(busbw, 2),
+        "unit": "GB/s",
+        "n_gpus": n_gpus,
+        "steps": args.steps,
+        "warmup": args.warmup,
+        "ms_per_step": round(ms_per_step, 5),
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": round(busbw / BASELINE_GBPS_128MB, 3),
+        "dtype": "fp32",
+        "data": "synthetic U(-1,1), seed 1234+rank; result verified on device: " + ("ok" if ok else "MISMATCH"),
+        "impl": "yali_b200",
+        "config": {
+            "model": "sum all-reduce, 128 MiB fp32 per rank, pre-allocated symmetric buffers",
+            "global_batch": MESSAGE_BYTES * ranks,
+            "seq_len": elems,
+            "parallelism": ("1 GPU: 2 ranks emulated in one cooperative launch (HBM-bound, no NVLink)" if emulated
+                            else f"{ranks} ranks, one GPU per process"),
+            "l2": "inputs (128 MiB per rank) larger than L2; 1 MiB latency rotates over 320 MiB of buffers",
+            "kernel": variant,
+            "baseline": "reference README: 79.2 GB/s at 128 MB fp32 on 2x A100 NV4",
+        },
+        "latency_1MiB_us": {"p50": round(p50 * 1e3, 2), "p99": round(p99 * 1e3, 2),
+                            "p99_over_p50": round(p99 / p50, 3) if p50 else None, "samples": lat_steps},
+        "e2e": {"value": round(e2e_busbw, 2), "unit": "GB/s", "h2d_bytes_per_step": MESSAGE_BYTES * n_local,
+                "d2h_bytes_per_step": MESSAGE_BYTES * n_local, "steps": e2e_steps},
+        "gpu_launches": int(launches),
+        "clocks": clocks,
+    }
+
+
+def run_reference(args) -> dict:
+    """The unmodified reference, through its own benchmark binary (device-timed number) and its
+    own ops API inside a small timing harness (end-to-end number).  It supports exactly two
+    GPUs driven by one process, so only rank 0 of a 2-rank launch runs it."""
+    ref_dir = ROOT / "baseline" / "_ref"
+    rank = int(os.environ.get("RANK", "0"))
+    if args.gpus != 2:
+        return {"impl": "reference",
+                "unavailable": f"the reference runs on exactly 2 GPUs (asked for {args.gpus}): "
+                               "src/ops/allreduce_mpi.cuh:113-118, README.md:199-203"}
+    binary, harness = ref_dir / "benchmark_yali", ref_dir / "ref_e2e"
+    if not binary.exists() or not harness.exists():
+        return {"impl": "reference", "unavailable": "baseline/_ref is not built (run baseline/build_reference.sh)"}
+    if rank != 0:
+        return {}
+    elems = MESSAGE_BYTES // 4
+    sampler = ClockSampler(0)
+    sampler.start()
+    # argv: elements calls verify mode lanes timing dtype (bench/benchmark_yali.cu:764-789); its
+    # warm-up count is fixed at 100 calls in the source.
+    try:
+        out = subprocess.run([str(binary), str(elems), str(args.steps), "0", "auto", "0", "cuda-events", "fp32"],
+                             capture_output=True, text=True, timeout=600)
+    except subprocess.TimeoutExpired:
+        sampler.stop()
+        return {"impl": "reference", "unavailable": "reference benchmark_yali did not finish within 600 s"}
+    clocks = sampler.stop()
+    import re
+    m = re.search(r"YALI \(([^)]*)\): (\d+) calls, ([\d.]+) us/call avg, ([\d.]+) GB/s", out.stdout)
+    if out.returncode != 0 or not m:
+        return {"impl": "reference", "unavailable": "reference benchmark_yali failed: " +
+                (out.stderr.strip() or out.stdout.strip())[-200:].replace("\n", " ")}
+    us, gbps = float(m.group(3)), float(m.group(4))
+    small = subprocess.run([str(binary), str((1 << 20) // 4), "1000", "0", "auto", "0", "cuda-events", "fp32"],
+                           capture_output=True, text=True, timeout=600)
+    ms = re.search(r"([\d.]+) us/call avg, ([\d.]+) GB/s", small.stdout)
+    e2e = subprocess.run([str(harness), str(elems), str(max(3, min(args.steps, 20))), "3"], capture_output=True,
+                         text=True, timeout=600)
+    me = re.search(r"REF_E2E fp32 (\d+) (\d+) (\d+) ([\d.]+) ([\d.]+)", e2e.stdout)
+    e2e_val = MESSAGE_BYTES / (float(me.group(4)) * 1e-6) / 1e9 if me else None
+    return {
+        "metric": "allreduce_busbw_GBps_128MiB_fp32", "value": gbps, "unit": "GB/s", "n_gpus": 2,
+        "steps": args.steps, "warmup": 100, "ms_per_step": round(us / 1e3, 5), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": round(gbps / BASELINE_GBPS_128MB, 3), "dtype": "fp32",
+        "data": "synthetic (the reference's constant fill)", "impl": "reference",
+        "config": {"model": "sum all-reduce, 128 MiB fp32 per rank", "global_batch": MESSAGE_BYTES * 2,
+                   "seq_len": elems, "parallelism": "2 GPUs, one process (the reference's single-process mode)",
+                   "kernel": m.group(1),
+                   "note": "reference times with one event pair on GPU 0's first lane stream only "
+                           "(bench/benchmark_yali.cu:587-622); warm-up is fixed at 100 calls in its source"},
+        "latency_1MiB_us": {"avg": float(ms.group(1)) if ms else None},
+        "e2e": {"value": round(e2e_val, 2) if e2e_val else None, "unit": "GB/s",
+                "h2d_bytes_per_step": MESSAGE_BYTES * 2, "d2h_bytes_per_step": MESSAGE_BYTES * 2,
+                "timing": "wall clock around H2D + yali::allreduce + D2H on both GPUs"},
+        "gpu_launches": 0, "clocks": clocks,
+    }
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="own", choices=["own", "reference"])
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    res = run_reference(args) if args.impl == "reference" else run_own(args)
+    if int(os.environ.get("RANK", "0")) == 0 and res:
+        print(json.dumps(res), flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -73,7 +73,7 @@ def _compile(src: Path, flags: list[str], hdr_digest: str, verbose: bool) -> Pat
     obj = BUILD / (src.relative_to(CSRC).as_posix().replace("/", "_") + "." + key + ".o")
     if obj.exists():
         return obj
-    for old in BUILD.glob(src.relative_to(CSRC).as_posix().replace("/", "_") + ".*.o"):
+    for old in BUILD.glob(src.relative_to(CSRC).as_posix().replace("/", "_") + ".*.o*"):
         old.unlink()
     if src.suffix == ".cu":
         cmd = [NVCC] + NVCC_FLAGS + flags + ["-I", str(CSRC), "-c", str(src), "-o", str(obj)]
