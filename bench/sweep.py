@@ -1,0 +1,158 @@
+#!/usr/bin/env python
+"""Size sweep of the all-reduce variants against NCCL on the same GPUs.
+
+    python -m torch.distributed.run --nproc-per-node N --master-addr 127.0.0.1 bench/sweep.py \
+        [--min-bytes 4096] [--max-bytes 2147483648] [--dtypes fp32,bf16] [--variants auto,flash,stream,nvls] \
+        [--nccl] [--out sweep.jsonl] [--tuning-out tuning.json]
+
+Every (size, dtype, variant) is timed on the device (CUDA events around the timed
+calls on the launching stream, 20 warm-up calls, barrier + synchronize on both
+sides, max over ranks) and reported as NCCL-convention bus bandwidth; small
+messages rotate over buffers that together exceed L2.  `--nccl` times
+torch.distributed.all_reduce (backend nccl) with the same loop as the baseline.
+`--tuning-out` writes the fastest variant per size as a table the library loads
+through YALI_TUNING_FILE.
+
+Reference counterpart: scripts/sweep.py (phases 'YALI/NCCL x single/MPI sweeps'),
+which shells out to the benchmark binaries and regexes their stdout."""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import struct
+import sys
+from pathlib import Path
+
+import torch
+
+sys.path.insert(0, str(Path(__file__).resolve().parent.parent))
+import yali_b200 as yali  # noqa: E402
+
+DT = {"fp32": torch.float32, "fp16": torch.float16, "bf16": torch.bfloat16}
+L2_BYTES = 126 << 20
+
+
+def gather_max(comm, v: float) -> float:
+    if comm.world == 1 or comm.nlocal != 1:
+        return v
+    return max(struct.unpack("d", p)[0] for p in comm.allgather_object_bytes(struct.pack("d", v)))
+
+
+def timed(comm, fn, iters: int, warmup: int) -> float:
+    """Average microseconds per call, max over ranks."""
+    for i in range(warmup):
+        fn(i)
+    comm.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(iters):
+        fn(warmup + i)
+    e1.record()
+    torch.cuda.synchronize()
+    comm.barrier()
+    return gather_max(comm, e0.elapsed_time(e1) * 1e3 / iters)
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--min-bytes", type=int, default=4096)
+    ap.add_argument("--max-bytes", type=int, default=1 << 30)
+    ap.add_argument("--dtypes", default="fp32")
+    ap.add_argument("--variants", default="auto,flash,stream,nvls")
+    ap.add_argument("--nccl", action="store_true")
+    ap.add_argument("--emulate", type=int, default=0, help="emulate this many ranks on one GPU (no launcher)")
+    ap.add_argument("--out", default="")
+    ap.add_argument("--tuning-out", default="")
+    ap.add_argument("--iters", type=int, default=0, help="0: scaled by size")
+    args = ap.parse_args()
+
+    heap = 2 * args.max_bytes + (3 << 30)
+    if args.emulate:
+        comm = yali.Comm.emulated(args.emulate, heap_bytes=heap)
+    else:
+        comm = yali.Comm.from_env(heap_bytes=heap)
+    world, rank = comm.world, comm.rank
+    emu = bool(args.emulate)
+    lst = (lambda t: t if isinstance(t, list) else [t])
+    if args.nccl and not emu:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", comm.device))
+    factor = 2.0 * (world - 1) / world
+    variants = [v for v in args.variants.split(",") if v]
+    rows, best = [], {}
+    out_f = open(args.out, "w") if (args.out and rank == 0) else None
+    pool_bytes = max(args.max_bytes, L2_BYTES * 2 + (64 << 20))
+    comm.symm_reset()
+    pool_s = comm.symm_empty(pool_bytes, torch.uint8)
+    pool_r = comm.symm_empty(pool_bytes, torch.uint8)
+
+    for dname in args.dtypes.split(","):
+        dt = DT[dname]
+        esz = torch.empty(0, dtype=dt).element_size()
+        for t in lst(pool_s):
+            t.view(dt).normal_()
+        size = args.min_bytes
+        while size <= args.max_bytes:
+            n = size // esz
+            nbuf = max(1, min(256, (2 * L2_BYTES) // size)) if size < L2_BYTES else 1
+            views_s = [[t[k * size:(k + 1) * size].view(dt) for t in lst(pool_s)] for k in range(nbuf)]
+            views_r = [[t[k * size:(k + 1) * size].view(dt) for t in lst(pool_r)] for k in range(nbuf)]
+            pick = (lambda v: v if emu else v[0])
+            iters = args.iters or (200 if size <= (1 << 20) else 50 if size <= (64 << 20) else 15)
+            for var in variants:
+                def call(i, var=var):
+                    comm.all_reduce(pick(views_s[i % nbuf]), pick(views_r[i % nbuf]), mode=var)
+                try:
+                    us = timed(comm, call, iters, 20 if size <= (16 << 20) else 5)
+                    comm.check()
+                except RuntimeError as e:
+                    if "cannot run" in str(e) or "Unsupported" in str(e):
+                        continue
+                    raise
+                lc = comm.last_call()
+                row = {"impl": "yali_b200", "world": world, "dtype": dname, "bytes": size, "variant": var,
+                       "kernel": lc["variant"], "ctas": lc["ctas"], "slot_bytes": lc["slot_bytes"], "us": round(us, 2),
+                       "busbw_gbps": round(size * factor / us / 1e3, 2), "emulated": emu}
+                rows.append(row)
+                if var != "auto":
+                    key = (dname, size)
+                    if key not in best or us < best[key]["us"]:
+                        best[key] = row
+                if rank == 0:
+                    print(json.dumps(row), flush=True)
+                    if out_f:
+                        out_f.write(json.dumps(row) + "\n")
+            if args.nccl and not emu:
+                import torch.distributed as dist
+                bufs = [v[0].clone() for v in views_s] if size <= (64 << 20) else [views_r[0][0]]
+
+                def ncall(i):
+                    dist.all_reduce(bufs[i % len(bufs)])
+                us = timed(comm, ncall, iters, 20 if size <= (16 << 20) else 5)
+                row = {"impl": "nccl", "world": world, "dtype": dname, "bytes": size, "variant": "nccl",
+                       "us": round(us, 2), "busbw_gbps": round(size * factor / us / 1e3, 2)}
+                if rank == 0:
+                    print(json.dumps(row), flush=True)
+                    if out_f:
+                        out_f.write(json.dumps(row) + "\n")
+                del bufs
+            size *= 2
+    if args.tuning_out and rank == 0:
+        trows = []
+        for (dname, size), row in sorted(best.items(), key=lambda kv: (kv[0][0], kv[0][1])):
+            name = {"flash": "flash", "stream": "stream", "nvls1": "nvls1", "nvls2": "nvls2"}[row["kernel"]]
+            trows.append({"world": world, "elem_bytes": 4 if dname == "fp32" else 2, "max_bytes": size,
+                          "variant": name, "ctas": 0, "slot_bytes": 0, "busbw": row["busbw_gbps"]})
+        Path(args.tuning_out).write_text(json.dumps({"rows": trows}, indent=1))
+    if out_f:
+        out_f.close()
+    if args.nccl and not emu:
+        import torch.distributed as dist
+        dist.destroy_process_group()
+    comm.close()
+
+
+if __name__ == "__main__":
+    main()

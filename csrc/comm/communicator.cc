@@ -370,6 +370,8 @@ Result Communicator::Collective(const void* const* send, void* const* recv, uint
     caps.symmetric = symmetric;
     caps.peer_recv = peer_recv && !rs_only;
     caps.max_ctas = max_ctas_;
+    caps.force_ctas = opt.ctas > 0 ? static_cast<uint32_t>(opt.ctas) : 0u;
+    caps.force_slot_bytes = opt.slot_bytes > 0 ? static_cast<uint32_t>(opt.slot_bytes) : 0u;
     caps.vec_ok = true;
     for (int i = 0; i < nlocal(); ++i) caps.vec_ok = caps.vec_ok && Aligned16(send[i]) && Aligned16(recv[i]);
 
@@ -380,11 +382,6 @@ Result Communicator::Collective(const void* const* send, void* const* recv, uint
     std::string why;
     r = MakePlan(world_, count, in, out, opt.epilogue, mode, caps, EnvTuningTable(), &plan, &why);
     if (r != Result::Success) return Fail(r, why);
-    if (opt.ctas > 0) {
-        const uint32_t lim = plan.variant == Variant::Stream ? kMaxLanes
-                                                             : (plan.variant == Variant::Flash ? kMaxFlashCtas : kBarSlots);
-        plan.ctas = std::min<uint32_t>(std::min<uint32_t>(opt.ctas, max_ctas_), lim);
-    }
     if (world_ == 1 && plan.variant != Variant::Flash)
         return Fail(Result::Unsupported, "a single rank only runs the one-shot kernel");
 

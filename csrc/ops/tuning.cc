@@ -266,8 +266,11 @@ Result MakePlan(int world, uint64_t count, Dtype in, Dtype out, int epilogue, Ke
     }
     p.variant = v;
 
-    const int dev_ctas = env::DevCtas(), dev_lanes = env::DevLanes();
-    const long long dev_slot = env::DevSlotBytes();
+    // Per-call overrides win over the environment knobs.
+    const int dev_ctas = caps.force_ctas ? static_cast<int>(caps.force_ctas) : env::DevCtas();
+    const int dev_lanes = caps.force_ctas ? static_cast<int>(caps.force_ctas) : env::DevLanes();
+    const long long dev_slot = caps.force_slot_bytes ? static_cast<long long>(caps.force_slot_bytes)
+                                                      : env::DevSlotBytes();
     switch (v) {
         case Variant::Flash: {
             uint32_t c = row && row->ctas ? row->ctas : static_cast<uint32_t>(FlashLanePreset(bytes, in, world));

@@ -31,6 +31,8 @@ struct PlanCaps {
     bool peer_recv = false;        // every rank's recv is peer-addressable (direct all-gather possible)
     bool vec_ok = true;            // all pointers 16-byte aligned
     uint32_t max_ctas = 296;       // upper bound on CTAs per rank (co-residency for emulated ranks)
+    uint32_t force_ctas = 0;       // >0: caller's CTA / lane count (still clamped to the limits)
+    uint32_t force_slot_bytes = 0; // >0: caller's ring slot size (still clamped to the ring region)
 };
 
 struct Plan {

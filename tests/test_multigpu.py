@@ -1,0 +1,180 @@
+"""Real peer-to-peer paths: one process driving several GPUs (yali::Comm style) and
+one process per GPU (yali::MPIComm style, environment rendezvous + cuMem file
+descriptors), including the NVLS kernels when the box offers multicast.  Child
+processes run with NCCL_NVLS_ENABLE=0 for any library they load; this library's own
+multicast use is exercised only by ranks that all exit in an orderly way.
+
+Reference counterparts: tests/test_ops_allreduce.cu, tests/test_ops_allreduce_mpi.cu."""
+import multiprocessing as mp
+import os
+import time
+
+import pytest
+import torch
+
+import yali_b200 as yali
+from yali_b200 import _native
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu(2)]
+CTX = mp.get_context("spawn")
+
+
+def _ngpu():
+    return torch.cuda.device_count() if torch.cuda.is_available() else 0
+
+
+def _worlds():
+    n = _ngpu()
+    return [w for w in (2, 4, 8) if w <= n] or [2]
+
+
+def _fill(ts, dist=0, seed=1234, ranks=None):
+    ext = _native.ext()
+    for i, t in enumerate(ts):
+        with torch.cuda.device(t.device):
+            ext.fill_random(t, dist, seed + (ranks[i] if ranks else i))
+
+
+def _check(outs, in_dtype, world, dist=0, seed=1234, scale=1.0):
+    ext = _native.ext()
+    for o in outs:
+        with torch.cuda.device(o.device):
+            rep = ext.validate_sum(o, in_dtype, dist, seed, world, scale)
+        assert rep["mismatches"] == 0, rep
+
+
+@pytest.mark.parametrize("world", _worlds())
+def test_single_process_all_variants(world):
+    with yali.Comm.single_process(list(range(world)), heap_bytes=2 << 30) as comm:
+        assert comm.world == world and comm.nlocal == world
+        modes = ["flash", "stream"] + (["nvls"] if comm.has_multicast else [])
+        for dtype in (torch.float32, torch.bfloat16, torch.float16):
+            for n in (1, 33, 4099, 262144, (1 << 21) + 16):
+                xs = [torch.empty(n, dtype=dtype, device=f"cuda:{d}") for d in range(world)]
+                _fill(xs)
+                for mode in modes:
+                    if mode == "nvls" and (n * xs[0].element_size()) % 16:
+                        continue
+                    outs = comm.all_reduce(xs, mode=mode)
+                    comm.sync()
+                    _check(outs, dtype, world)
+        # symmetric buffers: zero-copy NVLS and direct all-gather
+        n = 1 << 20
+        send, recv = comm.symm_empty(n, torch.bfloat16), comm.symm_empty(n, torch.bfloat16)
+        _fill(send, dist=1)
+        for mode in modes:
+            for _ in range(5):  # back to back, no sync
+                comm.all_reduce(send, recv, mode=mode)
+            comm.sync()
+            _check(recv, torch.bfloat16, world, dist=1)
+        # in place on symmetric memory
+        comm.all_reduce(send, send, mode=modes[-1])
+        comm.sync()
+        _check(send, torch.bfloat16, world, dist=1)
+        # fused row epilogue across real GPUs
+        rows, hidden = 16, 4096
+        xs = [torch.empty(rows, hidden, dtype=torch.bfloat16, device=f"cuda:{d}") for d in range(world)]
+        _fill(xs, dist=1)
+        ws = [torch.ones(hidden, dtype=torch.bfloat16, device=f"cuda:{d}") for d in range(world)]
+        ys = comm.all_reduce_rmsnorm(xs, ws, None, eps=1e-5)
+        comm.sync()
+        ref, _ = yali.reference.residual_rmsnorm(yali.reference.all_reduce_sum(xs), ws[0].cpu().double(), None, 1e-5)
+        for y in ys:
+            torch.testing.assert_close(y.cpu().double(), ref, rtol=2e-2, atol=2e-2)
+
+
+def _rank_main(rank, world, port, q, scenario):
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
+                      MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    try:
+        import yali_b200 as yl
+        from yali_b200 import _native as nat
+        ext = nat.ext()
+        comm = yl.Comm.from_env(heap_bytes=2 << 30, timeout_ms=3000)
+        dev = f"cuda:{comm.device}"
+        info = {"kind": comm.heap_kind, "mc": comm.has_multicast}
+        ok = True
+        if scenario == "collectives":
+            modes = ["flash", "stream"] + (["nvls"] if comm.has_multicast else [])
+            for dtype in (torch.float32, torch.bfloat16):
+                for n in (7, 4096, 300000, (1 << 22)):
+                    x = torch.empty(n, dtype=dtype, device=dev)
+                    ext.fill_random(x, 0, 1234 + rank)
+                    for mode in modes:
+                        if mode == "nvls" and (n * x.element_size()) % 16:
+                            continue
+                        y = comm.all_reduce(x, mode=mode)
+                        comm.sync()
+                        ok &= ext.validate_sum(y, dtype, 0, 1234, world)["mismatches"] == 0
+            n = 1 << 20
+            s, r = comm.symm_empty(n, torch.float32), comm.symm_empty(n, torch.float32)
+            ext.fill_random(s, 1, 99 + rank)
+            for mode in modes:
+                for _ in range(4):
+                    comm.all_reduce(s, r, mode=mode)
+                comm.sync()
+                ok &= ext.validate_sum(r, torch.float32, 1, 99, world)["mismatches"] == 0
+            sh = comm.reduce_scatter(s)
+            full = comm.all_gather(sh, n)
+            comm.sync()
+            ok &= ext.validate_sum(full, torch.float32, 1, 99, world)["mismatches"] == 0
+        elif scenario == "leave_between_steps":
+            x = torch.empty(65536, dtype=torch.float32, device=dev)
+            ext.fill_random(x, 0, 1234 + rank)
+            y = comm.all_reduce(x, mode="flash")
+            comm.sync()
+            ok &= ext.validate_sum(y, torch.float32, 0, 1234, world)["mismatches"] == 0
+            comm.barrier()  # nothing in flight anywhere
+            if rank == world - 1:
+                # This rank stops taking part (its process stays alive until the others are done, so
+                # its heap stays mapped); the others' next collective must time out, not hang.
+                q.put((rank, True, info))
+                time.sleep(8)
+                os._exit(0)
+            comm.all_reduce(x, mode="flash")
+            try:
+                comm.sync()
+                ok = False
+            except Exception as e:  # noqa: BLE001
+                ok &= "waiting for rank" in str(e)
+            q.put((rank, bool(ok), info))
+            os._exit(0)  # the communicator cannot be closed collectively any more
+        comm.close()
+        q.put((rank, bool(ok), info))
+    except Exception as e:  # noqa: BLE001
+        q.put((rank, False, {"error": repr(e)[:300]}))
+
+
+def _spawn(world, scenario, free_port, timeout=300):
+    q = CTX.Queue()
+    procs = [CTX.Process(target=_rank_main, args=(r, world, free_port, q, scenario)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = {}
+    deadline = time.time() + timeout
+    while len(res) < world and time.time() < deadline:
+        try:
+            r, ok, info = q.get(timeout=1.0)
+            res[r] = (ok, info)
+        except Exception:  # noqa: BLE001
+            if all(not p.is_alive() for p in procs):
+                break
+    for p in procs:
+        p.join(20)
+        if p.is_alive():
+            p.kill()
+    return res
+
+
+@pytest.mark.parametrize("world", _worlds())
+def test_one_process_per_gpu(world, free_port):
+    res = _spawn(world, "collectives", free_port)
+    assert len(res) == world, res
+    assert all(ok for ok, _ in res.values()), res
+    assert all(info["kind"] in ("cumem-fd", "cuda-ipc") for _, info in res.values())
+
+
+def test_rank_that_stops_between_steps_times_out_the_others(free_port, monkeypatch):
+    monkeypatch.setenv("YALI_NVLS_DISABLE", "1")  # plain peer loads/stores only
+    res = _spawn(2, "leave_between_steps", free_port + 1, timeout=120)
+    assert len(res) == 2 and all(ok for ok, _ in res.values()), res
