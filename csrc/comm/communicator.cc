@@ -33,7 +33,7 @@ bool MakeHeapLayout(int world, uint64_t requested_total, uint64_t granularity, H
         l.nvls_cap = 64 * MiB;
         off += 2 * l.nvls_cap;
         l.gemm_off = off;
-        l.gemm_cap = 4 * MiB;
+        l.gemm_cap = std::max<uint64_t>(4 * MiB, 16 * MiB / world);  // 2048 rows of 4096 bf16 sharded over the ranks
         off += 2ull * world * l.gemm_cap;
     }
     l.user_off = off;
@@ -522,6 +522,7 @@ Result Communicator::Reset() {
         std::memset(l.status, 0, sizeof(DeviceStatus));
     }
     flash_epoch_ = bar_epoch_ = stream_seq_ = gemm_epoch_ = 0;
+    gemm_ = GemmCounters();
     poisoned_ = false;
     if (bs_ && bs_->barrier() != Result::Success) return Fail(Result::BootstrapError, bs_->last_error());
     return Result::Success;

@@ -120,6 +120,16 @@ class Communicator {
     // Reserves epochs for an externally launched kernel that uses the per-CTA barrier.
     uint32_t TakeBarrierEpochs(uint32_t n);
     uint32_t TakeGemmEpoch() { return ++gemm_epoch_; }
+    // Cumulative targets of the fused GEMM's arrival / delivered-rows counters, indexed by rank
+    // (identical on every rank; cleared by Reset()).
+    struct GemmCounters {
+        uint32_t cnt[kMaxRanks] = {};
+        uint32_t done[kMaxRanks] = {};
+    };
+    GemmCounters& gemm_counters() { return gemm_; }
+    bool poisoned() const { return poisoned_; }
+    uint32_t max_ctas() const { return max_ctas_; }
+    void set_error(const std::string& e) { err_ = e; }
     void CountLaunch(uint64_t n = 1) { last_.launches += n; }
 
    private:
@@ -161,6 +171,7 @@ class Communicator {
     uint32_t bar_epoch_ = 0;
     uint32_t stream_seq_ = 0;
     uint32_t gemm_epoch_ = 0;
+    GemmCounters gemm_;
     uint64_t user_bump_ = 0;
     bool poisoned_ = false;
     LastCallInfo last_;

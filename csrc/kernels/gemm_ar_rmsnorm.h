@@ -1,0 +1,43 @@
+// Argument block and host entry points of the fused row-parallel GEMM +
+// all-reduce + residual + RMSNorm kernel (gemm_ar_rmsnorm.cu).
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../comm/layout.h"
+
+namespace yali {
+
+constexpr int kGemmTileM = 128;
+constexpr int kGemmTileN = 128;
+constexpr int kGemmThreads = 128;
+constexpr int kGemmMaxVecPerThread = 4;  // N <= 4 * 128 threads * 8 bf16 = 4096
+
+struct alignas(64) GemmArArgs {
+    CUtensorMap tmap_a;  // x  [T, K] bf16, box 64 x 128, 128-byte swizzle
+    CUtensorMap tmap_b;  // W  [N, K] bf16, box 64 x 128, 128-byte swizzle
+    CommView cv;
+    const void* residual;     // [T, N] bf16 or nullptr
+    void* residual_out;       // [T, N] bf16 or nullptr (sum + residual), this rank's copy
+    void* residual_out_all[kMaxRanks];  // two-shot: every rank's residual_out (the row owner writes all copies)
+    const void* norm_weight;  // [N] bf16
+    void* out[kMaxRanks];     // every rank's output [T, N] (two-shot writes all, one-shot only its own)
+    uint32_t T, N, K;
+    uint32_t rows_per_owner;  // two-shot: rows normalised by each rank
+    uint32_t oneshot;         // 1: every rank receives all partial rows and normalises all of them
+    uint32_t epoch;           // parity selects the landing-zone half
+    uint32_t cnt_wanted;      // arrival counter value (per source) at which this rank's partials are complete
+    uint32_t done_wanted[kMaxRanks];  // per owner: delivered-rows counter value at which this rank's output is complete
+    float eps;
+};
+
+struct GemmArEmuArgs {
+    GemmArArgs r[kMaxRanks];
+};
+
+const void* GemmArKernel(bool emu);
+uint32_t GemmArSmemBytes();
+
+}  // namespace yali

@@ -1,0 +1,207 @@
+#include "fused_linear.h"
+
+#include <algorithm>
+#include <cstring>
+
+#include "../comm/cuda_driver.h"
+#include "../kernels/gemm_ar_rmsnorm.h"
+
+namespace yali {
+
+namespace {
+
+bool EncodeTileMap(const DriverApi* d, CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols_k,
+                   uint32_t box_rows, std::string* err) {
+    const cuuint64_t dims[2] = {cols_k, rows};             // innermost first
+    const cuuint64_t strides[1] = {cols_k * 2};            // bytes between rows
+    const cuuint32_t box[2] = {64, box_rows};              // 64 bf16 = 128 bytes = one swizzle row
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = d->TensorMapEncodeTiled(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims,
+                                         strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        if (err) *err = "cuTensorMapEncodeTiled: " + d->ErrorText(r);
+        return false;
+    }
+    return true;
+}
+
+}  // namespace
+
+uint32_t FusedLinearOneShotMaxRows(int world) { return world <= 2 ? 256u : 32u; }
+
+Result FusedLinearAllReduceRmsNorm(Communicator& comm, const FusedLinearDesc* descs, uint32_t T, uint32_t N,
+                                   uint32_t K, const FusedLinearOptions& opt, const cudaStream_t* streams) {
+    auto fail = [&](Result r, const std::string& what) {
+        comm.set_error(what);
+        return r;
+    };
+    if (comm.poisoned()) return fail(Result::Timeout, "communicator is poisoned by an earlier timeout; call Reset()");
+    if (T == 0) return Result::Success;
+    if (N % kGemmTileN != 0 || N > 4096 || K % 64 != 0 || K == 0)
+        return fail(Result::Unsupported, "fused linear needs N a multiple of 128 (at most 4096) and K a multiple of 64");
+    const int W = comm.world(), nlocal = comm.nlocal();
+    for (int i = 0; i < nlocal; ++i) {
+        const FusedLinearDesc& d = descs[i];
+        if (!d.x || !d.w || !d.norm_weight || !d.out) return fail(Result::InvalidArg, "null tensor");
+        if ((reinterpret_cast<uintptr_t>(d.x) | reinterpret_cast<uintptr_t>(d.w) | reinterpret_cast<uintptr_t>(d.out) |
+             reinterpret_cast<uintptr_t>(d.norm_weight) | reinterpret_cast<uintptr_t>(d.residual) |
+             reinterpret_cast<uintptr_t>(d.residual_out)) & 15u)
+            return fail(Result::InvalidArg, "tensors must be 16-byte aligned");
+    }
+    std::string derr;
+    const DriverApi* drv = DriverApi::Get(&derr);
+    if (!drv) return fail(Result::CudaError, derr);
+
+    const HeapLayout& lay = comm.layout();
+    const uint64_t row_bytes = static_cast<uint64_t>(N) * 2;
+    bool oneshot = opt.force_oneshot >= 0 ? opt.force_oneshot != 0 : T <= FusedLinearOneShotMaxRows(W);
+    if (W == 1) oneshot = true;
+    // Two-shot writes into every rank's output: those must be addressable from here.
+    bool outs_addressable = nlocal == W;
+    uint64_t out_off = 0;
+    if (!outs_addressable) {
+        outs_addressable = comm.IsSymmetric(0, descs[0].out, static_cast<uint64_t>(T) * row_bytes);
+        if (outs_addressable) out_off = static_cast<const char*>(descs[0].out) - comm.View(0).heap[comm.rank_of(0)];
+    }
+    uint64_t res_out_off = 0;
+    if (nlocal != W && descs[0].residual_out) {
+        // One GPU per process, two-shot: the owner of a row also writes every rank's residual_out.
+        if (comm.IsSymmetric(0, descs[0].residual_out, static_cast<uint64_t>(T) * row_bytes))
+            res_out_off = static_cast<const char*>(descs[0].residual_out) - comm.View(0).heap[comm.rank_of(0)];
+        else
+            outs_addressable = false;
+    }
+    if (!oneshot && !outs_addressable) {
+        if (opt.force_oneshot == 0)
+            return fail(Result::Unsupported, "two-shot fused linear needs out (and residual_out) in symmetric memory");
+        oneshot = true;
+    }
+    uint32_t Rs = oneshot ? T : (T + W - 1) / W;
+    if (static_cast<uint64_t>(Rs) * row_bytes > lay.gemm_cap) {
+        if (oneshot && outs_addressable && static_cast<uint64_t>((T + W - 1) / W) * row_bytes <= lay.gemm_cap &&
+            opt.force_oneshot != 1) {
+            oneshot = false;
+            Rs = (T + W - 1) / W;
+        } else {
+            return fail(Result::Unsupported, "rows do not fit the landing zone of the fused linear (" +
+                                                 std::to_string(lay.gemm_cap) + " bytes per source)");
+        }
+    }
+
+    const uint32_t ntm = (T + kGemmTileM - 1) / kGemmTileM, ntn = N / kGemmTileN;
+    // Arrivals owner q expects from every source in this call, and rows owner q delivers.
+    uint32_t arrivals[kMaxRanks] = {}, rows_of[kMaxRanks] = {};
+    for (int q = 0; q < W; ++q) {
+        if (oneshot) {
+            arrivals[q] = ntm * ntn;
+            rows_of[q] = 0;
+        } else {
+            const uint32_t lo = std::min<uint32_t>(T, q * Rs), hi = std::min<uint32_t>(T, lo + Rs);
+            if (hi > lo) {
+                const uint32_t first = lo / kGemmTileM, last = (hi - 1) / kGemmTileM;
+                arrivals[q] = (last - first + 1) * ntn;
+            }
+            rows_of[q] = hi - lo;
+        }
+    }
+    Communicator::GemmCounters& gc = comm.gemm_counters();
+    for (int q = 0; q < W; ++q) {
+        gc.cnt[q] += arrivals[q];
+        gc.done[q] += rows_of[q];
+    }
+    const uint32_t epoch = comm.TakeGemmEpoch();
+
+    const void* fn = GemmArKernel(comm.emulated());
+    const uint32_t smem = GemmArSmemBytes();
+    static bool attr_set[2] = {false, false};
+    if (!attr_set[comm.emulated() ? 1 : 0]) {
+        // Per device in a multi-GPU process; cheap enough to repeat for each local device once.
+        for (int i = 0; i < nlocal; ++i) {
+            if (nlocal > 1) cudaSetDevice(comm.device_of(i));
+            cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+            if (e != cudaSuccess) return fail(Result::CudaError, std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(e));
+            if (comm.emulated()) break;
+        }
+        attr_set[comm.emulated() ? 1 : 0] = true;
+    }
+    int per_sm = 0, sms = 0;
+    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fn, kGemmThreads, smem);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, comm.device_of(0));
+    uint32_t resident = static_cast<uint32_t>(std::max(1, per_sm) * std::max(1, sms));
+    if (comm.emulated()) resident = std::max<uint32_t>(1, resident / W);
+    const uint32_t work = std::max<uint32_t>(ntm * ntn, oneshot ? T : Rs);
+    uint32_t ctas = std::min<uint32_t>(resident, work);
+    if (opt.ctas > 0) ctas = std::min<uint32_t>(ctas, opt.ctas);
+
+    std::vector<GemmArArgs> args(nlocal);
+    for (int i = 0; i < nlocal; ++i) {
+        GemmArArgs& a = args[i];
+        std::memset(&a, 0, sizeof(a));
+        const FusedLinearDesc& d = descs[i];
+        const int rank = comm.rank_of(i);
+        if (nlocal > 1) cudaSetDevice(comm.device_of(i));
+        if (!EncodeTileMap(drv, &a.tmap_a, d.x, T, K, kGemmTileM, &derr) ||
+            !EncodeTileMap(drv, &a.tmap_b, d.w, N, K, kGemmTileN, &derr))
+            return fail(Result::CudaError, derr);
+        a.cv = comm.View(i);
+        a.residual = d.residual;
+        a.residual_out = d.residual_out;
+        a.norm_weight = d.norm_weight;
+        for (int q = 0; q < W; ++q) a.out[q] = a.residual_out_all[q] = nullptr;
+        a.out[rank] = d.out;
+        a.residual_out_all[rank] = d.residual_out;
+        if (!oneshot) {
+            if (nlocal == W) {
+                for (int j = 0; j < nlocal; ++j) {
+                    a.out[comm.rank_of(j)] = descs[j].out;
+                    a.residual_out_all[comm.rank_of(j)] = descs[j].residual_out;
+                }
+            } else {
+                for (int q = 0; q < W; ++q) {
+                    a.out[q] = a.cv.heap[q] + out_off;
+                    if (d.residual_out) a.residual_out_all[q] = a.cv.heap[q] + res_out_off;
+                }
+            }
+        }
+        a.T = T;
+        a.N = N;
+        a.K = K;
+        a.rows_per_owner = Rs;
+        a.oneshot = oneshot ? 1u : 0u;
+        a.epoch = epoch;
+        a.cnt_wanted = gc.cnt[rank];
+        for (int q = 0; q < W; ++q) a.done_wanted[q] = gc.done[q];
+        a.eps = opt.eps;
+    }
+    if (comm.emulated()) {
+        GemmArEmuArgs* e = new GemmArEmuArgs();
+        std::memset(e, 0, sizeof(*e));
+        for (int i = 0; i < nlocal; ++i) e->r[comm.rank_of(i)] = args[i];
+        cudaStream_t s = streams && streams[0] ? streams[0] : comm.default_stream(0);
+        void* params[] = {e};
+        cudaError_t ce = cudaLaunchCooperativeKernel(fn, dim3(ctas, W), dim3(kGemmThreads), params, smem, s);
+        delete e;
+        if (ce != cudaSuccess) {
+            (void)cudaGetLastError();
+            return fail(Result::CudaError, std::string("cooperative launch failed: ") + cudaGetErrorString(ce));
+        }
+        comm.CountLaunch(1);
+        return Result::Success;
+    }
+    for (int i = 0; i < nlocal; ++i) {
+        if (nlocal > 1) cudaSetDevice(comm.device_of(i));
+        cudaStream_t s = streams && streams[i] ? streams[i] : comm.default_stream(i);
+        void* params[] = {&args[i]};
+        cudaError_t ce = cudaLaunchKernel(fn, dim3(ctas), dim3(kGemmThreads), params, smem, s);
+        if (ce != cudaSuccess) {
+            (void)cudaGetLastError();
+            return fail(Result::CudaError, std::string("kernel launch failed: ") + cudaGetErrorString(ce));
+        }
+        comm.CountLaunch(1);
+    }
+    return Result::Success;
+}
+
+}  // namespace yali

@@ -1,0 +1,37 @@
+// Host side of the fused tensor-parallel layer:
+//     out = RMSNorm(residual + sum over ranks of x @ W^T) * norm_weight
+// x: [T, K] bf16 per rank, W: [N, K] bf16 per rank (torch.nn.Linear layout), out / residual:
+// [T, N] bf16, norm_weight: [N] bf16.  N a multiple of 128 and at most 4096, K a multiple of 64.
+// Two-shot (rows sharded over the ranks, results written to every rank's output) needs every
+// rank's `out` to be peer-addressable: buffers of one process, or symmetric buffers.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include "../comm/communicator.h"
+
+namespace yali {
+
+struct FusedLinearDesc {
+    const void* x = nullptr;
+    const void* w = nullptr;
+    const void* residual = nullptr;  // optional
+    void* residual_out = nullptr;    // optional
+    const void* norm_weight = nullptr;
+    void* out = nullptr;
+};
+
+struct FusedLinearOptions {
+    int force_oneshot = -1;  // -1: by size; 0: two-shot; 1: one-shot
+    int ctas = 0;            // 0: as many as are resident
+    float eps = 1e-5f;
+};
+
+// descs: one per local rank.  Launches one kernel per rank (one cooperative launch for emulated ranks).
+Result FusedLinearAllReduceRmsNorm(Communicator& comm, const FusedLinearDesc* descs, uint32_t T, uint32_t N,
+                                   uint32_t K, const FusedLinearOptions& opt, const cudaStream_t* streams);
+
+// Rows from which the two-shot form is used when `force_oneshot` is -1.
+uint32_t FusedLinearOneShotMaxRows(int world);
+
+}  // namespace yali

@@ -16,6 +16,7 @@
 #include "comm/communicator.h"
 #include "comm/topology.h"
 #include "ops/buffer_ops.h"
+#include "ops/fused_linear.h"
 #include "ops/tuning.h"
 
 namespace py = pybind11;
@@ -273,6 +274,53 @@ class PyComm {
         Throw(res, c().last_error());
     }
 
+    // out = RMSNorm(residual + sum_r x_r @ w_r^T) * norm_weight, one kernel per rank.
+    void FusedLinear(std::vector<at::Tensor> x, std::vector<at::Tensor> w, std::vector<at::Tensor> norm_weight,
+                     std::vector<at::Tensor> out, c10::optional<std::vector<at::Tensor>> residual,
+                     c10::optional<std::vector<at::Tensor>> residual_out, double eps, int force_oneshot, int ctas) {
+        at::ScalarType d;
+        int64_t n;
+        CheckTensors(x, "x", &d, &n);
+        TORCH_CHECK(d == at::kBFloat16, "yali: fused linear takes bf16 tensors");
+        CheckTensors(w, "w", &d, &n);
+        TORCH_CHECK(d == at::kBFloat16, "yali: fused linear takes bf16 tensors");
+        CheckTensors(norm_weight, "norm_weight", &d, &n);
+        TORCH_CHECK(d == at::kBFloat16, "yali: fused linear takes bf16 tensors");
+        CheckTensors(out, "out", &d, &n);
+        TORCH_CHECK(d == at::kBFloat16, "yali: fused linear takes bf16 tensors");
+        TORCH_CHECK(x[0].dim() == 2 && w[0].dim() == 2 && out[0].dim() == 2, "yali: x [T,K], w [N,K], out [T,N]");
+        const int64_t T = x[0].size(0), K = x[0].size(1), N = w[0].size(0);
+        TORCH_CHECK(w[0].size(1) == K && out[0].size(0) == T && out[0].size(1) == N && norm_weight[0].numel() == N,
+                    "yali: fused linear shape mismatch");
+        const int nl = c().nlocal();
+        std::vector<FusedLinearDesc> descs(nl);
+        for (int i = 0; i < nl; ++i) {
+            descs[i].x = x[i].data_ptr();
+            descs[i].w = w[i].data_ptr();
+            descs[i].norm_weight = norm_weight[i].data_ptr();
+            descs[i].out = out[i].data_ptr();
+        }
+        if (residual.has_value()) {
+            CheckTensors(*residual, "residual", &d, &n);
+            TORCH_CHECK(d == at::kBFloat16 && n == T * N, "yali: residual must be bf16 [T,N]");
+            for (int i = 0; i < nl; ++i) descs[i].residual = (*residual)[i].data_ptr();
+        }
+        if (residual_out.has_value()) {
+            CheckTensors(*residual_out, "residual_out", &d, &n);
+            TORCH_CHECK(d == at::kBFloat16 && n == T * N, "yali: residual_out must be bf16 [T,N]");
+            for (int i = 0; i < nl; ++i) descs[i].residual_out = (*residual_out)[i].data_ptr();
+        }
+        FusedLinearOptions o;
+        o.force_oneshot = force_oneshot;
+        o.ctas = ctas;
+        o.eps = static_cast<float>(eps);
+        auto st = Streams();
+        c10::cuda::OptionalCUDAGuard guard(c().device_of(0));
+        Throw(FusedLinearAllReduceRmsNorm(c(), descs.data(), static_cast<uint32_t>(T), static_cast<uint32_t>(N),
+                                          static_cast<uint32_t>(K), o, st.data()),
+              c().last_error());
+    }
+
     // One tensor per local rank, at the same offset of every rank's heap.  The tensors alias
     // heap memory: they stay valid until the communicator is closed.
     std::vector<at::Tensor> SymmEmpty(std::vector<int64_t> shape, at::ScalarType dtype) {
@@ -430,6 +478,9 @@ PYBIND11_MODULE(_C, m) {
              py::arg("slot_bytes") = 0)
         .def("all_gather", &PyComm::AllGather, py::arg("send"), py::arg("recv"), py::arg("ctas") = 0,
              py::arg("slot_bytes") = 0)
+        .def("fused_linear", &PyComm::FusedLinear, py::arg("x"), py::arg("w"), py::arg("norm_weight"), py::arg("out"),
+             py::arg("residual") = py::none(), py::arg("residual_out") = py::none(), py::arg("eps") = 1e-5,
+             py::arg("force_oneshot") = -1, py::arg("ctas") = 0)
         .def("symm_empty", &PyComm::SymmEmpty, py::arg("shape"), py::arg("dtype"))
         .def("symm_reset", &PyComm::SymmReset)
         .def("sync", &PyComm::Sync)

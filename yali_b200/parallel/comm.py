@@ -167,6 +167,31 @@ class Comm:
             raise _translate(e) from None
         return self._like_input(x, r)
 
+    def fused_linear_rmsnorm(self, x: TensorOrList, w: TensorOrList, norm_weight: TensorOrList,
+                             residual: Optional[TensorOrList] = None, *, eps: float = 1e-5,
+                             out: Optional[TensorOrList] = None, residual_out: Optional[TensorOrList] = None,
+                             oneshot: Optional[bool] = None, ctas: int = 0):
+        """out = RMSNorm(residual + sum over ranks of x @ w.T) * norm_weight in ONE kernel per rank
+        (tcgen05 GEMM whose epilogue pushes partial rows to their owner over NVLink, then reduce + norm).
+        x: [T, K], w: [N, K] (this rank's slice, nn.Linear layout), bf16.  With one GPU per process the
+        two-shot form (T above a few dozen rows) needs `out` from symm_empty()."""
+        xs, ws, nws = self._as_list(x, "x"), self._as_list(w, "w"), self._as_list(norm_weight, "norm_weight")
+        if out is None:
+            T, N = xs[0].shape[0], ws[0].shape[0]
+            if self.nlocal == 1 and self.world > 1:
+                outs = [self.symm_empty([T, N], torch.bfloat16)]
+            else:
+                outs = [torch.empty(T, N, dtype=torch.bfloat16, device=t.device) for t in xs]
+        else:
+            outs = self._as_list(out, "out")
+        res = None if residual is None else self._as_list(residual, "residual")
+        ro = None if residual_out is None else self._as_list(residual_out, "residual_out")
+        try:
+            self._impl.fused_linear(xs, ws, nws, outs, res, ro, eps, -1 if oneshot is None else int(oneshot), ctas)
+        except RuntimeError as e:
+            raise _translate(e) from None
+        return self._like_input(x, outs)
+
     def shard_elems(self, count: int) -> int:
         return _native.ext().shard_elems(count, self.world)
 
