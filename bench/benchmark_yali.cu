@@ -1,0 +1,185 @@
+// benchmark_yali: all-reduce over 2..8 GPUs driven by ONE process (yali::Comm style).
+//
+//   benchmark_yali [elements] [calls] [verify] [mode] [lanes] [timing] [dtype] [gpus] [symmetric]
+//
+// Inputs are U(-1,1) from seed 1234+rank.  In cuda-events mode every call is
+// bracketed by events on every rank's stream; a call's time is the max over
+// ranks, and the average / p50 / p99 are taken over calls.  `throughput` is wall
+// clock with one sync at the end, `latency` syncs after every call.  With
+// YALI_EMULATE=1 the ranks are emulated on GPU 0 (for machines with one GPU).
+//
+// Parity: bench/benchmark_yali.cu of the reference (same positional arguments and
+// result line; two GPUs only; one event pair on GPU 0; constant fills).
+#include <cuda_runtime.h>
+
+#include <chrono>
+#include <memory>
+
+#include "bench_common.h"
+#include "comm/communicator.h"
+#include "ops/buffer_ops.h"
+
+using namespace yali;
+
+#define CK(x)                                                                                     \
+    do {                                                                                          \
+        cudaError_t e_ = (x);                                                                     \
+        if (e_ != cudaSuccess) {                                                                  \
+            std::fprintf(stderr, "%s:%d: %s\n", __FILE__, __LINE__, cudaGetErrorString(e_));      \
+            std::exit(1);                                                                         \
+        }                                                                                         \
+    } while (0)
+
+int main(int argc, char** argv) {
+    bench::Args a = bench::Parse(argc, argv);
+    if (a.help) {
+        bench::Usage(argv[0], "All-reduce benchmark, one process driving all GPUs.");
+        return 0;
+    }
+    const bool emulate = std::getenv("YALI_EMULATE") && std::atoi(std::getenv("YALI_EMULATE")) != 0;
+    const int W = a.gpus;
+    const size_t bytes = a.elements * DtypeSize(a.dtype);
+    CommOptions copt;
+    copt.heap_bytes = (3ull << 30) + 2 * bytes;
+    std::unique_ptr<Communicator> comm;
+    std::string err;
+    Result r;
+    if (emulate) {
+        r = Communicator::CreateEmulated(W, 0, copt, &comm, &err);
+    } else {
+        std::vector<int> devs(W);
+        for (int i = 0; i < W; ++i) devs[i] = i;
+        r = Communicator::CreateSingleProcess(devs, copt, &comm, &err);
+    }
+    if (r != Result::Success) {
+        std::fprintf(stderr, "communicator: %s (%s)\n", GetErrorString(r), err.c_str());
+        return 2;
+    }
+    std::vector<void*> send(W), recv(W);
+    if (a.symmetric) {
+        if (comm->SymmAlloc(bytes, &send) != Result::Success || comm->SymmAlloc(bytes, &recv) != Result::Success) {
+            std::fprintf(stderr, "symmetric allocation failed: %s\n", comm->last_error().c_str());
+            return 2;
+        }
+    } else {
+        for (int i = 0; i < W; ++i) {
+            CK(cudaSetDevice(comm->device_of(i)));
+            CK(cudaMalloc(&send[i], bytes ? bytes : 16));
+            CK(cudaMalloc(&recv[i], bytes ? bytes : 16));
+        }
+    }
+    std::vector<cudaStream_t> st(W);
+    for (int i = 0; i < W; ++i) {
+        CK(cudaSetDevice(comm->device_of(i)));
+        st[i] = comm->default_stream(i);
+        CK(FillRandom(send[i], a.elements, a.dtype, kDistUniformPm1, 1234 + i, st[i]));
+        CK(cudaStreamSynchronize(st[i]));
+    }
+    OpOptions opt;
+    opt.mode = a.mode;
+    opt.ctas = a.lanes;
+    std::vector<const void*> csend(send.begin(), send.end());
+    auto call = [&]() {
+        Result rr = comm->AllReduce(csend.data(), recv.data(), a.elements, a.dtype, a.dtype, opt, st.data());
+        if (rr != Result::Success) {
+            std::fprintf(stderr, "all-reduce: %s (%s)\n", GetErrorString(rr), comm->last_error().c_str());
+            std::exit(3);
+        }
+    };
+    auto sync_all = [&]() {
+        if (comm->Sync(st.data()) != Result::Success) {
+            std::fprintf(stderr, "sync: %s\n", comm->last_error().c_str());
+            std::exit(3);
+        }
+    };
+    std::printf("================================================================================\n");
+    std::printf("YALI-B200 AllReduce Benchmark (%s)  ranks=%d%s  %zu elements (%.2f MB)  calls=%d warmup=%d\n",
+                DtypeName(a.dtype), W, emulate ? " (emulated on one GPU)" : "", a.elements, bytes / 1e6, a.calls,
+                a.warmup);
+    std::printf("heap=%s multicast=%d buffers=%s timing=%s\n", comm->heap_kind(), comm->has_multicast() ? 1 : 0,
+                a.symmetric ? "symmetric" : "cudaMalloc", bench::TimingModeName(a.timing));
+    std::printf("================================================================================\n");
+    for (int i = 0; i < a.warmup; ++i) call();
+    sync_all();
+
+    double avg_us = 0;
+    bench::Stats per_call;
+    const int nev = emulate ? 1 : W;
+    if (a.timing == bench::TimingMode::CudaEvents) {
+        std::vector<std::vector<cudaEvent_t>> ev(nev, std::vector<cudaEvent_t>(a.calls + 1));
+        for (int i = 0; i < nev; ++i) {
+            CK(cudaSetDevice(comm->device_of(i)));
+            for (auto& e : ev[i]) CK(cudaEventCreate(&e));
+            CK(cudaEventRecord(ev[i][0], st[i]));
+        }
+        for (int c = 0; c < a.calls; ++c) {
+            call();
+            for (int i = 0; i < nev; ++i) {
+                CK(cudaSetDevice(comm->device_of(i)));
+                CK(cudaEventRecord(ev[i][c + 1], st[i]));
+            }
+        }
+        sync_all();
+        std::vector<double> per(a.calls, 0.0);
+        double total = 0;
+        for (int i = 0; i < nev; ++i) {
+            float ms = 0;
+            CK(cudaEventElapsedTime(&ms, ev[i][0], ev[i][a.calls]));
+            total = std::max(total, static_cast<double>(ms) * 1e3);
+            for (int c = 0; c < a.calls; ++c) {
+                CK(cudaEventElapsedTime(&ms, ev[i][c], ev[i][c + 1]));
+                per[c] = std::max(per[c], static_cast<double>(ms) * 1e3);
+            }
+        }
+        avg_us = total / a.calls;
+        per_call = bench::Summarise(per);
+    } else if (a.timing == bench::TimingMode::Throughput) {
+        auto t0 = std::chrono::steady_clock::now();
+        for (int c = 0; c < a.calls; ++c) call();
+        sync_all();
+        avg_us = std::chrono::duration<double, std::micro>(std::chrono::steady_clock::now() - t0).count() / a.calls;
+    } else {
+        std::vector<double> per(a.calls);
+        auto t0 = std::chrono::steady_clock::now();
+        for (int c = 0; c < a.calls; ++c) {
+            auto s0 = std::chrono::steady_clock::now();
+            call();
+            sync_all();
+            per[c] = std::chrono::duration<double, std::micro>(std::chrono::steady_clock::now() - s0).count();
+        }
+        avg_us = std::chrono::duration<double, std::micro>(std::chrono::steady_clock::now() - t0).count() / a.calls;
+        per_call = bench::Summarise(per);
+    }
+    const LastCallInfo& lc = comm->last_call();
+    char extra[160];
+    std::snprintf(extra, sizeof(extra), "\"ctas\":%u,\"slot_bytes\":%u,\"symmetric\":%d,\"emulated\":%d", lc.ctas,
+                  lc.slot_bytes, a.symmetric ? 1 : 0, emulate ? 1 : 0);
+    const char* kname = lc.variant == Variant::Flash ? "Flash" : lc.variant == Variant::Stream ? "Stream"
+                        : lc.variant == Variant::NvlsOneShot ? "NVLS1" : "NVLS2";
+    bench::Report("YALI", kname, a, W, avg_us, &per_call, extra);
+    int rc = 0;
+    if (a.verify) {
+        bool all_ok = true;
+        for (int i = 0; i < W; ++i) {
+            CK(cudaSetDevice(comm->device_of(i)));
+            ValidateReport rep;
+            bool ok = ValidateRandomResult(recv[i], a.elements, a.dtype, a.dtype, kDistUniformPm1, 1234, W, 1.0f, &rep);
+            if (!ok) {
+                std::printf("FAILED: rank %d: %llu mismatches, first at %llu, max abs err %g\n", i, rep.mismatches,
+                            rep.first_mismatch, rep.max_abs_err);
+                all_ok = false;
+            }
+        }
+        std::printf("Correctness: %s\n", all_ok ? "PASSED" : "FAILED");
+        rc = all_ok ? 0 : 1;
+    }
+    if (!a.symmetric) {
+        for (int i = 0; i < W; ++i) {
+            cudaSetDevice(comm->device_of(i));
+            cudaFree(send[i]);
+            cudaFree(recv[i]);
+        }
+    }
+    comm.reset();
+    return rc;
+}

@@ -129,6 +129,8 @@ def _rank_main(rank, world, port, q, scenario):
                 # This rank stops taking part (its process stays alive until the others are done, so
                 # its heap stays mapped); the others' next collective must time out, not hang.
                 q.put((rank, True, info))
+                q.close()
+                q.join_thread()
                 time.sleep(8)
                 os._exit(0)
             comm.all_reduce(x, mode="flash")
@@ -138,6 +140,8 @@ def _rank_main(rank, world, port, q, scenario):
             except Exception as e:  # noqa: BLE001
                 ok &= "waiting for rank" in str(e)
             q.put((rank, bool(ok), info))
+            q.close()
+            q.join_thread()
             os._exit(0)  # the communicator cannot be closed collectively any more
         comm.close()
         q.put((rank, bool(ok), info))
