@@ -94,6 +94,17 @@ int main(int argc, char** argv) {
             CK(cudaEventElapsedTime(&ms, ev[c], ev[c + 1]));
             per[c] = ms * 1e3;
         }
+        // Average from a second batch with one event pair (see benchmark_yali.cu).
+        CK(comm.barrier());
+        cudaEvent_t b0, b1;
+        CK(cudaEventCreate(&b0));
+        CK(cudaEventCreate(&b1));
+        CK(cudaEventRecord(b0, st));
+        for (int c = 0; c < a.calls; ++c) call();
+        CK(cudaEventRecord(b1, st));
+        CK(comm.sync());
+        CK(cudaEventElapsedTime(&ms, b0, b1));
+        total_us = ms * 1e3;
     } else {
         auto t0 = std::chrono::steady_clock::now();
         for (int c = 0; c < a.calls; ++c) {

@@ -27,9 +27,10 @@
  * library routine is called, on the first call or later.
  *
  * First call on a device: looks up the device address of the scratch array
- * (cudaGetSymbolAddress) and clears its flag words on `stream`; that set-up is done
- * once per device, with that device current.  Make this first call before you start
- * capturing a stream.
+ * (cudaGetSymbolAddress); that set-up is done once per device, with that device
+ * current.  The flag words of the array are cleared on `stream` on that first call
+ * and again whenever `world` differs from the previous call on the device.  Make the
+ * first call before you start capturing a stream.
  *
  * Sharing: all calls on a device use the same scratch array, and the array keeps
  * what the last call left there.  Calls are safe one after another in one stream (or

@@ -400,15 +400,9 @@ Result Communicator::Collective(const void* const* send, void* const* recv, uint
         ep.hidden = opt.hidden;
     }
 
-    uint32_t epoch = 0, seq_base = 0;
-    switch (plan.variant) {
-        case Variant::Flash: epoch = ++flash_epoch_; break;
-        case Variant::Stream:
-            seq_base = stream_seq_;
-            stream_seq_ += plan.max_iters;
-            break;
-        default: epoch = TakeBarrierEpochs(2); break;
-    }
+    // Call numbers (one-shot epoch, ring sequence base, barrier epoch) live in each rank's heap
+    // and are advanced by the kernels; the host keeps no per-call state.
+    const uint32_t epoch = 0, seq_base = 0;
     plan.flags |= extra_flags;
     for (int i = 0; i < nlocal(); ++i) {
         CollArgs& a = args[i];

@@ -22,7 +22,16 @@ constexpr int kMaxLanes = 256;       // lanes (CTAs) of the two-shot ring kernel
 constexpr int kBarSlots = 1024;      // per-CTA cross-rank barriers (NVLS and fused kernels)
 constexpr int kGemmRowBlocks = 256;  // arrival counters of the fused GEMM, one per 128-row block
 
-constexpr uint32_t kFlashFlagOff = 0;                                        // [kMaxFlashCtas][kMaxRanks]
+// Call counters of this rank, advanced by the kernels themselves (the last CTA of a launch
+// bumps them), so a launch carries no per-call number and can be replayed from a CUDA graph.
+constexpr uint32_t kCallFlashEpoch = 0;   // one-shot calls so far
+constexpr uint32_t kCallStreamSeq = 1;    // ring sequence numbers consumed so far
+constexpr uint32_t kCallBarEpoch = 2;     // per-CTA barrier epochs consumed so far
+constexpr uint32_t kCallGemmEpoch = 3;    // fused GEMM calls so far
+constexpr uint32_t kCallGemmCnt = 4;      // arrivals (per source) this rank has been promised so far
+constexpr uint32_t kCallGemmDone = 8;     // [kMaxRanks] rows each owner has been asked to deliver so far
+constexpr uint32_t kCallDoneCtas = 16;    // [4] CTAs of the running launch that have finished, per kernel kind
+constexpr uint32_t kFlashFlagOff = 32;                                       // [kMaxFlashCtas][kMaxRanks]
 constexpr uint32_t kRsSeqOff = kFlashFlagOff + kMaxFlashCtas * kMaxRanks;    // [kMaxLanes][kMaxRanks]
 constexpr uint32_t kAgSeqOff = kRsSeqOff + kMaxLanes * kMaxRanks;            // [kMaxLanes][kMaxRanks]
 constexpr uint32_t kCreditOff = kAgSeqOff + kMaxLanes * kMaxRanks;           // [kMaxLanes][kMaxRanks]

@@ -85,6 +85,34 @@ __device__ __forceinline__ bool cta_barrier_all_ranks(const CommView& cv, uint32
     return wait_peers(cv, kBarOff + cta * kMaxRanks, epoch, deadline_ns, kSiteBarrier, cta, s_abort);
 }
 
+// Reads one of this rank's call counters (layout.h, kCall*) for the whole CTA.  The value was
+// written by the last CTA of the previous launch of this kind, which stream order makes visible.
+// Contains a CTA barrier.
+__device__ __forceinline__ uint32_t load_call_word(const CommView& cv, uint32_t word, uint32_t* s_slot) {
+    if (threadIdx.x == 0) *s_slot = *reinterpret_cast<volatile uint32_t*>(flag_word(cv, cv.rank, word));
+    __syncthreads();
+    return *s_slot;
+}
+
+// Every CTA that finished its part of the call normally checks out here; the last one advances
+// the call counter by `inc` for the next launch.  `kind` selects the check-out word.
+__device__ __forceinline__ bool check_out_last(const CommView& cv, uint32_t kind, uint32_t nctas) {
+    // thread 0 only
+    uint32_t* done = flag_word(cv, cv.rank, kCallDoneCtas + kind);
+    __threadfence();
+    if (atomicAdd(done, 1u) != nctas - 1) return false;
+    *reinterpret_cast<volatile uint32_t*>(done) = 0u;
+    return true;
+}
+__device__ __forceinline__ void advance_call_word(const CommView& cv, uint32_t word, uint32_t inc) {
+    volatile uint32_t* w = flag_word(cv, cv.rank, word);
+    *w = *w + inc;
+}
+__device__ __forceinline__ void finish_call(const CommView& cv, uint32_t kind, uint32_t word, uint32_t inc,
+                                            uint32_t nctas) {
+    if (threadIdx.x == 0 && check_out_last(cv, kind, nctas)) advance_call_word(cv, word, inc);
+}
+
 // Block-wide sum of one float per thread (all threads get the result).
 __device__ __forceinline__ float block_sum(float v, float* s_red /* >= 32 floats */) {
 #pragma unroll

@@ -8,7 +8,9 @@
 // ever talks to CTA c of the other ranks, so there is no grid-wide barrier, the
 // send buffer may equal the receive buffer, and user buffers never have to be
 // peer-mapped.  Staging alternates between two parities per call so that a peer
-// may start call k+1 while this rank still reads call k.
+// may start call k+1 while this rank still reads call k.  The call number lives in the
+// rank's heap and is advanced by the last CTA of each launch, so launches carry no per-call
+// state and can be replayed from a CUDA graph.
 //
 // Parity: yali::FlashKernel (src/all_reduce/flash.cuh:42-184) is the 2-GPU
 // counterpart: it pulls the peer's buffer with cp.async (sync loads on sm_100)
@@ -81,9 +83,11 @@ __device__ __forceinline__ void flash_body(const CollArgs& a, uint32_t cta) {
     const int W = world_of<WORLD>(cv), r = cv.rank;
     const int tid = threadIdx.x, nt = blockDim.x;
     __shared__ int s_abort;
+    __shared__ uint32_t s_epoch;
     if (tid == 0) s_abort = 0;
     const uint64_t deadline = ptx::globaltimer() + cv.timeout_ns;
-    const uint32_t parity = a.epoch & 1u;
+    const uint32_t epoch = load_call_word(cv, kCallFlashEpoch, &s_epoch) + 1;  // this call's number
+    const uint32_t parity = epoch & 1u;
 
     // Slice of this CTA: vectors [vb, ve); the last CTA also takes the scalar tail [tb, te).
     const uint64_t nvec = (a.flags & kFlagVecOk) ? a.count / VEC : 0;
@@ -101,8 +105,8 @@ __device__ __forceinline__ void flash_body(const CollArgs& a, uint32_t cta) {
 
     push_slice<Tin, WORLD>(a, parity, vb, ve, tb, te);
     __syncthreads();
-    signal_peers(cv, kFlashFlagOff + cta * kMaxRanks, a.epoch);
-    if (!wait_peers(cv, kFlashFlagOff + cta * kMaxRanks, a.epoch, deadline, kSiteFlashArrive, cta, &s_abort)) return;
+    signal_peers(cv, kFlashFlagOff + cta * kMaxRanks, epoch);
+    if (!wait_peers(cv, kFlashFlagOff + cta * kMaxRanks, epoch, deadline, kSiteFlashArrive, cta, &s_abort)) return;
 
     // Sum in rank order; own contribution comes from the send buffer itself.
     constexpr int kMaxW = WORLD ? WORLD : kMaxRanks;
@@ -159,6 +163,7 @@ __device__ __forceinline__ void flash_body(const CollArgs& a, uint32_t cta) {
             if (q < W) s += to_f32<Tin>(__ldcg(reinterpret_cast<const Tin*>(in[q]) + e));
         out[e] = from_f32<Tout>(epi(s));
     }
+    finish_call(cv, 0, kCallFlashEpoch, 1, a.ctas);
 }
 
 // One-shot all-reduce fused with residual-add + RMSNorm.  The message is
@@ -174,9 +179,11 @@ __device__ __forceinline__ void flash_rmsnorm_body(const CollArgs& a, uint32_t c
     const int tid = threadIdx.x, nt = blockDim.x;
     __shared__ int s_abort;
     __shared__ float s_red[32];
+    __shared__ uint32_t s_epoch;
     if (tid == 0) s_abort = 0;
     const uint64_t deadline = ptx::globaltimer() + cv.timeout_ns;
-    const uint32_t parity = a.epoch & 1u;
+    const uint32_t epoch = load_call_word(cv, kCallFlashEpoch, &s_epoch) + 1;  // this call's number
+    const uint32_t parity = epoch & 1u;
 
     const uint32_t H = a.ep.hidden;
     const uint32_t vec_per_row = H / VEC;
@@ -186,8 +193,8 @@ __device__ __forceinline__ void flash_rmsnorm_body(const CollArgs& a, uint32_t c
 
     push_slice<T, WORLD>(a, parity, rb * vec_per_row, re * vec_per_row, 0, 0);
     __syncthreads();
-    signal_peers(cv, kFlashFlagOff + cta * kMaxRanks, a.epoch);
-    if (!wait_peers(cv, kFlashFlagOff + cta * kMaxRanks, a.epoch, deadline, kSiteFlashArrive, cta, &s_abort)) return;
+    signal_peers(cv, kFlashFlagOff + cta * kMaxRanks, epoch);
+    if (!wait_peers(cv, kFlashFlagOff + cta * kMaxRanks, epoch, deadline, kSiteFlashArrive, cta, &s_abort)) return;
 
     constexpr int kMaxW = WORLD ? WORLD : kMaxRanks;
     const char* in[kMaxW];
@@ -236,6 +243,7 @@ __device__ __forceinline__ void flash_rmsnorm_body(const CollArgs& a, uint32_t c
             }
         }
     }
+    finish_call(cv, 0, kCallFlashEpoch, 1, a.ctas);
 }
 
 template <typename Tin, typename Tout, int WORLD>

@@ -82,7 +82,16 @@ __device__ __forceinline__ void gemm_ar_body(const GemmArArgs& a, const CUtensor
     const int W = cv.world, r = cv.rank;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint64_t deadline = ptx::globaltimer() + cv.timeout_ns;
-    const uint32_t parity = a.epoch & 1u;
+    // Call number and counter targets come from this rank's call words (advanced by the last
+    // CTA of the previous launch), so the launch itself carries no per-call state.
+    __shared__ uint32_t s_call[2 + kMaxRanks];
+    if (tid < 2 + W) {
+        const uint32_t word = tid == 0 ? kCallGemmEpoch : (tid == 1 ? kCallGemmCnt : kCallGemmDone + (tid - 2));
+        s_call[tid] = *reinterpret_cast<volatile uint32_t*>(flag_word(cv, r, word));
+    }
+    __syncthreads();
+    const uint32_t parity = (s_call[0] + 1u) & 1u;
+    const uint32_t cnt_wanted = s_call[1] + a.cnt_inc;
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
     if (tid == 0) {
@@ -227,8 +236,8 @@ __device__ __forceinline__ void gemm_ar_body(const GemmArArgs& a, const CUtensor
     if (my_rows > 0) {
         if (tid < W) {
             uint32_t seen;
-            if (!ptx::wait_flag_reached(flag_word(cv, r, kGemmCntOff + tid), a.cnt_wanted, deadline, &seen)) {
-                report_timeout(cv, kSiteGemmPartials, tid, cta, a.cnt_wanted, seen);
+            if (!ptx::wait_flag_reached(flag_word(cv, r, kGemmCntOff + tid), cnt_wanted, deadline, &seen)) {
+                report_timeout(cv, kSiteGemmPartials, tid, cta, cnt_wanted, seen);
                 s_abort = 1;
             }
         }
@@ -307,10 +316,19 @@ __device__ __forceinline__ void gemm_ar_body(const GemmArArgs& a, const CUtensor
     if (!a.oneshot && cta == 0) {
         if (tid < W) {
             uint32_t seen;
-            if (!ptx::wait_flag_reached(flag_word(cv, r, kGemmDoneOff + tid), a.done_wanted[tid], deadline, &seen)) {
-                report_timeout(cv, kSiteGemmDone, tid, cta, a.done_wanted[tid], seen);
+            const uint32_t want = s_call[2 + tid] + a.done_inc[tid];
+            if (!ptx::wait_flag_reached(flag_word(cv, r, kGemmDoneOff + tid), want, deadline, &seen)) {
+                report_timeout(cv, kSiteGemmDone, tid, cta, want, seen);
+                s_abort = 1;
             }
         }
+        __syncthreads();
+        if (s_abort) return;
+    }
+    if (tid == 0 && check_out_last(cv, 3, nctas)) {
+        advance_call_word(cv, kCallGemmEpoch, 1);
+        advance_call_word(cv, kCallGemmCnt, a.cnt_inc);
+        for (int q = 0; q < W; ++q) advance_call_word(cv, kCallGemmDone + q, a.done_inc[q]);
     }
 }
 

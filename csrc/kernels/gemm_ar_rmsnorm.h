@@ -27,9 +27,8 @@ struct alignas(64) GemmArArgs {
     uint32_t T, N, K;
     uint32_t rows_per_owner;  // two-shot: rows normalised by each rank
     uint32_t oneshot;         // 1: every rank receives all partial rows and normalises all of them
-    uint32_t epoch;           // parity selects the landing-zone half
-    uint32_t cnt_wanted;      // arrival counter value (per source) at which this rank's partials are complete
-    uint32_t done_wanted[kMaxRanks];  // per owner: delivered-rows counter value at which this rank's output is complete
+    uint32_t cnt_inc;         // arrivals per source that complete this rank's partial rows in this call
+    uint32_t done_inc[kMaxRanks];  // per owner: rows it delivers to every rank's output in this call
     float eps;
 };
 

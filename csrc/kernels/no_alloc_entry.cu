@@ -25,7 +25,7 @@ static_assert((yali::kFlashFlagOff + yali::kMaxFlashCtas * yali::kMaxRanks) * 4u
 constexpr int kMaxDevices = 64;
 struct PerDevice {
     unsigned char* base = nullptr;  // device address of g_no_alloc_scratch on this device
-    uint32_t epoch = 0;             // one-shot epoch of the last call
+    int world = 0;                  // group size of the last call (the ranks' call counters must agree)
     int sms = 0;
 };
 PerDevice g_dev[kMaxDevices];
@@ -73,14 +73,19 @@ extern "C" cudaError_t yaliAllReduceLocalNoAlloc(const void* const* send, void* 
         if (e != cudaSuccess) return Refuse(e, "cudaGetSymbolAddress of the scratch array failed");
         e = cudaDeviceGetAttribute(&pd.sms, cudaDevAttrMultiProcessorCount, dev);
         if (e != cudaSuccess) return Refuse(e, "cudaDeviceGetAttribute failed");
-        // Flags must start at zero; staging needs no clearing (it is written before it is read).
+        pd.base = static_cast<unsigned char*>(p);
+        pd.world = 0;
+    }
+    if (pd.world != world) {
+        // Flags and the ranks' call counters must start at zero, and all ranks of a group must
+        // have seen the same calls: clear them on first use and whenever the group size changes
+        // (stream-ordered, like the kernel).  Staging needs no clearing: it is written before it
+        // is read.
         for (int r = 0; r < YALI_NO_ALLOC_MAX_WORLD; ++r) {
-            e = cudaMemsetAsync(static_cast<unsigned char*>(p) + static_cast<size_t>(r) * YALI_NO_ALLOC_RANK_BYTES, 0,
-                                128u * 1024u, stream);
+            e = cudaMemsetAsync(pd.base + static_cast<size_t>(r) * YALI_NO_ALLOC_RANK_BYTES, 0, 128u * 1024u, stream);
             if (e != cudaSuccess) return Refuse(e, "clearing the flag words failed");
         }
-        pd.base = static_cast<unsigned char*>(p);
-        pd.epoch = 0;
+        pd.world = world;
     }
 
     const void* fn = FlashKernelFor(dt, dt, kEpiIdentity, world, /*emu=*/true);
@@ -92,7 +97,6 @@ extern "C" cudaError_t yaliAllReduceLocalNoAlloc(const void* const* send, void* 
     if (ctas > max_ctas) ctas = max_ctas;
     if (ctas < 1) ctas = 1;
 
-    const uint32_t epoch = ++pd.epoch;
     EmuArgs args;
     std::memset(&args, 0, sizeof(args));
     for (int r = 0; r < world; ++r) {
@@ -111,7 +115,6 @@ extern "C" cudaError_t yaliAllReduceLocalNoAlloc(const void* const* send, void* 
         a.send = send[r];
         a.recv = recv[r];
         a.count = count;
-        a.epoch = epoch;
         a.ctas = ctas;
         const bool aligned = ((reinterpret_cast<uintptr_t>(send[r]) | reinterpret_cast<uintptr_t>(recv[r])) & 15u) == 0;
         a.flags = aligned ? kFlagVecOk : 0u;

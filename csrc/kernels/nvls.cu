@@ -75,12 +75,13 @@ __global__ void __launch_bounds__(kNvlsThreads, 2) nvls_kernel(const __grid_cons
     const int tid = threadIdx.x, nt = blockDim.x;
     const uint32_t cta = blockIdx.x, nctas = a.ctas;
     __shared__ int s_abort;
+    __shared__ uint32_t s_epoch;
     if (tid == 0) s_abort = 0;
-    __syncthreads();
+    const uint32_t epoch = load_call_word(cv, kCallBarEpoch, &s_epoch);  // barrier epochs used before this call
     const uint64_t deadline = ptx::globaltimer() + cv.timeout_ns;
 
     const bool symmetric = (a.flags & kFlagSymmetric) != 0;
-    const uint32_t parity = (a.epoch >> 1) & 1u;
+    const uint32_t parity = (epoch >> 1) & 1u;
     const uint64_t total_vec = a.count / VEC;
     const float scale = a.ep.scale;
     const bool scaled = scale != 1.0f;
@@ -97,7 +98,7 @@ __global__ void __launch_bounds__(kNvlsThreads, 2) nvls_kernel(const __grid_cons
         const uint64_t per = (total_vec + nctas - 1) / nctas;
         const uint64_t vb = min(total_vec, cta * per), ve = min(total_vec, vb + per);
         if (!symmetric) copy16(heap + stage_off, send, vb, ve);
-        if (!cta_barrier_all_ranks(cv, cta, a.epoch + 1, deadline, &s_abort)) return;
+        if (!cta_barrier_all_ranks(cv, cta, epoch + 1, deadline, &s_abort)) return;
         const char* mc_in = cv.mc_heap + in_off;
         uint64_t v = vb + tid;
         for (; v + 3ull * nt < ve; v += 4ull * nt) {
@@ -115,7 +116,7 @@ __global__ void __launch_bounds__(kNvlsThreads, 2) nvls_kernel(const __grid_cons
         // kernel, so nobody leaves before everybody has read.  Staged input sits in
         // the half of the staging region that is not touched again before every
         // rank has passed the first barrier of the next call.
-        if (symmetric) cta_barrier_all_ranks(cv, cta, a.epoch + 2, deadline, &s_abort);
+        if (symmetric) cta_barrier_all_ranks(cv, cta, epoch + 2, deadline, &s_abort);
     } else {
         const uint64_t shard_vec = a.shard_elems / VEC;
         const uint64_t per = (shard_vec + nctas - 1) / nctas;
@@ -133,7 +134,7 @@ __global__ void __launch_bounds__(kNvlsThreads, 2) nvls_kernel(const __grid_cons
                 copy16(heap + stage_off, send, vb, ve);
             }
         }
-        if (!cta_barrier_all_ranks(cv, cta, a.epoch + 1, deadline, &s_abort)) return;
+        if (!cta_barrier_all_ranks(cv, cta, epoch + 1, deadline, &s_abort)) return;
         {
             uint64_t vb, ve;
             slice(r, &vb, &ve);
@@ -153,7 +154,7 @@ __global__ void __launch_bounds__(kNvlsThreads, 2) nvls_kernel(const __grid_cons
                 ptx::multimem_st_v4(mc_out + v * 16, scaled ? scale16<T>(x, scale) : x);
             }
         }
-        if (!cta_barrier_all_ranks(cv, cta, a.epoch + 2, deadline, &s_abort)) return;
+        if (!cta_barrier_all_ranks(cv, cta, epoch + 2, deadline, &s_abort)) return;
         if (!symmetric) {
             for (int k = 0; k < W; ++k) {
                 uint64_t vb, ve;
@@ -162,6 +163,7 @@ __global__ void __launch_bounds__(kNvlsThreads, 2) nvls_kernel(const __grid_cons
             }
         }
     }
+    finish_call(cv, 2, kCallBarEpoch, 2, nctas);
 }
 
 template <typename T>

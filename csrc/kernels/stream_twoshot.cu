@@ -68,8 +68,9 @@ __device__ __forceinline__ void stream_body(const CollArgs& a, uint32_t lane) {
     const int W = world_of<WORLD>(cv), r = cv.rank;
     const int tid = threadIdx.x, nt = blockDim.x;
     __shared__ int s_abort;
+    __shared__ uint32_t s_seq;
     if (tid == 0) s_abort = 0;
-    __syncthreads();
+    const uint32_t seq_base = load_call_word(cv, kCallStreamSeq, &s_seq);  // sequence numbers used before this call
     const uint64_t deadline = ptx::globaltimer() + cv.timeout_ns;
 
     const bool vec = (a.flags & kFlagVecOk) != 0;
@@ -105,7 +106,7 @@ __device__ __forceinline__ void stream_body(const CollArgs& a, uint32_t lane) {
         if (step < n_it && !ag_only) {
             const uint32_t i = step, slot = i % kRingCap;
             if (i >= kRingCap) {
-                if (!wait_peers(cv, cr_word, a.seq_base + (i - kRingCap) + 1, deadline, kSiteStreamCredit, lane,
+                if (!wait_peers(cv, cr_word, seq_base + (i - kRingCap) + 1, deadline, kSiteStreamCredit, lane,
                                 &s_abort))
                     return;
             }
@@ -120,15 +121,15 @@ __device__ __forceinline__ void stream_body(const CollArgs& a, uint32_t lane) {
                 }
             }
             __syncthreads();
-            signal_peers(cv, rs_word, a.seq_base + i + 1);
+            signal_peers(cv, rs_word, seq_base + i + 1);
         }
         // ---------------- stage B: reduce iteration `step-1`, all-gather push
         if (step >= 1 && step - 1 < n_it) {
             const uint32_t i = step - 1, slot = i % kRingCap;
             if (!ag_only) {
-                if (!wait_peers(cv, rs_word, a.seq_base + i + 1, deadline, kSiteStreamRs, lane, &s_abort)) return;
+                if (!wait_peers(cv, rs_word, seq_base + i + 1, deadline, kSiteStreamRs, lane, &s_abort)) return;
             } else if (i >= kRingCap && !direct) {
-                if (!wait_peers(cv, cr_word, a.seq_base + (i - kRingCap) + 1, deadline, kSiteStreamCredit, lane,
+                if (!wait_peers(cv, cr_word, seq_base + (i - kRingCap) + 1, deadline, kSiteStreamCredit, lane,
                                 &s_abort))
                     return;
             }
@@ -196,13 +197,13 @@ __device__ __forceinline__ void stream_body(const CollArgs& a, uint32_t lane) {
                     if (k < W && !rs_only) out_peer[k][e] = o;
             }
             __syncthreads();
-            if (!rs_only) signal_peers(cv, ag_word, a.seq_base + i + 1);
-            if ((direct || rs_only) && !ag_only) signal_peers(cv, cr_word, a.seq_base + i + 1);
+            if (!rs_only) signal_peers(cv, ag_word, seq_base + i + 1);
+            if ((direct || rs_only) && !ag_only) signal_peers(cv, cr_word, seq_base + i + 1);
         }
         // ---------------- stage C: all-gather consume of iteration `step-2`
         if (!direct && !rs_only && step >= 2 && step - 2 < n_it) {
             const uint32_t i = step - 2, slot = i % kRingCap;
-            if (!wait_peers(cv, ag_word, a.seq_base + i + 1, deadline, kSiteStreamAg, lane, &s_abort)) return;
+            if (!wait_peers(cv, ag_word, seq_base + i + 1, deadline, kSiteStreamAg, lane, &s_abort)) return;
 #pragma unroll
             for (int k = 1; k < kMaxW; ++k) {
                 if (k < W) {
@@ -215,20 +216,22 @@ __device__ __forceinline__ void stream_body(const CollArgs& a, uint32_t lane) {
                 }
             }
             __syncthreads();
-            signal_peers(cv, cr_word, a.seq_base + i + 1);
+            signal_peers(cv, cr_word, seq_base + i + 1);
         }
     }
     // Direct all-gather: peers wrote into this rank's output; leave only when all of it landed.
     if (direct && !rs_only && n_it > 0) {
-        if (!wait_peers(cv, ag_word, a.seq_base + n_it, deadline, kSiteStreamDrain, lane, &s_abort)) return;
+        if (!wait_peers(cv, ag_word, seq_base + n_it, deadline, kSiteStreamDrain, lane, &s_abort)) return;
     }
     // In the full all-reduce a rank can only finish after every peer has read all slots this
     // rank filled (its own completion depends on their results).  The half collectives lack
     // that dependency, so they drain the credits before leaving; the next call may then
     // reuse the slots at once.
     if ((rs_only || (ag_only && !direct)) && n_it > 0) {
-        if (!wait_peers(cv, cr_word, a.seq_base + n_it, deadline, kSiteStreamDrain, lane, &s_abort)) return;
+        if (!wait_peers(cv, cr_word, seq_base + n_it, deadline, kSiteStreamDrain, lane, &s_abort)) return;
     }
+    // The next call continues after the largest sequence number any lane can have used.
+    finish_call(cv, 1, kCallStreamSeq, static_cast<uint32_t>((n_pieces + nlanes - 1) / nlanes), nlanes);
 }
 
 template <typename Tin, typename Tout, int WORLD>

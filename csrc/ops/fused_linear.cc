@@ -106,13 +106,6 @@ Result FusedLinearAllReduceRmsNorm(Communicator& comm, const FusedLinearDesc* de
             rows_of[q] = hi - lo;
         }
     }
-    Communicator::GemmCounters& gc = comm.gemm_counters();
-    for (int q = 0; q < W; ++q) {
-        gc.cnt[q] += arrivals[q];
-        gc.done[q] += rows_of[q];
-    }
-    const uint32_t epoch = comm.TakeGemmEpoch();
-
     const void* fn = GemmArKernel(comm.emulated());
     const uint32_t smem = GemmArSmemBytes();
     static bool attr_set[2] = {false, false};
@@ -126,9 +119,14 @@ Result FusedLinearAllReduceRmsNorm(Communicator& comm, const FusedLinearDesc* de
         }
         attr_set[comm.emulated() ? 1 : 0] = true;
     }
-    int per_sm = 0, sms = 0;
-    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fn, kGemmThreads, smem);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, comm.device_of(0));
+    // Resident CTAs per GPU (queried once per kernel flavour; all GPUs of a group are alike).
+    static int cached_per_sm[2] = {0, 0}, cached_sms[2] = {0, 0};
+    const int flavour = comm.emulated() ? 1 : 0;
+    if (cached_sms[flavour] == 0) {
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&cached_per_sm[flavour], fn, kGemmThreads, smem);
+        cudaDeviceGetAttribute(&cached_sms[flavour], cudaDevAttrMultiProcessorCount, comm.device_of(0));
+    }
+    const int per_sm = cached_per_sm[flavour], sms = cached_sms[flavour];
     uint32_t resident = static_cast<uint32_t>(std::max(1, per_sm) * std::max(1, sms));
     if (comm.emulated()) resident = std::max<uint32_t>(1, resident / W);
     const uint32_t work = std::max<uint32_t>(ntm * ntn, oneshot ? T : Rs);
@@ -170,9 +168,8 @@ Result FusedLinearAllReduceRmsNorm(Communicator& comm, const FusedLinearDesc* de
         a.K = K;
         a.rows_per_owner = Rs;
         a.oneshot = oneshot ? 1u : 0u;
-        a.epoch = epoch;
-        a.cnt_wanted = gc.cnt[rank];
-        for (int q = 0; q < W; ++q) a.done_wanted[q] = gc.done[q];
+        a.cnt_inc = arrivals[rank];
+        for (int q = 0; q < W; ++q) a.done_inc[q] = rows_of[q];
         a.eps = opt.eps;
     }
     if (comm.emulated()) {

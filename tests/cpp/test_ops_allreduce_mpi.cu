@@ -27,6 +27,8 @@ static bool Run(MPIComm& comm, size_t n, Dtype dt, bool symmetric, bool stable) 
     cudaDeviceSynchronize();
     bool ok = allreduce(comm, send, recv, n, nullptr, stable) == cudaSuccess;
     ok = ok && ValidateRandomResult(recv, n, dt, dt, kDistUniformPm1, 1234, comm.world_size(), 1.0f, nullptr);
+    if (!ok) std::printf("rank %d: case n=%zu dtype=%s symmetric=%d FAILED (%s)\n", comm.rank(), n, DtypeName(dt),
+                         symmetric ? 1 : 0, comm.impl()->last_error().c_str());
     if (!symmetric) {
         cudaFree(send);
         cudaFree(recv);
@@ -35,7 +37,9 @@ static bool Run(MPIComm& comm, size_t n, Dtype dt, bool symmetric, bool stable) 
 }
 
 int main(int argc, char** argv) {
-    MPIComm comm(&argc, &argv);
+    CommOptions copt;
+    copt.heap_bytes = 2ull << 30;  // room for the 128 MiB symmetric cases
+    MPIComm comm(&argc, &argv, copt);
     if (!comm.ok()) return 2;
     int ok = 1;
     ok &= Run<float>(comm, 1024, Dtype::FP32, false, false);

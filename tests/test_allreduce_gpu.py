@@ -239,3 +239,34 @@ def test_errors_are_clean(comm):
     outs = comm.all_reduce(xs)
     comm.sync()
     check(comm, outs, torch.float32)
+
+
+def test_cuda_graph_replay(comm):
+    """Launches carry no per-call number (the kernels keep their call counters on the device), so a
+    captured sequence of collectives can be replayed."""
+    n = 50000
+    xs = make_inputs(comm, n, torch.float32)
+    ys = make_inputs(comm, 4 * n, torch.bfloat16, NORMAL, seed=5)
+    out_a = [torch.empty_like(x) for x in xs]
+    out_b = [torch.empty_like(y) for y in ys]
+    out_c = [torch.empty_like(x) for x in xs]
+    comm.all_reduce(xs, out_a, mode="flash")  # warm-up outside the capture
+    comm.all_reduce(ys, out_b, mode="stream")
+    comm.sync()
+    graph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            comm.all_reduce(xs, out_a, mode="flash")
+            comm.all_reduce(ys, out_b, mode="stream")
+            comm.all_reduce(xs, out_c, mode="flash", scale=0.5)
+    for _ in range(6):
+        for o in out_a + out_b + out_c:
+            o.zero_()
+        graph.replay()
+        comm.all_reduce(xs, mode="flash")  # eager calls may be mixed with replays
+    torch.cuda.synchronize()
+    comm.check()
+    check(comm, out_a, torch.float32)
+    check(comm, out_b, torch.bfloat16, NORMAL, seed=5)
+    check(comm, out_c, torch.float32, scale=0.5)
