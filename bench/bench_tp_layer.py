@@ -65,6 +65,8 @@ def main():
     ap.add_argument("--tokens", default="1,16,128,2048")
     ap.add_argument("--hidden", type=int, default=4096)
     ap.add_argument("--iters", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--arms", default="", help="comma list to restrict the arms")
     ap.add_argument("--out", default="")
     args = ap.parse_args()
     emu = args.emulate > 0
@@ -112,7 +114,9 @@ def main():
         bytes_two = 2.0 * (W - 1) / W * T * N * 2
         bytes_one = (W - 1) * T * N * 2.0
         for label, fn in arms.items():
-            us = timed(comm, fn, iters)
+            if args.arms and label not in args.arms.split(","):
+                continue
+            us = timed(comm, fn, iters, args.warmup)
             link_bytes = 0.0 if emu else (bytes_one if label == "fused_oneshot" else bytes_two)
             roof = max(t_gemm, link_bytes / (LINK_GBS * 1e9) * 1e6)
             row = {"T": T, "world": W, "arm": label, "us": round(us, 2), "roofline_us": round(roof, 3),
