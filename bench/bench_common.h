@@ -18,10 +18,13 @@
 
 namespace bench {
 
-enum class TimingMode { Throughput, Latency, CudaEvents };
+enum class TimingMode { Throughput, Latency, CudaEvents, Graph };
 
 inline const char* TimingModeName(TimingMode m) {
-    return m == TimingMode::CudaEvents ? "cuda-events" : (m == TimingMode::Latency ? "latency" : "throughput");
+    return m == TimingMode::CudaEvents ? "cuda-events"
+           : m == TimingMode::Latency  ? "latency"
+           : m == TimingMode::Graph    ? "graph"
+                                       : "throughput";
 }
 
 struct Args {
@@ -56,6 +59,7 @@ inline Args Parse(int argc, char** argv) {
     if (argc > 6) {
         if (!std::strcmp(argv[6], "latency")) a.timing = TimingMode::Latency;
         else if (!std::strcmp(argv[6], "throughput")) a.timing = TimingMode::Throughput;
+        else if (!std::strcmp(argv[6], "graph")) a.timing = TimingMode::Graph;
         else a.timing = TimingMode::CudaEvents;
     }
     if (argc > 7) yali::ParseDtype(argv[7], &a.dtype);
@@ -72,7 +76,8 @@ inline void Usage(const char* prog, const char* what) {
     std::printf("  verify     1: check every element against the fp64 sum of the seeded inputs\n");
     std::printf("  mode       auto | flash | stream | nvls\n");
     std::printf("  lanes      CTAs (flash, nvls) or lanes (stream) per rank, 0 = tuned\n");
-    std::printf("  timing     cuda-events (device time, per-call percentiles) | throughput | latency\n");
+    std::printf("  timing     cuda-events (device time, per-call percentiles) | throughput | latency |\n");
+    std::printf("             graph (all calls captured in one CUDA graph, device time of one replay; *_mpi only)\n");
     std::printf("  dtype      fp32 | fp16 | bf16 (or YALI_DTYPE)\n");
     std::printf("  gpus       ranks, one GPU each (default 2, or YALI_GPUS)\n");
     std::printf("  symmetric  1: buffers from the communicator's symmetric heap (default), 0: cudaMalloc\n");

@@ -105,6 +105,29 @@ int main(int argc, char** argv) {
         CK(comm.sync());
         CK(cudaEventElapsedTime(&ms, b0, b1));
         total_us = ms * 1e3;
+    } else if (a.timing == bench::TimingMode::Graph) {
+        // All calls in one CUDA graph: no host launch work between the kernels.  Two replays, the
+        // second one is timed.
+        cudaGraph_t graph;
+        cudaGraphExec_t exec;
+        CK(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
+        for (int c = 0; c < a.calls; ++c) call();
+        CK(cudaStreamEndCapture(st, &graph));
+        CK(cudaGraphInstantiate(&exec, graph, 0));
+        cudaEvent_t g0, g1;
+        CK(cudaEventCreate(&g0));
+        CK(cudaEventCreate(&g1));
+        CK(cudaGraphLaunch(exec, st));
+        CK(comm.sync());
+        CK(cudaEventRecord(g0, st));
+        CK(cudaGraphLaunch(exec, st));
+        CK(cudaEventRecord(g1, st));
+        CK(comm.sync());
+        float ms = 0;
+        CK(cudaEventElapsedTime(&ms, g0, g1));
+        total_us = ms * 1e3;
+        cudaGraphExecDestroy(exec);
+        cudaGraphDestroy(graph);
     } else {
         auto t0 = std::chrono::steady_clock::now();
         for (int c = 0; c < a.calls; ++c) {
@@ -140,7 +163,9 @@ int main(int argc, char** argv) {
         for (int o : oks) ok &= o;
     }
     if (rank == 0) {
-        bench::Stats s = a.timing == bench::TimingMode::Throughput ? bench::Stats() : bench::Summarise(per);
+        bench::Stats s = (a.timing == bench::TimingMode::Throughput || a.timing == bench::TimingMode::Graph)
+                             ? bench::Stats()
+                             : bench::Summarise(per);
         const LastCallInfo& lc = comm.impl()->last_call();
         char extra[160];
         std::snprintf(extra, sizeof(extra), "\"ctas\":%u,\"slot_bytes\":%u,\"symmetric\":%d,\"processes\":%d", lc.ctas,

@@ -6,6 +6,7 @@
 
 #include "../core/env.h"
 #include "../kernels/launch.h"
+#include "../ops/buffer_ops.h"
 #include "topology.h"
 
 namespace yali {
@@ -35,6 +36,9 @@ bool MakeHeapLayout(int world, uint64_t requested_total, uint64_t granularity, H
         l.gemm_off = off;
         l.gemm_cap = std::max<uint64_t>(4 * MiB, 16 * MiB / world);  // 2048 rows of 4096 bf16 sharded over the ranks
         off += 2ull * world * l.gemm_cap;
+        l.ll_off = off;
+        l.ll_cap = 1 * MiB;
+        off += 2ull * (world - 1) * 2 * l.ll_cap;
     }
     l.user_off = off;
     uint64_t total = requested_total ? requested_total : off + 256 * MiB;
@@ -195,6 +199,8 @@ Communicator::~Communicator() {
     heaps_.reset();
     for (Local& l : local_) {
         if (cudaSetDevice(l.device) != cudaSuccess) continue;
+        if (l.prof_start) cudaEventDestroy(l.prof_start);
+        if (l.prof_stop) cudaEventDestroy(l.prof_stop);
         if (l.status) cudaFreeHost(l.status);
         if (l.stream) cudaStreamDestroy(l.stream);
     }
@@ -290,7 +296,8 @@ Result Communicator::Launch(const Plan& plan, Dtype in, Dtype out, int epilogue,
     int threads = 0;
     switch (plan.variant) {
         case Variant::Flash:
-            fn = FlashKernelFor(in, out, epilogue, world_, emulated_);
+            fn = (plan.flags & kFlagLowLatency) ? FlashLLKernelFor(in, world_, emulated_)
+                                                : FlashKernelFor(in, out, epilogue, world_, emulated_);
             threads = kFlashThreads;
             break;
         case Variant::Stream:
@@ -332,10 +339,23 @@ Result Communicator::Launch(const Plan& plan, Dtype in, Dtype out, int epilogue,
         }
         cudaStream_t s = streams && streams[i] ? streams[i] : local_[i].stream;
         void* params[] = {&args[i]};
+        static const bool profile = env::ProfileKernels();
+        Local& l = local_[i];
+        if (profile) {
+            if (!l.prof_start) {
+                cudaEventCreate(&l.prof_start);
+                cudaEventCreate(&l.prof_stop);
+            }
+            cudaEventRecord(l.prof_start, s);
+        }
         cudaError_t ce = cudaLaunchKernel(fn, dim3(plan.ctas), dim3(threads), params, 0, s);
         if (ce != cudaSuccess) {
             (void)cudaGetLastError();
             return Fail(Result::CudaError, std::string("kernel launch failed: ") + cudaGetErrorString(ce));
+        }
+        if (profile) {
+            cudaEventRecord(l.prof_stop, s);
+            l.prof_pending = true;
         }
         last_.launches += 1;
     }
@@ -366,6 +386,7 @@ Result Communicator::Collective(const void* const* send, void* const* recv, uint
     caps.flash_cap = lay_.flash_cap;
     caps.ring_bytes = lay_.ring_bytes;
     caps.nvls_cap = lay_.nvls_cap;
+    caps.ll_cap = lay_.ll_cap;
     caps.has_multicast = has_multicast();
     caps.symmetric = symmetric;
     caps.peer_recv = peer_recv && !rs_only;
@@ -440,6 +461,28 @@ Result Communicator::Collective(const void* const* send, void* const* recv, uint
 
 Result Communicator::AllReduce(const void* const* send, void* const* recv, uint64_t count, Dtype in, Dtype out,
                                const OpOptions& opt, const cudaStream_t* streams) {
+    // The row-wise epilogue is fused into the one-shot kernel only.  A message beyond its
+    // staging capacity is reduced by the bandwidth kernels first and normalised by a local
+    // kernel afterwards (two launches per rank).
+    if (opt.epilogue == kEpiResidualRmsNorm && world_ > 1 && count * DtypeSize(in) > lay_.flash_cap && in == out &&
+        opt.hidden > 0 && count % opt.hidden == 0 && opt.weight) {
+        OpOptions plain = opt;
+        plain.epilogue = kEpiIdentity;
+        if (plain.mode == KernelMode::Flash) plain.mode = KernelMode::Auto;
+        Result r = Collective(send, recv, count, in, out, plain, streams, 0);
+        if (r != Result::Success) return r;
+        for (int i = 0; i < nlocal(); ++i) {
+            if (nlocal() > 1) cudaSetDevice(local_[i].device);
+            cudaStream_t s = streams && streams[i] ? streams[i] : local_[i].stream;
+            if (emulated_) s = streams && streams[0] ? streams[0] : local_[0].stream;
+            cudaError_t e = ResidualRmsNormInPlace(recv[i], opt.residual ? opt.residual[i] : nullptr,
+                                                   opt.residual_out ? opt.residual_out[i] : nullptr, opt.weight[i],
+                                                   count / opt.hidden, static_cast<uint32_t>(opt.hidden), opt.eps, out, s);
+            if (e != cudaSuccess) return Fail(Result::CudaError, std::string("rmsnorm kernel: ") + cudaGetErrorString(e));
+            last_.launches += 1;
+        }
+        return Result::Success;
+    }
     return Collective(send, recv, count, in, out, opt, streams, 0);
 }
 
@@ -476,6 +519,18 @@ Result Communicator::Sync(const cudaStream_t* streams) {
         }
         if (emulated_) break;  // one launch served every rank
     }
+    // YALI_PROFILE_KERNELS=1: device time of the last launch, slowest rank of this process.
+    float worst_ms = -1.f;
+    for (Local& l : local_) {
+        if (!l.prof_pending) continue;
+        l.prof_pending = false;
+        float ms = 0.f;
+        if (cudaEventElapsedTime(&ms, l.prof_start, l.prof_stop) == cudaSuccess) worst_ms = std::max(worst_ms, ms);
+        else (void)cudaGetLastError();
+    }
+    if (worst_ms >= 0.f)
+        std::fprintf(stderr, "[YALI_PROFILE] %s kernel: max_rank_ms=%.4f ctas=%u slot_bytes=%u\n",
+                     VariantName(last_.variant), worst_ms, last_.ctas, last_.slot_bytes);
     return Check();
 }
 

@@ -137,6 +137,8 @@ class Communicator {
         int rank = 0;
         int device = 0;
         cudaStream_t stream = nullptr;
+        cudaEvent_t prof_start = nullptr, prof_stop = nullptr;  // YALI_PROFILE_KERNELS=1: around the last launch
+        bool prof_pending = false;
         DeviceStatus* status = nullptr;  // pinned host memory, device-visible
     };
     struct PeerMap {  // multi-process registration of one user buffer

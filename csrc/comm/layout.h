@@ -28,6 +28,7 @@ constexpr uint32_t kCallFlashEpoch = 0;   // one-shot calls so far
 constexpr uint32_t kCallStreamSeq = 1;    // ring sequence numbers consumed so far
 constexpr uint32_t kCallBarEpoch = 2;     // per-CTA barrier epochs consumed so far
 constexpr uint32_t kCallGemmEpoch = 3;    // fused GEMM calls so far
+constexpr uint32_t kCallFlashEpochHi = 5;  // upper half of the one-shot call number (flag-in-data protocol)
 constexpr uint32_t kCallGemmCnt = 4;      // arrivals (per source) this rank has been promised so far
 constexpr uint32_t kCallGemmDone = 8;     // [kMaxRanks] rows each owner has been asked to deliver so far
 constexpr uint32_t kCallDoneCtas = 16;    // [4] CTAs of the running launch that have finished, per kernel kind
@@ -56,6 +57,8 @@ struct HeapLayout {
     uint64_t nvls_cap;
     uint64_t gemm_off;     // partial-sum landing zone of the fused GEMM: [2][world][gemm_cap]
     uint64_t gemm_cap;
+    uint64_t ll_off;       // staging of the flag-in-data one-shot protocol: [2 parities][world-1 sources][2 * ll_cap]
+    uint64_t ll_cap;       // largest message (bytes of payload) that protocol takes
     uint64_t user_off;     // symmetric allocations handed to the user
     uint64_t user_bytes;
 };
@@ -135,6 +138,7 @@ enum CollFlags : uint32_t {
     kFlagSymmetric = 1u << 2,   // NVLS: send/recv live in the heap at cv offsets (zero copy)
     kFlagReduceScatterOnly = 1u << 3,
     kFlagAllGatherOnly = 1u << 4,
+    kFlagLowLatency = 1u << 6,  // one-shot: flag-in-data protocol (no separate flag, no release fence)
     kFlagSkipRank = 1u << 5,    // this rank leaves at once (models a rank that never launched; tests of the timeouts)
 };
 

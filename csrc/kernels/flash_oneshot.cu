@@ -246,6 +246,126 @@ __device__ __forceinline__ void flash_rmsnorm_body(const CollArgs& a, uint32_t c
     finish_call(cv, 0, kCallFlashEpoch, 1, a.ctas);
 }
 
+// Flag-in-data form of the one-shot all-reduce for small messages.  Every 16-byte line
+// that crosses NVLink carries 8 bytes of payload and the 64-bit number of the call, split
+// over its two 8-byte halves {data, call_lo} {data, call_hi}.  A receiver polls the line
+// itself until both halves show this call's number, so there is no separate flag, no CTA
+// barrier and no release fence between the push and the reduction: latency is one
+// one-way trip.  Twice the bytes on the wire, so only small messages take this path.  Its
+// staging is never written by anything else, hence stale lines always show an older call.
+__device__ __forceinline__ char* ll_stage(const CommView& cv, int on_rank, int src, uint32_t parity) {
+    return cv.heap[on_rank] + cv.lay.ll_off +
+           (static_cast<uint64_t>(parity) * (cv.world - 1) + SrcSlot(src, on_rank)) * (2 * cv.lay.ll_cap);
+}
+__device__ __forceinline__ uint4 ld_volatile_v4(const void* p) {
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p)
+                 : "memory");
+    return v;
+}
+
+template <typename T, int WORLD>
+__device__ __forceinline__ void flash_ll_body(const CollArgs& a, uint32_t cta) {
+    constexpr int VEC = TypeTraits<T>::kVec;
+    constexpr int kMaxW = WORLD ? WORLD : kMaxRanks;
+    constexpr int kMaxPeers = kMaxW - 1;
+    if (a.flags & kFlagSkipRank) return;
+    const CommView& cv = a.cv;
+    const int W = world_of<WORLD>(cv), r = cv.rank;
+    const int tid = threadIdx.x, nt = blockDim.x;
+    __shared__ uint32_t s_call[2];
+    if (tid < 2)
+        s_call[tid] = *reinterpret_cast<volatile uint32_t*>(flag_word(cv, r, tid == 0 ? kCallFlashEpoch : kCallFlashEpochHi));
+    __syncthreads();
+    const uint32_t lo = s_call[0] + 1u;                       // this call's number (shared with the flagged form)
+    const uint32_t hi = (s_call[1] + (lo == 0u ? 1u : 0u)) | 0x80000000u;  // never zero: fresh memory never matches
+    const uint32_t parity = lo & 1u;
+    const uint64_t deadline = ptx::globaltimer() + cv.timeout_ns;
+
+    const uint64_t nvec = a.count / VEC;  // the planner only picks this form for whole, aligned vectors
+    const uint64_t per = (nvec + a.ctas - 1) / a.ctas;
+    const uint64_t vb = min(nvec, static_cast<uint64_t>(cta) * per), ve = min(nvec, vb + per);
+    const char* src = static_cast<const char*>(a.send);
+
+    char* dst[kMaxPeers];
+    const char* in[kMaxW];
+#pragma unroll
+    for (int k = 0; k < kMaxPeers; ++k) dst[k] = (k < W - 1) ? ll_stage(cv, (r + 1 + k) % W, r, parity) : nullptr;
+#pragma unroll
+    for (int q = 0; q < kMaxW; ++q) in[q] = (q < W && q != r) ? ll_stage(cv, r, q, parity) : nullptr;
+
+    // ---- push: payload vector v becomes lines 2v and 2v+1
+    for (uint64_t v = vb + tid; v < ve; v += nt) {
+        const uint4 x = *reinterpret_cast<const uint4*>(src + v * 16);
+        const uint4 l0 = make_uint4(x.x, lo, x.y, hi), l1 = make_uint4(x.z, lo, x.w, hi);
+#pragma unroll
+        for (int k = 0; k < kMaxPeers; ++k) {
+            if (k < W - 1) {
+                ptx::st_v4(dst[k] + v * 32, l0);
+                ptx::st_v4(dst[k] + v * 32 + 16, l1);
+            }
+        }
+    }
+    // ---- reduce: poll the peers' lines for the same vectors
+    const EpiScale epi(a.ep);
+    T* out = static_cast<T*>(a.recv);
+    bool timed_out = false;
+    for (uint64_t v = vb + tid; v < ve && !timed_out; v += nt) {
+        float f[VEC];
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) f[i] = 0.f;
+#pragma unroll
+        for (int q = 0; q < kMaxW; ++q) {
+            if (q >= W) continue;
+            if (q == r) {
+                accumulate<T>(f, *reinterpret_cast<const uint4*>(src + v * 16));
+                continue;
+            }
+            uint4 l0, l1;
+            uint32_t polls = 0;
+            for (;;) {
+                l0 = ld_volatile_v4(in[q] + v * 32);
+                l1 = ld_volatile_v4(in[q] + v * 32 + 16);
+                if (l0.y == lo && l0.w == hi && l1.y == lo && l1.w == hi) break;
+                if ((++polls & 63u) == 0u && ptx::globaltimer() > deadline) {
+                    report_timeout(cv, kSiteFlashArrive, q, cta, lo, l0.y);
+                    timed_out = true;
+                    break;
+                }
+            }
+            if (timed_out) break;
+            accumulate<T>(f, make_uint4(l0.x, l0.z, l1.x, l1.z));
+        }
+        if (timed_out) break;
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) f[i] = epi(f[i]);
+        store_lanes<T, VEC>(out + v * VEC, f);
+    }
+    if (__syncthreads_or(timed_out ? 1 : 0)) return;
+    if (tid == 0 && check_out_last(cv, 0, a.ctas)) {
+        advance_call_word(cv, kCallFlashEpoch, 1);
+        if (lo == 0u) advance_call_word(cv, kCallFlashEpochHi, 1);
+    }
+}
+
+template <typename T, int WORLD>
+__global__ void __launch_bounds__(kFlashThreads, 2) flash_ll_kernel(const __grid_constant__ CollArgs a) {
+    flash_ll_body<T, WORLD>(a, blockIdx.x);
+}
+template <typename T, int WORLD>
+__global__ void __launch_bounds__(kFlashThreads, 2) flash_ll_kernel_emu(const __grid_constant__ EmuArgs e) {
+    flash_ll_body<T, WORLD>(e.r[blockIdx.y], blockIdx.x);
+}
+template <typename T>
+const void* pick_flash_ll(int world, bool emu) {
+    switch (world) {
+        case 2: return emu ? (const void*)flash_ll_kernel_emu<T, 2> : (const void*)flash_ll_kernel<T, 2>;
+        case 4: return emu ? (const void*)flash_ll_kernel_emu<T, 4> : (const void*)flash_ll_kernel<T, 4>;
+        case 8: return emu ? (const void*)flash_ll_kernel_emu<T, 8> : (const void*)flash_ll_kernel<T, 8>;
+        default: return emu ? (const void*)flash_ll_kernel_emu<T, 0> : (const void*)flash_ll_kernel<T, 0>;
+    }
+}
+
 template <typename Tin, typename Tout, int WORLD>
 __global__ void __launch_bounds__(kFlashThreads, 2) flash_kernel(const __grid_constant__ CollArgs a) {
     flash_body<Tin, Tout, WORLD>(a, blockIdx.x);
@@ -283,6 +403,15 @@ const void* pick_flash_rms(int world, bool emu) {
 }
 
 }  // namespace
+
+const void* FlashLLKernelFor(Dtype dt, int world, bool emu) {
+    switch (dt) {
+        case Dtype::FP32: return pick_flash_ll<float>(world, emu);
+        case Dtype::FP16: return pick_flash_ll<__half>(world, emu);
+        case Dtype::BF16: return pick_flash_ll<__nv_bfloat16>(world, emu);
+    }
+    return nullptr;
+}
 
 const void* FlashKernelFor(Dtype in, Dtype out, int epilogue, int world, bool emu) {
     if (epilogue == kEpiResidualRmsNorm) {

@@ -7,14 +7,16 @@
 // [N, K] (this rank's slice of the row-parallel weight, K contiguous, the layout of
 // torch.nn.Linear.weight), both bf16; the sum runs over the ranks.
 //
-// Phase 1 (GEMM): a persistent grid walks 128x128 output tiles.  One elected thread
-// feeds a 3-stage shared-memory pipeline with TMA (cp.async.bulk.tensor, 128-byte
-// swizzle, no multicast) and issues tcgen05.mma (bf16 x bf16 -> fp32) into a
-// 128-column TMEM accumulator; completion arrives on mbarriers through
-// tcgen05.commit.  The four warps read the accumulator back with tcgen05.ld, round
-// to bf16, transpose through shared memory and PUSH every row straight into the
-// landing zone of the rank that owns that row (peer stores over NVLink), then bump
-// that rank's arrival counter with red.release.sys.
+// Phase 1 (GEMM): a persistent grid (one 6-warp CTA per SM) walks 128x128 output
+// tiles, warp-specialised.  Warp 0 feeds a 5-stage shared-memory pipeline with TMA
+// (cp.async.bulk.tensor, 128-byte swizzle, no multicast); warp 1 issues tcgen05.mma
+// (bf16 x bf16 -> fp32) into one of two 128-column TMEM accumulators and signals
+// stage release and accumulator completion through tcgen05.commit on mbarriers;
+// warps 2..5 read a finished accumulator back with tcgen05.ld while the next tile's
+// MMAs run into the other one, round to bf16, transpose through swizzled shared
+// memory and PUSH every row straight into the landing zone of the rank that owns
+// that row (peer stores over NVLink), then bump that rank's arrival counter with
+// red.release.sys.
 // Phase 2 (reduce): the same CTAs wait (bounded) until all ranks' partial rows for
 // the rows this rank owns have landed, add them in fp32 in rank order, add the
 // residual, normalise the row and write the bf16 result into EVERY rank's output
@@ -35,11 +37,13 @@ namespace yali {
 namespace {
 
 constexpr int BM = kGemmTileM, BN = kGemmTileN, BK = 64;  // BK bf16 = one 128-byte swizzle row
-constexpr int kStages = 3;
+constexpr int kStages = 5;
+constexpr int kEpilogueWarps = 4;
 constexpr uint32_t kStageABytes = BM * BK * 2, kStageBBytes = BN * BK * 2;
 constexpr uint32_t kStageBytes = kStageABytes + kStageBBytes;
-constexpr uint32_t kSmemBytes = kStages * kStageBytes + 1024;  // + slack to align the base to 1024 bytes
-constexpr uint32_t kTmemCols = 128;
+constexpr uint32_t kEpiStageBytes = kEpilogueWarps * 32 * BN * 2;  // transposition buffer of the epilogue warps
+constexpr uint32_t kSmemBytes = kStages * kStageBytes + kEpiStageBytes + 1024;  // + slack to align the base
+constexpr uint32_t kTmemCols = 256;  // two accumulators of BN fp32 columns
 
 // tcgen05 instruction descriptor: D = fp32, A = B = bf16, both K-major, N at bit 17 (>>3), M at bit 24 (>>4).
 constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) |
@@ -73,9 +77,9 @@ __device__ __forceinline__ char* landing(const GemmArArgs& a, int on_rank, int s
 __device__ __forceinline__ void gemm_ar_body(const GemmArArgs& a, const CUtensorMap* tmap_a, const CUtensorMap* tmap_b,
                                              uint32_t cta, uint32_t nctas) {
     extern __shared__ uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t full_bar[kStages], empty_bar[kStages], accum_bar;
+    __shared__ __align__(8) uint64_t full_bar[kStages], empty_bar[kStages], tmem_full_bar[2], tmem_empty_bar[2];
     __shared__ uint32_t s_tmem;
-    __shared__ int s_abort;
+    __shared__ volatile int s_abort;
     __shared__ float s_red[32];
 
     const CommView& cv = a.cv;
@@ -100,12 +104,15 @@ __device__ __forceinline__ void gemm_ar_body(const GemmArArgs& a, const CUtensor
             ptx::mbar_init(&full_bar[s], 1);
             ptx::mbar_init(&empty_bar[s], 1);
         }
-        ptx::mbar_init(&accum_bar, 1);
+        for (int b = 0; b < 2; ++b) {
+            ptx::mbar_init(&tmem_full_bar[b], 1);
+            ptx::mbar_init(&tmem_empty_bar[b], kEpilogueWarps);
+        }
         ptx::mbar_fence_init();
         ptx::tma_prefetch_desc(tmap_a);
         ptx::tma_prefetch_desc(tmap_b);
     }
-    if (warp == 0) {
+    if (warp == 1) {
         ptx::tmem_alloc(&s_tmem, kTmemCols);
         ptx::tmem_relinquish();
     }
@@ -117,115 +124,138 @@ __device__ __forceinline__ void gemm_ar_body(const GemmArArgs& a, const CUtensor
     const uint32_t ntm = (a.T + BM - 1) / BM, ntn = a.N / BN, kblocks = a.K / BK;
     const uint32_t ntiles = ntm * ntn;
     const uint32_t Rs = a.rows_per_owner;
-    uint32_t g_load = 0, g_mma = 0, tile_iter = 0;
-    bool ok = true;
+    // Two-shot: every rank starts with the row blocks owned by its right-hand neighbour and walks
+    // on from there, so that at any moment the ranks push to different owners instead of all
+    // converging on the owner of the first rows (which would serialise on that rank's links).
+    const uint32_t mt_shift = a.oneshot ? 0u : (((static_cast<uint32_t>(r) + 1u) % W) * Rs / BM) % ntm;
 
-    // ------------------------------------------------------------------ phase 1: GEMM tiles
-    for (uint32_t tile = cta; ok && tile < ntiles; tile += nctas, ++tile_iter) {
-        const uint32_t mt = tile / ntn, nt = tile % ntn;
-        if (tid == 0) {
-            uint32_t issued = 0, consumed = 0;
-            while (consumed < kblocks) {
-                while (issued < kblocks && issued - consumed < kStages) {
-                    const uint32_t s = g_load % kStages;
-                    if (g_load >= kStages && !mbar_wait_deadline(&empty_bar[s], ((g_load / kStages) - 1) & 1, deadline)) {
-                        report_timeout(cv, kSiteMbar, r, cta, 1, g_load);
+    // ------------------------------------------------------------------ phase 1: GEMM tiles, warp-specialised
+    // warp 0: TMA producer; warp 1: MMA issuer; warps 2..5: epilogue (TMEM -> bf16 -> peers).
+    // Two TMEM accumulators of 128 columns alternate, so the MMAs of tile i+1 run while tile i
+    // is read back and pushed.
+    if (warp == 0) {
+        if (lane == 0) {
+            uint32_t g = 0;  // k-blocks loaded so far
+            for (uint32_t tile = cta; tile < ntiles && !s_abort; tile += nctas) {
+                const uint32_t mt = (tile / ntn + mt_shift) % ntm, nt = tile % ntn;
+                for (uint32_t kb = 0; kb < kblocks; ++kb, ++g) {
+                    const uint32_t s = g % kStages;
+                    if (!mbar_wait_deadline(&empty_bar[s], ((g / kStages) & 1u) ^ 1u, deadline)) {
+                        report_timeout(cv, kSiteMbar, r, cta, 1, g);
                         s_abort = 1;
                         break;
                     }
                     ptx::mbar_expect_tx(&full_bar[s], kStageBytes);
-                    ptx::tma_load_2d(smem + s * kStageBytes, tmap_a, issued * BK, mt * BM, &full_bar[s]);
-                    ptx::tma_load_2d(smem + s * kStageBytes + kStageABytes, tmap_b, issued * BK, nt * BN, &full_bar[s]);
-                    ++g_load;
-                    ++issued;
+                    ptx::tma_load_2d(smem + s * kStageBytes, tmap_a, kb * BK, mt * BM, &full_bar[s]);
+                    ptx::tma_load_2d(smem + s * kStageBytes + kStageABytes, tmap_b, kb * BK, nt * BN, &full_bar[s]);
                 }
-                if (s_abort) break;
-                const uint32_t s = g_mma % kStages;
-                if (!mbar_wait_deadline(&full_bar[s], (g_mma / kStages) & 1, deadline)) {
-                    report_timeout(cv, kSiteMbar, r, cta, 2, g_mma);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            uint32_t g = 0, it = 0;
+            for (uint32_t tile = cta; tile < ntiles && !s_abort; tile += nctas, ++it) {
+                const uint32_t b = it & 1u;
+                if (!mbar_wait_deadline(&tmem_empty_bar[b], ((it >> 1) & 1u) ^ 1u, deadline)) {
+                    report_timeout(cv, kSiteMbar, r, cta, 4, it);
                     s_abort = 1;
                     break;
                 }
                 ptx::tc_fence_after_sync();
-                const uint32_t a_addr = ptx::smem_u32(smem + s * kStageBytes);
-                const uint64_t da = smem_desc_sw128(a_addr), db = smem_desc_sw128(a_addr + kStageABytes);
-#pragma unroll
-                for (int k = 0; k < BK / 16; ++k) {
-                    // 16 bf16 = 32 bytes further along K inside the swizzle row: +2 in the address field
-                    ptx::tc_mma_f16(tmem, da + 2 * k, db + 2 * k, kIdesc, (consumed | k) != 0 ? 1u : 0u);
-                }
-                ptx::tc_commit(&empty_bar[s]);  // frees the stage when these MMAs have read it
-                ++g_mma;
-                ++consumed;
-            }
-            if (!s_abort) ptx::tc_commit(&accum_bar);
-        }
-        // Everybody waits for the accumulator of this tile.
-        if (!mbar_wait_deadline(&accum_bar, tile_iter & 1, deadline)) {
-            if (tid == 0 && !s_abort) report_timeout(cv, kSiteMbar, r, cta, 3, tile_iter);
-            s_abort = 1;
-        }
-        __syncthreads();
-        if (s_abort) {
-            ok = false;
-            break;
-        }
-        ptx::tc_fence_after_sync();
-
-        // ---- epilogue: TMEM -> bf16 -> swizzled shared memory (stage 0 is idle now) -> owner's landing zone
-        uint8_t* stage = smem + warp * (32 * BN * 2);  // 32 rows x 256 bytes per warp
-#pragma unroll
-        for (int c = 0; c < BN / 32; ++c) {
-            uint32_t v[32];
-            ptx::tmem_ld_32x32(tmem + (static_cast<uint32_t>(warp * 32) << 16) + c * 32, v);
-            ptx::tmem_ld_wait();
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {  // 4 chunks of 8 columns = 16 bytes of bf16
-                float f[8];
-#pragma unroll
-                for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(v[j * 8 + i]);
-                const uint4 packed = pack16<__nv_bfloat16>(f);
-                const int chunk = c * 4 + j;  // logical 16-byte chunk of the 256-byte row
-                *reinterpret_cast<uint4*>(stage + lane * (BN * 2) + ((chunk ^ (lane & 15)) << 4)) = packed;
-            }
-        }
-        __syncwarp();
-        const int half = lane >> 4, c16 = lane & 15;
-#pragma unroll 4
-        for (int rr = 0; rr < 32; rr += 2) {
-            const int row_in_warp = rr + half;
-            const uint32_t grow = mt * BM + warp * 32 + row_in_warp;  // global row
-            if (grow < a.T) {
-                const uint4 x =
-                    *reinterpret_cast<const uint4*>(stage + row_in_warp * (BN * 2) + ((c16 ^ (row_in_warp & 15)) << 4));
-                const uint64_t col_off = (static_cast<uint64_t>(nt) * BN) * 2 + c16 * 16;
-                if (a.oneshot) {
-                    for (int k = 0; k < W; ++k) {
-                        const int d = (r + k) % W;
-                        ptx::st_v4(landing(a, d, r, parity) + static_cast<uint64_t>(grow) * a.N * 2 + col_off, x);
+                const uint32_t d_tmem = tmem + b * BN;
+                for (uint32_t kb = 0; kb < kblocks; ++kb, ++g) {
+                    const uint32_t s = g % kStages;
+                    if (!mbar_wait_deadline(&full_bar[s], (g / kStages) & 1u, deadline)) {
+                        report_timeout(cv, kSiteMbar, r, cta, 2, g);
+                        s_abort = 1;
+                        break;
                     }
-                } else {
-                    const int d = grow / Rs;
-                    ptx::st_v4(landing(a, d, r, parity) + static_cast<uint64_t>(grow - d * Rs) * a.N * 2 + col_off, x);
+                    ptx::tc_fence_after_sync();
+                    const uint32_t a_addr = ptx::smem_u32(smem + s * kStageBytes);
+                    const uint64_t da = smem_desc_sw128(a_addr), db = smem_desc_sw128(a_addr + kStageABytes);
+#pragma unroll
+                    for (int k = 0; k < BK / 16; ++k) {
+                        // 16 bf16 = 32 bytes further along K inside the swizzle row: +2 in the address field
+                        ptx::tc_mma_f16(d_tmem, da + 2 * k, db + 2 * k, kIdesc, (kb | k) != 0 ? 1u : 0u);
+                    }
+                    ptx::tc_commit(&empty_bar[s]);  // frees the stage when these MMAs have read it
                 }
+                if (s_abort) break;
+                ptx::tc_commit(&tmem_full_bar[b]);  // accumulator complete
             }
         }
-        ptx::tc_fence_before_sync();
-        __syncthreads();  // all pushes of this tile are issued; TMEM and stage 0 are free again
-        // One arrival per (tile, destination that received rows of it).
-        if (tid < W) {
-            const uint32_t row_lo = mt * BM, row_hi = min(a.T, row_lo + BM);
-            bool touched = a.oneshot != 0;
-            if (!touched) touched = static_cast<uint32_t>(tid) * Rs < row_hi && (static_cast<uint32_t>(tid) + 1) * Rs > row_lo;
-            if (touched) ptx::red_release_sys_add(flag_word(cv, tid, kGemmCntOff + r), 1u);
+    } else {
+        const int q = warp & 3;                       // TMEM lane quarter this warp may read
+        const int etid = tid - 2 * 32;                // 0..127 among the epilogue threads
+        uint8_t* stage = smem + kStages * kStageBytes + q * (32 * BN * 2);  // 32 rows x 256 bytes per warp
+        uint32_t it = 0;
+        for (uint32_t tile = cta; tile < ntiles; tile += nctas, ++it) {
+            const uint32_t mt = (tile / ntn + mt_shift) % ntm, nt = tile % ntn, b = it & 1u;
+            // (Only this wait decides whether the epilogue warps go on: all four see the same
+            // barrier, so they leave together and nobody is left alone at the named barrier below.)
+            if (!mbar_wait_deadline(&tmem_full_bar[b], (it >> 1) & 1u, deadline)) {
+                if (lane == 0 && !s_abort) report_timeout(cv, kSiteMbar, r, cta, 3, it);
+                s_abort = 1;
+                break;
+            }
+            ptx::tc_fence_after_sync();
+#pragma unroll
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t v[32];
+                ptx::tmem_ld_32x32(tmem + b * BN + (static_cast<uint32_t>(q * 32) << 16) + c * 32, v);
+                ptx::tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {  // 4 chunks of 8 columns = 16 bytes of bf16
+                    float f[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(v[j * 8 + i]);
+                    const int chunk = c * 4 + j;  // logical 16-byte chunk of the 256-byte row
+                    *reinterpret_cast<uint4*>(stage + lane * (BN * 2) + ((chunk ^ (lane & 15)) << 4)) =
+                        pack16<__nv_bfloat16>(f);
+                }
+            }
+            // The accumulator is in shared memory now: hand it back to the MMA warp.
+            ptx::tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(&tmem_empty_bar[b]);
+            const int half = lane >> 4, c16 = lane & 15;
+#pragma unroll 4
+            for (int rr = 0; rr < 32; rr += 2) {
+                const int row_in_warp = rr + half;
+                const uint32_t grow = mt * BM + q * 32 + row_in_warp;  // global row
+                if (grow < a.T) {
+                    const uint4 x = *reinterpret_cast<const uint4*>(stage + row_in_warp * (BN * 2) +
+                                                                    ((c16 ^ (row_in_warp & 15)) << 4));
+                    const uint64_t col_off = (static_cast<uint64_t>(nt) * BN) * 2 + c16 * 16;
+                    if (a.oneshot) {
+                        for (int k = 0; k < W; ++k) {
+                            const int d = (r + k) % W;
+                            ptx::st_v4(landing(a, d, r, parity) + static_cast<uint64_t>(grow) * a.N * 2 + col_off, x);
+                        }
+                    } else {
+                        const int d = grow / Rs;
+                        ptx::st_v4(landing(a, d, r, parity) + static_cast<uint64_t>(grow - d * Rs) * a.N * 2 + col_off, x);
+                    }
+                }
+            }
+            // All four epilogue warps have issued their pushes of this tile (and are done with
+            // the staging buffer): one arrival per destination that received rows of it.
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (etid < W) {
+                const uint32_t row_lo = mt * BM, row_hi = min(a.T, row_lo + BM);
+                bool touched = a.oneshot != 0;
+                if (!touched)
+                    touched = static_cast<uint32_t>(etid) * Rs < row_hi && (static_cast<uint32_t>(etid) + 1) * Rs > row_lo;
+                if (touched) ptx::red_release_sys_add(flag_word(cv, etid, kGemmCntOff + r), 1u);
+            }
         }
-        ptx::tc_fence_after_sync();
     }
 
     // TMEM is not needed any more (also on the abort path).
+    ptx::tc_fence_before_sync();
     __syncthreads();
-    if (warp == 0) ptx::tmem_dealloc(tmem, kTmemCols);
-    if (!ok) return;
+    if (warp == 1) ptx::tmem_dealloc(tmem, kTmemCols);
+    if (s_abort) return;
 
     // ------------------------------------------------------------------ phase 2: reduce + residual + RMSNorm
     // Rows this rank normalises: its shard (two-shot) or all rows (one-shot).
@@ -334,12 +364,12 @@ __device__ __forceinline__ void gemm_ar_body(const GemmArArgs& a, const CUtensor
 
 }  // namespace
 
-__global__ void __launch_bounds__(kGemmThreads, 2) gemm_ar_rmsnorm_kernel(const __grid_constant__ GemmArArgs a) {
+__global__ void __launch_bounds__(kGemmThreads, 1) gemm_ar_rmsnorm_kernel(const __grid_constant__ GemmArArgs a) {
     gemm_ar_body(a, &a.tmap_a, &a.tmap_b, blockIdx.x, gridDim.x);
 }
 
 // All ranks of an emulated communicator in one cooperative launch (ranks = blockIdx.y).
-__global__ void __launch_bounds__(kGemmThreads, 2) gemm_ar_rmsnorm_kernel_emu(const __grid_constant__ GemmArEmuArgs e) {
+__global__ void __launch_bounds__(kGemmThreads, 1) gemm_ar_rmsnorm_kernel_emu(const __grid_constant__ GemmArEmuArgs e) {
     const GemmArArgs& a = e.r[blockIdx.y];
     gemm_ar_body(a, &a.tmap_a, &a.tmap_b, blockIdx.x, gridDim.x);
 }

@@ -12,8 +12,8 @@ namespace yali {
 
 constexpr int kGemmTileM = 128;
 constexpr int kGemmTileN = 128;
-constexpr int kGemmThreads = 128;
-constexpr int kGemmMaxVecPerThread = 4;  // N <= 4 * 128 threads * 8 bf16 = 4096
+constexpr int kGemmThreads = 192;  // TMA warp, MMA warp, four epilogue warps
+constexpr int kGemmMaxVecPerThread = 3;  // N <= 3 * 192 threads * 8 bf16 = 4608 (the host caps N at 4096)
 
 struct alignas(64) GemmArArgs {
     CUtensorMap tmap_a;  // x  [T, K] bf16, box 64 x 128, 128-byte swizzle

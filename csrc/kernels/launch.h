@@ -21,6 +21,8 @@ constexpr int kNvlsThreads = 512;
 
 // nullptr when the combination is not built.
 const void* FlashKernelFor(Dtype in, Dtype out, int epilogue, int world, bool emu);
+// Flag-in-data form of the one-shot kernel (equal in/out type, scale epilogue only).
+const void* FlashLLKernelFor(Dtype dt, int world, bool emu);
 const void* StreamKernelFor(Dtype in, Dtype out, int epilogue, int world, bool emu);
 const void* NvlsKernelFor(Dtype dt, int world, bool two_shot);
 

@@ -71,6 +71,38 @@ __global__ void validate_sum_kernel(const Tout* out, uint64_t n, uint64_t index_
               static_cast<unsigned long long>(__double_as_longlong(worst)));
 }
 
+// In-place residual add + RMSNorm over rows of `hidden` elements (one CTA per row, grid-stride).
+// Used when a message is too large for the one-shot kernel that fuses this step: the all-reduce
+// runs first, then this kernel normalises the local result.
+template <typename T>
+__global__ void residual_rmsnorm_kernel(T* x, const T* residual, T* residual_out, const T* weight, uint64_t rows,
+                                        uint32_t hidden, float eps) {
+    __shared__ float s_part[32];
+    const int tid = threadIdx.x, nt = blockDim.x;
+    for (uint64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+        T* xr = x + row * hidden;
+        float ss = 0.f;
+        for (uint32_t c = tid; c < hidden; c += nt) {
+            float v = to_f32<T>(xr[c]);
+            if (residual) v += to_f32<T>(residual[row * hidden + c]);
+            if (residual_out) residual_out[row * hidden + c] = from_f32<T>(v);
+            ss += v * v;
+        }
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        __syncthreads();
+        if ((tid & 31) == 0) s_part[tid >> 5] = ss;
+        __syncthreads();
+        float tot = 0.f;
+        for (int w = 0; w < (nt + 31) / 32; ++w) tot += s_part[w];
+        const float inv = rsqrtf(tot / static_cast<float>(hidden) + eps);
+        for (uint32_t c = tid; c < hidden; c += nt) {
+            float v = to_f32<T>(xr[c]);
+            if (residual) v += to_f32<T>(residual[row * hidden + c]);
+            xr[c] = from_f32<T>(v * inv * to_f32<T>(weight[c]));
+        }
+    }
+}
+
 int GridFor(uint64_t n) {
     uint64_t b = (n + 255) / 256;
     if (b < 1) b = 1;
@@ -149,6 +181,30 @@ cudaError_t ValidateSumAsync(const void* out, uint64_t n, uint64_t index_offset,
                                               d_rep, s);
     }
     return cudaErrorInvalidValue;
+}
+
+cudaError_t ResidualRmsNormInPlace(void* x, const void* residual, void* residual_out, const void* weight,
+                                   uint64_t rows, uint32_t hidden, float eps, Dtype dt, cudaStream_t s) {
+    if (rows == 0) return cudaSuccess;
+    const int grid = static_cast<int>(rows < 148 * 8 ? rows : 148 * 8);
+    switch (dt) {
+        case Dtype::FP32:
+            residual_rmsnorm_kernel<<<grid, 256, 0, s>>>(static_cast<float*>(x), static_cast<const float*>(residual),
+                                                         static_cast<float*>(residual_out),
+                                                         static_cast<const float*>(weight), rows, hidden, eps);
+            break;
+        case Dtype::FP16:
+            residual_rmsnorm_kernel<<<grid, 256, 0, s>>>(static_cast<__half*>(x), static_cast<const __half*>(residual),
+                                                         static_cast<__half*>(residual_out),
+                                                         static_cast<const __half*>(weight), rows, hidden, eps);
+            break;
+        case Dtype::BF16:
+            residual_rmsnorm_kernel<<<grid, 256, 0, s>>>(
+                static_cast<__nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(residual),
+                static_cast<__nv_bfloat16*>(residual_out), static_cast<const __nv_bfloat16*>(weight), rows, hidden, eps);
+            break;
+    }
+    return cudaGetLastError();
 }
 
 }  // namespace yali

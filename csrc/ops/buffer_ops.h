@@ -80,6 +80,10 @@ cudaError_t ValidateSumAsync(const void* out, uint64_t n, uint64_t index_offset,
                              uint64_t seed_base, int world, float scale, double rtol, double atol,
                              ValidateReport* d_rep, cudaStream_t s);
 
+// x[row] = RMSNorm(x[row] + residual[row]) * weight, in place; residual / residual_out may be nullptr.
+cudaError_t ResidualRmsNormInPlace(void* x, const void* residual, void* residual_out, const void* weight,
+                                   uint64_t rows, uint32_t hidden, float eps, Dtype dt, cudaStream_t s);
+
 // ---- synchronous conveniences with the reference's names ----
 // Fills with one value and waits (reference: SeedBufferSync).
 cudaError_t SeedBufferSync(void* p, size_t n, Dtype dt, float value);

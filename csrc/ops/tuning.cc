@@ -36,12 +36,18 @@ uint64_t FlashCrossoverBytes(Dtype /*dt*/, int world) {
     return 256ull << 10;
 }
 
+uint64_t LowLatencyMaxBytes(int /*world*/) {
+    const long long e = env::GetInt("YALI_LL_MAX_BYTES", -1);
+    return e >= 0 ? static_cast<uint64_t>(e) : (256ull << 10);
+}
+
 int FlashLanePreset(uint64_t bytes, Dtype /*dt*/, int /*world*/) {
-    // About 8 KiB per CTA (one 16-byte vector per thread) while the message is
-    // small, then 32 KiB per CTA, capped by the flag rows.
-    if (bytes <= (8ull << 10)) return 1;
-    if (bytes <= (2ull << 20)) return static_cast<int>(std::min<uint64_t>(CeilDiv(bytes, 8ull << 10), 256));
-    return static_cast<int>(std::min<uint64_t>(std::max<uint64_t>(CeilDiv(bytes, 32ull << 10), 256), kMaxFlashCtas));
+    // Measured on 2 x B200: about 32 KiB per CTA is best from 64 KiB to a few MiB (more CTAs
+    // only add launch and flag traffic), 128 CTAs from 16 MiB, 256 for the largest messages.
+    if (bytes <= (4ull << 10)) return 1;
+    if (bytes <= (512ull << 10)) return static_cast<int>(std::min<uint64_t>(CeilDiv(bytes, 4ull << 10), 16));
+    if (bytes < (32ull << 20)) return static_cast<int>(std::min<uint64_t>(std::max<uint64_t>(CeilDiv(bytes, 32ull << 10), 16), 128));
+    return 256;
 }
 
 int StreamLanePreset(uint64_t bytes, Dtype /*dt*/, int /*world*/) {
@@ -275,6 +281,14 @@ Result MakePlan(int world, uint64_t count, Dtype in, Dtype out, int epilogue, Ke
         case Variant::Flash: {
             uint32_t c = row && row->ctas ? row->ctas : static_cast<uint32_t>(FlashLanePreset(bytes, in, world));
             if (dev_ctas > 0) c = dev_ctas;
+            // Small messages of equal in/out type take the flag-in-data form (twice the bytes on
+            // the wire, but no flag round trip).
+            if (!rows && world > 1 && in == out && caps.vec_ok && bytes % 16 == 0 && bytes <= caps.ll_cap &&
+                bytes <= LowLatencyMaxBytes(world)) {
+                p.flags |= kFlagLowLatency;
+                if (!(row && row->ctas) && dev_ctas <= 0)
+                    c = static_cast<uint32_t>(std::min<uint64_t>(std::max<uint64_t>(CeilDiv(bytes, 16ull << 10), 1), 64));
+            }
             p.ctas = std::max<uint32_t>(1, std::min<uint32_t>(std::min<uint32_t>(c, max_ctas), kMaxFlashCtas));
             break;
         }

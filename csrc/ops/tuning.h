@@ -26,6 +26,7 @@ struct PlanCaps {
     uint64_t flash_cap = 0;        // bytes of one-shot staging per source
     uint64_t ring_bytes = 0;       // bytes of the ring region
     uint64_t nvls_cap = 0;         // bytes of one NVLS staging half
+    uint64_t ll_cap = 0;           // largest payload of the flag-in-data one-shot protocol
     bool has_multicast = false;
     bool symmetric = false;        // send and recv of every rank live in the heap at equal offsets
     bool peer_recv = false;        // every rank's recv is peer-addressable (direct all-gather possible)
@@ -47,6 +48,8 @@ struct Plan {
 // ---- the reference's tuning entry points, generalised to a world size ----
 // Largest message (bytes) that takes the one-shot path.
 uint64_t FlashCrossoverBytes(Dtype dt, int world = 2);
+// Largest message (bytes) that takes the flag-in-data form of the one-shot kernel (YALI_LL_MAX_BYTES).
+uint64_t LowLatencyMaxBytes(int world = 2);
 // CTAs of the one-shot kernel.
 int FlashLanePreset(uint64_t bytes, Dtype dt, int world = 2);
 // Lanes of the two-shot kernel.

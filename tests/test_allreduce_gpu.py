@@ -270,3 +270,38 @@ def test_cuda_graph_replay(comm):
     check(comm, out_a, torch.float32)
     check(comm, out_b, torch.bfloat16, NORMAL, seed=5)
     check(comm, out_c, torch.float32, scale=0.5)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_flag_in_data_form_for_small_messages(comm, dtype):
+    """Small aligned messages take the flag-in-data protocol (flags bit 6); larger or ragged ones the flagged one."""
+    for n, expect_ll in [(8, True), (4096, True), (65536, True), (65537, False), (1 << 20, False)]:
+        xs = make_inputs(comm, n, dtype, NORMAL, seed=n)
+        for _ in range(3):  # consecutive calls reuse the two staging halves
+            outs = comm.all_reduce(xs, mode="flash")
+        comm.sync()
+        lc = comm.last_call()
+        nbytes = n * xs[0].element_size()
+        assert bool(lc["flags"] & 64) == (expect_ll and nbytes % 16 == 0 and nbytes <= 256 * 1024), (n, lc)
+        check(comm, outs, dtype, NORMAL, seed=n)
+    # scale epilogue on the same path
+    xs = make_inputs(comm, 2048, dtype)
+    outs = comm.all_reduce(xs, mode="flash", scale=0.25)
+    comm.sync()
+    assert comm.last_call()["flags"] & 64
+    check(comm, outs, dtype, scale=0.25)
+
+
+def test_rmsnorm_beyond_the_one_shot_capacity_uses_two_launches(comm):
+    hidden = 4096
+    rows = comm.layout()["flash_cap"] // (hidden * 2) + 64  # just above the one-shot staging
+    xs = [x.view(rows, hidden) for x in make_inputs(comm, rows * hidden, torch.bfloat16, NORMAL)]
+    g = torch.Generator(device="cpu").manual_seed(11)
+    weight = (torch.rand(hidden, generator=g) + 0.5).to(torch.bfloat16).cuda()
+    before = comm.launches
+    outs = comm.all_reduce_rmsnorm(xs, [weight] * comm.world, None, eps=1e-5)
+    comm.sync()
+    assert comm.launches - before == 1 + comm.world  # one cooperative all-reduce + one norm kernel per rank
+    ref, _ = yali.reference.residual_rmsnorm(yali.reference.all_reduce_sum(xs), weight.cpu().double(), None, 1e-5)
+    torch.testing.assert_close(outs[0][:256].cpu().double(), ref[:256], rtol=3e-2, atol=3e-2)
+    torch.testing.assert_close(outs[-1][-256:].cpu().double(), ref[-256:], rtol=3e-2, atol=3e-2)

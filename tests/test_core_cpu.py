@@ -19,7 +19,7 @@ MiB = 1 << 20
 
 def caps(world, **kw):
     c = PlanCaps(flash_cap=(64 if world == 2 else 16 if world <= 4 else 8) * MiB, ring_bytes=256 * MiB,
-                 nvls_cap=64 * MiB, has_multicast=0, symmetric=0, peer_recv=0, vec_ok=1, max_ctas=1184)
+                 nvls_cap=64 * MiB, has_multicast=0, symmetric=0, peer_recv=0, vec_ok=1, max_ctas=1184, ll_cap=1 * MiB)
     for k, v in kw.items():
         setattr(c, k, v)
     return c
@@ -72,18 +72,19 @@ def test_shard_elems(native_lib):
 
 
 def test_heap_layout(native_lib):
-    f = (ctypes.c_uint64 * 12)()
+    f = (ctypes.c_uint64 * 14)()
     for world in (1, 2, 4, 8):
         assert native_lib.yali_c_heap_layout(world, 0, f) == 0
         total, flags_off, flash_off, flash_cap, ring_off, ring_bytes, nvls_off, nvls_cap, gemm_off, gemm_cap, \
-            user_off, user_bytes = list(f)
+            user_off, user_bytes, ll_off, ll_cap = list(f)
         assert flags_off == 0 and user_off + user_bytes == total and user_bytes >= 256 * MiB
         if world > 1:
             assert flash_off >= 1 * MiB
             assert ring_off == flash_off + 2 * (world - 1) * flash_cap
             assert nvls_off == ring_off + ring_bytes
             assert gemm_off == nvls_off + 2 * nvls_cap
-            assert user_off == gemm_off + 2 * world * gemm_cap
+            assert ll_off == gemm_off + 2 * world * gemm_cap
+            assert user_off == ll_off + 2 * (world - 1) * 2 * ll_cap
     assert native_lib.yali_c_heap_layout(8, 1 * MiB, f) != 0  # too small for the fixed regions
 
 
@@ -99,7 +100,9 @@ def test_plan_auto_selection(native_lib):
     rc, p, _ = make_plan(lib, 8, 64 * MiB, cp=caps(8, has_multicast=1, symmetric=0))
     assert rc == 0 and p.variant == 1  # 256 MiB does not fit the NVLS staging: ring kernel
     rc, p, _ = make_plan(lib, 8, 1024)
-    assert rc == 0 and p.variant == 0 and p.ctas == 1
+    assert rc == 0 and p.variant == 0 and p.ctas == 1 and p.flags & 64  # flag-in-data form for tiny messages
+    rc, p, _ = make_plan(lib, 8, 1024, cp=caps(8, vec_ok=0))
+    assert rc == 0 and not p.flags & 64  # needs aligned buffers
 
 
 def test_plan_forced_modes_and_errors(native_lib):

@@ -1,0 +1,82 @@
+"""Tooling without a GPU: statistics, report generation from sweep lines, nccl-tests log parsing, NVLink status
+parsing, the launcher, and the baseline validator's version check."""
+import json
+import subprocess
+import sys
+from pathlib import Path
+
+from yali_b200.utils import hw_info
+from yali_b200.utils.stats import percentile, summarise
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def test_stats():
+    s = summarise([1.0, 2.0, 3.0, 4.0])
+    assert s.mean == 2.5 and s.min == 1.0 and s.max == 4.0 and s.samples == 4
+    assert abs(s.stddev - 1.2909944) < 1e-6 and abs(s.cv_pct - 51.6397779) < 1e-5
+    assert s.p50 == 2.5 and percentile([1, 2, 3, 4], 100) == 4 and percentile([], 50) == 0.0
+    assert summarise([]).samples == 0 and summarise([7.0]).stddev == 0.0
+
+
+def test_report_from_sweep_lines(tmp_path):
+    rows = []
+    for size, y, n in [(4096, 0.5, 0.2), (1 << 20, 90.0, 56.0), (1 << 30, 670.0, 566.0)]:
+        for var in ("auto", "flash"):
+            rows.append({"impl": "yali_b200", "world": 2, "dtype": "fp32", "bytes": size, "variant": var,
+                         "kernel": "flash", "ctas": 8, "slot_bytes": 0, "us": size / y / 1e3, "busbw_gbps": y})
+        rows.append({"impl": "nccl", "world": 2, "dtype": "fp32", "bytes": size, "variant": "nccl", "us": size / n / 1e3,
+                     "busbw_gbps": n})
+    run = tmp_path / "run.jsonl"
+    run.write_text("\n".join(json.dumps(r) for r in rows) + "\nnoise line\n")
+    out = tmp_path / "rep"
+    subprocess.run([sys.executable, str(ROOT / "bench" / "report.py"), "--out", str(out), str(run), str(run)], check=True)
+    summary = (out / "summary.md").read_text()
+    assert "| 1M | 90.0 | 90.0 | - | - | 56.0 | 1.61x |" in summary and "## 2 ranks, fp32" in summary
+    csv_text = (out / "yali_b200_w2_fp32.csv").read_text()
+    assert "mean_gbps" in csv_text and ",2\n" in csv_text  # two runs per point
+
+
+def test_consolidate_eval(tmp_path):
+    log = """#       size         count      type   redop    root     time   algbw   busbw #wrong     time   algbw   busbw #wrong
+     1048576        262144     float     sum      -1    18.70   56.07   56.07      0    18.50   56.68   56.68      0
+  1073741824     268435456     float     sum      -1   1897.1  566.00  566.00      0   1890.0  568.12  568.12      0
+"""
+    (tmp_path / "nccl.log").write_text(log)
+    sweep = [{"impl": "yali_b200", "world": 2, "dtype": "fp32", "bytes": 1 << 20, "variant": "auto", "us": 11.9,
+              "busbw_gbps": 88.1},
+             {"impl": "yali_b200", "world": 2, "dtype": "fp32", "bytes": 1 << 30, "variant": "auto", "us": 1595.0,
+              "busbw_gbps": 673.2}]
+    (tmp_path / "s.jsonl").write_text("\n".join(json.dumps(r) for r in sweep))
+    r = subprocess.run([sys.executable, str(ROOT / "bench" / "consolidate_eval.py"), "--sweep", str(tmp_path / "s.jsonl"),
+                        "--nccl-log", str(tmp_path / "nccl.log"), "--out", str(tmp_path / "eval")], capture_output=True,
+                       text=True, check=True)
+    assert "2 sizes joined" in r.stdout and "none" in r.stdout
+    assert "1.571x" in (tmp_path / "eval" / "ratio.md").read_text()
+
+
+def test_nvlink_parsing_and_capability_table():
+    text = "GPU 0: NVIDIA B200 (UUID: x)\n\t Link 0: 53.125 GB/s\n\t Link 1: 53.125 GB/s\nGPU 1: NVIDIA B200\n\t Link 0: 53.125 GB/s\n"
+    st = hw_info.parse_nvlink_status(text)
+    assert st[0]["links"] == 2 and st[1]["links"] == 1 and st[0]["gbs_per_link"] == 53.125
+    b200 = hw_info.nvlink_for_capability(10)
+    assert b200["links"] == 18 and b200["unidirectional_gbs"] == 900.0
+    assert hw_info.measured_peaks()["source"] in ("measured", "fallback")
+
+
+def test_launcher_sets_rank_environment(tmp_path):
+    script = tmp_path / "p.py"
+    script.write_text("import os,sys\nprint(os.environ['RANK'], os.environ['WORLD_SIZE'], os.environ['LOCAL_RANK'])\n"
+                      "sys.exit(3 if os.environ['RANK']=='1' and os.environ.get('FAIL') else 0)\n")
+    r = subprocess.run([sys.executable, "-m", "yali_b200.launch", "-np", "3", sys.executable, str(script)],
+                       capture_output=True, text=True, cwd=str(ROOT))
+    assert r.returncode == 0 and sorted(r.stdout.split("\n")[:3]) == ["0 3 0", "1 3 1", "2 3 2"]
+    r = subprocess.run([sys.executable, "-m", "yali_b200.launch", "-np", "2", sys.executable, str(script)],
+                       capture_output=True, text=True, cwd=str(ROOT), env={**__import__("os").environ, "FAIL": "1"})
+    assert r.returncode == 3
+
+
+def test_nccl_header_matches_library():
+    sys.path.insert(0, str(ROOT / "bench"))
+    import validate_baselines as vb
+    assert vb.header_version() == vb.library_version()

@@ -29,6 +29,7 @@ CXX_FLAGS = ["-std=c++17", "-O2", "-fPIC", "-Wall", "-Wno-unused-function"]
 LIB_SOURCES = [
     "core/core.cc",
     "comm/bootstrap.cc",
+    "comm/bootstrap_mpi.cc",
     "comm/cuda_driver.cc",
     "comm/topology.cc",
     "comm/symm_heap.cc",
