@@ -43,11 +43,29 @@ def gather_max(comm, v):
     return max(struct.unpack("d", p)[0] for p in comm.allgather_object_bytes(struct.pack("d", v)))
 
 
-def timed(comm, fn, iters, warmup=10):
+def timed(comm, fn, iters, warmup=10, graph=False):
     for _ in range(warmup):
         fn()
     comm.barrier()
     torch.cuda.synchronize()
+    if graph:  # all calls in one CUDA graph, one replay timed: no host work between the kernels
+        g = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(g, stream=side):
+                for _ in range(iters):
+                    fn()
+        g.replay()
+        torch.cuda.synchronize()
+        comm.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        comm.barrier()
+        comm.check()
+        return gather_max(comm, e0.elapsed_time(e1) * 1e3 / iters)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(iters):
@@ -66,6 +84,7 @@ def main():
     ap.add_argument("--hidden", type=int, default=4096)
     ap.add_argument("--iters", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--graph", action="store_true", help="time one CUDA-graph replay of all calls")
     ap.add_argument("--arms", default="", help="comma list to restrict the arms")
     ap.add_argument("--out", default="")
     args = ap.parse_args()
@@ -116,11 +135,12 @@ def main():
         for label, fn in arms.items():
             if args.arms and label not in args.arms.split(","):
                 continue
-            us = timed(comm, fn, iters, args.warmup)
+            us = timed(comm, fn, iters, args.warmup, graph=args.graph)
             link_bytes = 0.0 if emu else (bytes_one if label == "fused_oneshot" else bytes_two)
             roof = max(t_gemm, link_bytes / (LINK_GBS * 1e9) * 1e6)
             row = {"T": T, "world": W, "arm": label, "us": round(us, 2), "roofline_us": round(roof, 3),
-                   "fraction_of_roofline": round(roof / us, 4), "peaks": src, "emulated": emu}
+                   "fraction_of_roofline": round(roof / us, 4), "peaks": src, "emulated": emu,
+                   "timing": "graph" if args.graph else "events"}
             rows.append(row)
             if rank == 0:
                 print(json.dumps(row), flush=True)

@@ -39,12 +39,31 @@ def gather_max(comm, v: float) -> float:
     return max(struct.unpack("d", p)[0] for p in comm.allgather_object_bytes(struct.pack("d", v)))
 
 
-def timed(comm, fn, iters: int, warmup: int) -> float:
-    """Average microseconds per call, max over ranks."""
+def timed(comm, fn, iters: int, warmup: int, graph: bool = False) -> float:
+    """Average microseconds per call, max over ranks.  graph=True captures the `iters` calls in one CUDA
+    graph and times one replay (after one untimed replay): no host launch work between the kernels."""
     for i in range(warmup):
         fn(i)
     comm.barrier()
     torch.cuda.synchronize()
+    if graph:
+        g = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(g, stream=side):
+                for i in range(iters):
+                    fn(warmup + i)
+        g.replay()
+        torch.cuda.synchronize()
+        comm.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        comm.barrier()
+        del g
+        return gather_max(comm, e0.elapsed_time(e1) * 1e3 / iters)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for i in range(iters):
@@ -66,6 +85,8 @@ def main() -> None:
     ap.add_argument("--out", default="")
     ap.add_argument("--tuning-out", default="")
     ap.add_argument("--iters", type=int, default=0, help="0: scaled by size")
+    ap.add_argument("--graph-max-bytes", type=int, default=0,
+                    help="sizes up to this are timed as one CUDA-graph replay of all calls (both arms)")
     args = ap.parse_args()
 
     heap = 2 * args.max_bytes + (3 << 30)
@@ -105,7 +126,7 @@ def main() -> None:
                 def call(i, var=var):
                     comm.all_reduce(pick(views_s[i % nbuf]), pick(views_r[i % nbuf]), mode=var)
                 try:
-                    us = timed(comm, call, iters, 20 if size <= (16 << 20) else 5)
+                    us = timed(comm, call, iters, 20 if size <= (16 << 20) else 5, graph=size <= args.graph_max_bytes)
                     comm.check()
                 except RuntimeError as e:
                     if "cannot run" in str(e) or "Unsupported" in str(e):
@@ -114,7 +135,8 @@ def main() -> None:
                 lc = comm.last_call()
                 row = {"impl": "yali_b200", "world": world, "dtype": dname, "bytes": size, "variant": var,
                        "kernel": lc["variant"], "ctas": lc["ctas"], "slot_bytes": lc["slot_bytes"], "us": round(us, 2),
-                       "busbw_gbps": round(size * factor / us / 1e3, 2), "emulated": emu}
+                       "busbw_gbps": round(size * factor / us / 1e3, 2), "emulated": emu,
+                       "timing": "graph" if size <= args.graph_max_bytes else "events"}
                 rows.append(row)
                 if var != "auto":
                     key = (dname, size)
@@ -130,9 +152,10 @@ def main() -> None:
 
                 def ncall(i):
                     dist.all_reduce(bufs[i % len(bufs)])
-                us = timed(comm, ncall, iters, 20 if size <= (16 << 20) else 5)
+                us = timed(comm, ncall, iters, 20 if size <= (16 << 20) else 5, graph=size <= args.graph_max_bytes)
                 row = {"impl": "nccl", "world": world, "dtype": dname, "bytes": size, "variant": "nccl",
-                       "us": round(us, 2), "busbw_gbps": round(size * factor / us / 1e3, 2)}
+                       "us": round(us, 2), "busbw_gbps": round(size * factor / us / 1e3, 2),
+                       "timing": "graph" if size <= args.graph_max_bytes else "events"}
                 if rank == 0:
                     print(json.dumps(row), flush=True)
                     if out_f:

@@ -86,6 +86,12 @@ __device__ __forceinline__ void gemm_ar_body(const GemmArArgs& a, const CUtensor
     const int W = cv.world, r = cv.rank;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint64_t deadline = ptx::globaltimer() + cv.timeout_ns;
+    // Optional timeline of CTA 0 (a.trace != nullptr): %globaltimer at the phase boundaries.
+#define YALI_STAMP(slot, who)                                                              \
+    do {                                                                                   \
+        if (a.trace && cta == 0 && tid == (who)) a.trace[slot] = ptx::globaltimer();       \
+    } while (0)
+    YALI_STAMP(0, 0);  // entry
     // Call number and counter targets come from this rank's call words (advanced by the last
     // CTA of the previous launch), so the launch itself carries no per-call state.
     __shared__ uint32_t s_call[2 + kMaxRanks];
@@ -120,6 +126,7 @@ __device__ __forceinline__ void gemm_ar_body(const GemmArArgs& a, const CUtensor
     __syncthreads();
     ptx::tc_fence_after_sync();
     const uint32_t tmem = s_tmem;
+    YALI_STAMP(1, 0);  // barriers initialised, TMEM allocated
 
     const uint32_t ntm = (a.T + BM - 1) / BM, ntn = a.N / BN, kblocks = a.K / BK;
     const uint32_t ntiles = ntm * ntn;
@@ -199,11 +206,16 @@ __device__ __forceinline__ void gemm_ar_body(const GemmArArgs& a, const CUtensor
                 break;
             }
             ptx::tc_fence_after_sync();
+            if (it == 0) YALI_STAMP(2, 64);  // first accumulator complete
+            // Warps whose 32 rows lie entirely beyond T (small batches) have nothing to read back.
+            const bool warp_has_rows = mt * BM + q * 32 < a.T;
 #pragma unroll
             for (int c = 0; c < BN / 32; ++c) {
+                if (!warp_has_rows) break;
                 uint32_t v[32];
                 ptx::tmem_ld_32x32(tmem + b * BN + (static_cast<uint32_t>(q * 32) << 16) + c * 32, v);
                 ptx::tmem_ld_wait();
+                if (mt * BM + q * 32 + lane >= a.T) continue;  // this lane's row is padding
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {  // 4 chunks of 8 columns = 16 bytes of bf16
                     float f[8];
@@ -248,6 +260,7 @@ __device__ __forceinline__ void gemm_ar_body(const GemmArArgs& a, const CUtensor
                     touched = static_cast<uint32_t>(etid) * Rs < row_hi && (static_cast<uint32_t>(etid) + 1) * Rs > row_lo;
                 if (touched) ptx::red_release_sys_add(flag_word(cv, etid, kGemmCntOff + r), 1u);
             }
+            if (it == 0) YALI_STAMP(3, 64);  // first tile pushed and announced
         }
     }
 
@@ -256,6 +269,7 @@ __device__ __forceinline__ void gemm_ar_body(const GemmArArgs& a, const CUtensor
     __syncthreads();
     if (warp == 1) ptx::tmem_dealloc(tmem, kTmemCols);
     if (s_abort) return;
+    YALI_STAMP(4, 0);  // all tiles of this CTA done
 
     // ------------------------------------------------------------------ phase 2: reduce + residual + RMSNorm
     // Rows this rank normalises: its shard (two-shot) or all rows (one-shot).
@@ -273,6 +287,7 @@ __device__ __forceinline__ void gemm_ar_body(const GemmArArgs& a, const CUtensor
         }
         __syncthreads();
         if (s_abort) return;
+        YALI_STAMP(5, 0);  // partial rows of every rank have landed
 
         constexpr int VEC = 8;  // bf16 per 16 bytes
         const uint32_t vec_per_row = a.N / VEC;
@@ -292,7 +307,14 @@ __device__ __forceinline__ void gemm_ar_body(const GemmArArgs& a, const CUtensor
 #pragma unroll
                     for (int i = 0; i < VEC; ++i) f[j][i] = 0.f;
                     const uint64_t off = (static_cast<uint64_t>(lr) * a.N + static_cast<uint64_t>(c) * VEC) * 2;
-                    for (int q = 0; q < W; ++q) accumulate<__nv_bfloat16>(f[j], ptx::ld_cg_v4(landing(a, r, q, parity) + off));
+                    // All sources' loads are issued before the first one is consumed.
+                    uint4 part[kMaxRanks];
+#pragma unroll
+                    for (int q = 0; q < kMaxRanks; ++q)
+                        if (q < W) part[q] = ptx::ld_cg_v4(landing(a, r, q, parity) + off);
+#pragma unroll
+                    for (int q = 0; q < kMaxRanks; ++q)
+                        if (q < W) accumulate<__nv_bfloat16>(f[j], part[q]);
                     const uint64_t goff = (static_cast<uint64_t>(grow) * a.N + static_cast<uint64_t>(c) * VEC) * 2;
                     if (res) accumulate<__nv_bfloat16>(f[j], ptx::ld_cg_v4(res + goff));
                     if (res_out) {
@@ -335,6 +357,7 @@ __device__ __forceinline__ void gemm_ar_body(const GemmArArgs& a, const CUtensor
             }
             ++rows_done;
         }
+        YALI_STAMP(6, 0);  // own rows reduced and written
         // Two-shot: tell every rank how many of its output rows this CTA delivered.
         if (!a.oneshot) {
             __syncthreads();
@@ -355,6 +378,8 @@ __device__ __forceinline__ void gemm_ar_body(const GemmArArgs& a, const CUtensor
         __syncthreads();
         if (s_abort) return;
     }
+    YALI_STAMP(7, 0);  // output complete
+#undef YALI_STAMP
     if (tid == 0 && check_out_last(cv, 3, nctas)) {
         advance_call_word(cv, kCallGemmEpoch, 1);
         advance_call_word(cv, kCallGemmCnt, a.cnt_inc);

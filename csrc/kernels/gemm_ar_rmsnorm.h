@@ -30,6 +30,7 @@ struct alignas(64) GemmArArgs {
     uint32_t cnt_inc;         // arrivals per source that complete this rank's partial rows in this call
     uint32_t done_inc[kMaxRanks];  // per owner: rows it delivers to every rank's output in this call
     float eps;
+    unsigned long long* trace;  // optional: 8 x %globaltimer of CTA 0 at the phase boundaries (debugging aid)
 };
 
 struct GemmArEmuArgs {

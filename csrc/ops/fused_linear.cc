@@ -171,6 +171,7 @@ Result FusedLinearAllReduceRmsNorm(Communicator& comm, const FusedLinearDesc* de
         a.cnt_inc = arrivals[rank];
         for (int q = 0; q < W; ++q) a.done_inc[q] = rows_of[q];
         a.eps = opt.eps;
+        a.trace = opt.trace ? opt.trace[i] : nullptr;
     }
     if (comm.emulated()) {
         GemmArEmuArgs* e = new GemmArEmuArgs();

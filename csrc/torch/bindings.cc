@@ -277,7 +277,8 @@ class PyComm {
     // out = RMSNorm(residual + sum_r x_r @ w_r^T) * norm_weight, one kernel per rank.
     void FusedLinear(std::vector<at::Tensor> x, std::vector<at::Tensor> w, std::vector<at::Tensor> norm_weight,
                      std::vector<at::Tensor> out, c10::optional<std::vector<at::Tensor>> residual,
-                     c10::optional<std::vector<at::Tensor>> residual_out, double eps, int force_oneshot, int ctas) {
+                     c10::optional<std::vector<at::Tensor>> residual_out, double eps, int force_oneshot, int ctas,
+                     c10::optional<std::vector<at::Tensor>> trace) {
         at::ScalarType d;
         int64_t n;
         CheckTensors(x, "x", &d, &n);
@@ -314,6 +315,16 @@ class PyComm {
         o.force_oneshot = force_oneshot;
         o.ctas = ctas;
         o.eps = static_cast<float>(eps);
+        std::vector<unsigned long long*> tr(nl, nullptr);
+        if (trace.has_value()) {
+            TORCH_CHECK(static_cast<int>(trace->size()) == nl, "yali: one trace tensor per local rank");
+            for (int i = 0; i < nl; ++i) {
+                TORCH_CHECK((*trace)[i].scalar_type() == at::kLong && (*trace)[i].numel() >= 8 && (*trace)[i].is_cuda(),
+                            "yali: trace tensors are int64 CUDA tensors with 8 elements");
+                tr[i] = reinterpret_cast<unsigned long long*>((*trace)[i].data_ptr());
+            }
+            o.trace = tr.data();
+        }
         auto st = Streams();
         c10::cuda::OptionalCUDAGuard guard(c().device_of(0));
         Throw(FusedLinearAllReduceRmsNorm(c(), descs.data(), static_cast<uint32_t>(T), static_cast<uint32_t>(N),
@@ -480,7 +491,7 @@ PYBIND11_MODULE(_C, m) {
              py::arg("slot_bytes") = 0)
         .def("fused_linear", &PyComm::FusedLinear, py::arg("x"), py::arg("w"), py::arg("norm_weight"), py::arg("out"),
              py::arg("residual") = py::none(), py::arg("residual_out") = py::none(), py::arg("eps") = 1e-5,
-             py::arg("force_oneshot") = -1, py::arg("ctas") = 0)
+             py::arg("force_oneshot") = -1, py::arg("ctas") = 0, py::arg("trace") = py::none())
         .def("symm_empty", &PyComm::SymmEmpty, py::arg("shape"), py::arg("dtype"))
         .def("symm_reset", &PyComm::SymmReset)
         .def("sync", &PyComm::Sync)
