@@ -22,13 +22,15 @@ $(LIB):
 $(BIN):
 	mkdir -p $(BIN)
 
-BENCH := $(BIN)/benchmark_yali $(BIN)/benchmark_yali_mpi
+BENCH := $(BIN)/benchmark_yali $(BIN)/benchmark_yali_mpi $(BIN)/p2p_bandwidth
 BENCH_NCCL := $(BIN)/benchmark_nccl $(BIN)/benchmark_nccl_mpi
 bench: $(BENCH) $(BENCH_NCCL)
 $(BIN)/benchmark_yali: bench/benchmark_yali.cu bench/bench_common.h $(LIB) | $(BIN)
 	$(NVCC) $(NVFLAGS) $< -o $@ $(LINK)
 $(BIN)/benchmark_yali_mpi: bench/benchmark_yali_mpi.cu bench/bench_common.h $(LIB) | $(BIN)
 	$(NVCC) $(NVFLAGS) $< -o $@ $(LINK)
+$(BIN)/p2p_bandwidth: bench/p2p_bandwidth.cu | $(BIN)
+	$(NVCC) $(NVFLAGS) $< -o $@
 $(BIN)/benchmark_nccl: bench/benchmark_nccl.cu bench/bench_common.h $(LIB) | $(BIN)
 	$(NVCC) $(NVFLAGS) $< -o $@ $(LINK) -lnccl
 $(BIN)/benchmark_nccl_mpi: bench/benchmark_nccl_mpi.cu bench/bench_common.h $(LIB) | $(BIN)
