@@ -127,6 +127,21 @@ def time_steps(comm, torch, fn, steps: int, warmup: int):
     return gather_max(comm, total), per
 
 
+def time_steps_batched(comm, torch, fn, steps: int):
+    """`steps` calls back to back with ONE event pair; returns (total_ms max over ranks, None)."""
+    comm.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps):
+        fn(i)
+    e1.record()
+    torch.cuda.synchronize()
+    comm.barrier()
+    comm.check()
+    return gather_max(comm, e0.elapsed_time(e1)), None
+
+
 def percentile(xs, q):
     s = sorted(xs)
     if not s:
@@ -195,6 +210,27 @@ def run_own(args) -> dict:
     p50, p99 = percentile(lat, 50), percentile(lat, 99)
     p50 = gather_max(comm, p50)
     p99 = gather_max(comm, p99)
+    # The same calls without an event between them (the events keep consecutive launches from
+    # overlapping), and as one CUDA-graph replay (no host launch work at all).
+    batch_ms, _ = time_steps_batched(comm, torch, small_step, lat_steps)
+    graph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            for i in range(lat_steps):
+                small_step(i)
+    graph.replay()
+    torch.cuda.synchronize()
+    comm.barrier()
+    g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    g0.record()
+    graph.replay()
+    g1.record()
+    torch.cuda.synchronize()
+    comm.barrier()
+    comm.check()
+    graph_us = gather_max(comm, g0.elapsed_time(g1) * 1e3 / lat_steps)
+    del graph
 
     # ---- end to end through the public API: pinned H2D, all-reduce, D2H of the result ----
     n_local = len(aslist(send))
@@ -248,7 +284,10 @@ def run_own(args) -> dict:
             "baseline": "reference README: 79.2 GB/s at 128 MB fp32 on 2x A100 NV4",
         },
         "latency_1MiB_us": {"p50": round(p50 * 1e3, 2), "p99": round(p99 * 1e3, 2),
-                            "p99_over_p50": round(p99 / p50, 3) if p50 else None, "samples": lat_steps},
+                            "p99_over_p50": round(p99 / p50, 3) if p50 else None, "samples": lat_steps,
+                            "avg_back_to_back": round(batch_ms * 1e3 / lat_steps, 2),
+                            "avg_cuda_graph": round(graph_us, 2),
+                            "note": "p50/p99: one event pair per call; the averages: one pair around all calls"},
         "e2e": {"value": round(e2e_busbw, 2), "unit": "GB/s", "h2d_bytes_per_step": MESSAGE_BYTES * n_local,
                 "d2h_bytes_per_step": MESSAGE_BYTES * n_local, "steps": e2e_steps},
         "gpu_launches": int(launches),

@@ -298,6 +298,22 @@ __device__ __forceinline__ void gemm_ar_body(const GemmArArgs& a, const CUtensor
         uint32_t rows_done = 0;
         for (uint32_t lr = cta; lr < my_rows; lr += nctas) {
             const uint32_t grow = row_lo + lr;
+            // Every load of the row (W partial vectors, residual, weight, for each of this thread's
+            // vectors) is issued before the first one is consumed: one memory round trip per row.
+            uint4 part[kGemmMaxVecPerThread][kMaxRanks], rv[kGemmMaxVecPerThread], wv[kGemmMaxVecPerThread];
+#pragma unroll
+            for (int j = 0; j < kGemmMaxVecPerThread; ++j) {
+                const uint32_t c = tid + j * blockDim.x;
+                if (c < vec_per_row) {
+                    const uint64_t off = (static_cast<uint64_t>(lr) * a.N + static_cast<uint64_t>(c) * VEC) * 2;
+                    const uint64_t goff = (static_cast<uint64_t>(grow) * a.N + static_cast<uint64_t>(c) * VEC) * 2;
+#pragma unroll
+                    for (int q = 0; q < kMaxRanks; ++q)
+                        if (q < W) part[j][q] = ptx::ld_cg_v4(landing(a, r, q, parity) + off);
+                    rv[j] = res ? ptx::ld_cg_v4(res + goff) : make_uint4(0, 0, 0, 0);
+                    wv[j] = *reinterpret_cast<const uint4*>(wgt + static_cast<uint64_t>(c) * 16);
+                }
+            }
             float f[kGemmMaxVecPerThread][VEC];
             float ss = 0.f;
 #pragma unroll
@@ -306,18 +322,12 @@ __device__ __forceinline__ void gemm_ar_body(const GemmArArgs& a, const CUtensor
                 if (c < vec_per_row) {
 #pragma unroll
                     for (int i = 0; i < VEC; ++i) f[j][i] = 0.f;
-                    const uint64_t off = (static_cast<uint64_t>(lr) * a.N + static_cast<uint64_t>(c) * VEC) * 2;
-                    // All sources' loads are issued before the first one is consumed.
-                    uint4 part[kMaxRanks];
 #pragma unroll
                     for (int q = 0; q < kMaxRanks; ++q)
-                        if (q < W) part[q] = ptx::ld_cg_v4(landing(a, r, q, parity) + off);
-#pragma unroll
-                    for (int q = 0; q < kMaxRanks; ++q)
-                        if (q < W) accumulate<__nv_bfloat16>(f[j], part[q]);
-                    const uint64_t goff = (static_cast<uint64_t>(grow) * a.N + static_cast<uint64_t>(c) * VEC) * 2;
-                    if (res) accumulate<__nv_bfloat16>(f[j], ptx::ld_cg_v4(res + goff));
+                        if (q < W) accumulate<__nv_bfloat16>(f[j], part[j][q]);
+                    if (res) accumulate<__nv_bfloat16>(f[j], rv[j]);
                     if (res_out) {
+                        const uint64_t goff = (static_cast<uint64_t>(grow) * a.N + static_cast<uint64_t>(c) * VEC) * 2;
                         const uint4 pre = pack16<__nv_bfloat16>(f[j]);
                         if (a.oneshot) {
                             ptx::st_v4(res_out + goff, pre);
@@ -340,7 +350,7 @@ __device__ __forceinline__ void gemm_ar_body(const GemmArArgs& a, const CUtensor
                     float w[VEC];
 #pragma unroll
                     for (int i = 0; i < VEC; ++i) w[i] = 0.f;
-                    accumulate<__nv_bfloat16>(w, *reinterpret_cast<const uint4*>(wgt + static_cast<uint64_t>(c) * 16));
+                    accumulate<__nv_bfloat16>(w, wv[j]);
 #pragma unroll
                     for (int i = 0; i < VEC; ++i) f[j][i] = f[j][i] * inv_rms * w[i];
                     const uint4 y = pack16<__nv_bfloat16>(f[j]);
