@@ -111,13 +111,17 @@ def main():
         outs = outs if isinstance(outs, list) else [outs]
         one = (lambda v: v if nl > 1 else v[0])
         arms = {}
-        for label, oneshot in (("fused_oneshot", True), ("fused_twoshot", False)):
+        has_nvls = bool(comm.has_multicast) and not comm.emulated_ranks
+        for label, oneshot, nvls in (("fused_oneshot", True, False), ("fused_twoshot", False, False),
+                                     ("fused_twoshot_nvls", False, True)):
             if oneshot and T * N * 2 > comm.layout()["gemm_cap"]:
                 continue
             if not oneshot and -(-T // W) * N * 2 > comm.layout()["gemm_cap"]:
                 continue
-            arms[label] = lambda oneshot=oneshot: comm.fused_linear_rmsnorm(one(xs), one(ws), one(nw), one(res),
-                                                                             out=one(outs), oneshot=oneshot)
+            if nvls and not has_nvls:
+                continue
+            arms[label] = lambda oneshot=oneshot, nvls=nvls: comm.fused_linear_rmsnorm(
+                one(xs), one(ws), one(nw), one(res), out=one(outs), oneshot=oneshot, nvls=nvls)
         arms["gemm+ar_norm"] = lambda: tp.unfused_row_parallel(comm, xs, ws, nw, res) if nl > 1 else \
             comm.all_reduce_rmsnorm(xs[0] @ ws[0].T, nw[0], res[0])
         if use_nccl:

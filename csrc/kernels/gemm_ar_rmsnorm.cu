@@ -23,6 +23,12 @@
 // (two-shot: rows are sharded over the ranks), or, for few rows, every rank owns
 // all rows and writes only its own output (one-shot).  A final counter tells each
 // rank when all rows of its output have arrived.
+// NVLS form of the two-shot (ranks joined by an NVSwitch multicast object): the
+// epilogue keeps the partial rows in this rank's OWN landing zone, so phase 1 has no
+// peer stores at all; the owner of a row reads the sum over all ranks with one
+// multimem.ld_reduce per 16 bytes (fp32 accumulation in the switch) and delivers the
+// normalised row to every rank with one multimem.st.  Per rank that moves T*N*2/W
+// bytes in and out instead of (W-1)/W * T*N*2 each way.
 //
 // Parity: none in the reference (it has no GEMM, no fused op and no tensor-core
 // code; see its src/kernels and src/all_reduce).  The unfused composition (library
@@ -72,6 +78,11 @@ __device__ __forceinline__ bool mbar_wait_deadline(uint64_t* bar, uint32_t parit
 __device__ __forceinline__ char* landing(const GemmArArgs& a, int on_rank, int src, uint32_t parity) {
     return a.cv.heap[on_rank] + a.cv.lay.gemm_off +
            (static_cast<uint64_t>(parity) * a.cv.world + src) * a.cv.lay.gemm_cap;
+}
+
+// NVLS form: one [T, N] bf16 image per call parity at the same offset of every rank's heap.
+__device__ __forceinline__ uint64_t landing_nvls_off(const GemmArArgs& a, uint32_t parity) {
+    return a.cv.lay.gemm_off + static_cast<uint64_t>(parity) * a.cv.world * a.cv.lay.gemm_cap;
 }
 
 __device__ __forceinline__ void gemm_ar_body(const GemmArArgs& a, const CUtensorMap* tmap_a, const CUtensorMap* tmap_b,
@@ -239,7 +250,9 @@ __device__ __forceinline__ void gemm_ar_body(const GemmArArgs& a, const CUtensor
                     const uint4 x = *reinterpret_cast<const uint4*>(stage + row_in_warp * (BN * 2) +
                                                                     ((c16 ^ (row_in_warp & 15)) << 4));
                     const uint64_t col_off = (static_cast<uint64_t>(nt) * BN) * 2 + c16 * 16;
-                    if (a.oneshot) {
+                    if (a.nvls) {
+                        ptx::st_v4(cv.heap[r] + landing_nvls_off(a, parity) + static_cast<uint64_t>(grow) * a.N * 2 + col_off, x);
+                    } else if (a.oneshot) {
                         for (int k = 0; k < W; ++k) {
                             const int d = (r + k) % W;
                             ptx::st_v4(landing(a, d, r, parity) + static_cast<uint64_t>(grow) * a.N * 2 + col_off, x);
@@ -296,6 +309,71 @@ __device__ __forceinline__ void gemm_ar_body(const GemmArArgs& a, const CUtensor
         const char* wgt = static_cast<const char*>(a.norm_weight);
         const float inv_n = 1.f / static_cast<float>(a.N);
         uint32_t rows_done = 0;
+        if (a.nvls) {
+            // The switch adds the W copies of a row (fp32 accumulation, bf16 result); two rows are in
+            // flight per CTA so that their round trips through the switch overlap.
+            constexpr int R = 2;
+            const uint32_t rows_at_once = my_rows > nctas ? R : 1;  // few rows: one per CTA, on more CTAs
+            const char* mc_in = cv.mc_heap + landing_nvls_off(a, parity);
+            for (uint32_t lr0 = cta * rows_at_once; lr0 < my_rows; lr0 += nctas * rows_at_once) {
+                uint4 sum[R][kGemmMaxVecPerThread], rv[R][kGemmMaxVecPerThread], wv[kGemmMaxVecPerThread];
+#pragma unroll
+                for (int j = 0; j < kGemmMaxVecPerThread; ++j) {
+                    const uint32_t c = tid + j * blockDim.x;
+                    if (c < vec_per_row) {
+#pragma unroll
+                        for (int u = 0; u < R; ++u) {
+                            if (u < rows_at_once && lr0 + u < my_rows) {
+                                const uint64_t goff =
+                                    (static_cast<uint64_t>(row_lo + lr0 + u) * a.N + static_cast<uint64_t>(c) * VEC) * 2;
+                                sum[u][j] = ptx::multimem_ld_reduce_bf16x8(mc_in + goff);
+                                rv[u][j] = res ? ptx::ld_cg_v4(res + goff) : make_uint4(0, 0, 0, 0);
+                            }
+                        }
+                        wv[j] = *reinterpret_cast<const uint4*>(wgt + static_cast<uint64_t>(c) * 16);
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < R; ++u) {
+                    if (u >= rows_at_once || lr0 + u >= my_rows) break;  // same for the whole CTA
+                    const uint32_t grow = row_lo + lr0 + u;
+                    float f[kGemmMaxVecPerThread][VEC];
+                    float ss = 0.f;
+#pragma unroll
+                    for (int j = 0; j < kGemmMaxVecPerThread; ++j) {
+                        const uint32_t c = tid + j * blockDim.x;
+                        if (c < vec_per_row) {
+#pragma unroll
+                            for (int i = 0; i < VEC; ++i) f[j][i] = 0.f;
+                            accumulate<__nv_bfloat16>(f[j], sum[u][j]);
+                            if (res) accumulate<__nv_bfloat16>(f[j], rv[u][j]);
+                            if (a.residual_out_mc) {
+                                const uint64_t goff = (static_cast<uint64_t>(grow) * a.N + static_cast<uint64_t>(c) * VEC) * 2;
+                                ptx::multimem_st_v4(a.residual_out_mc + goff, pack16<__nv_bfloat16>(f[j]));
+                            }
+#pragma unroll
+                            for (int i = 0; i < VEC; ++i) ss += f[j][i] * f[j][i];
+                        }
+                    }
+                    const float inv_rms = rsqrtf(block_sum(ss, s_red) * inv_n + a.eps);
+#pragma unroll
+                    for (int j = 0; j < kGemmMaxVecPerThread; ++j) {
+                        const uint32_t c = tid + j * blockDim.x;
+                        if (c < vec_per_row) {
+                            float w[VEC];
+#pragma unroll
+                            for (int i = 0; i < VEC; ++i) w[i] = 0.f;
+                            accumulate<__nv_bfloat16>(w, wv[j]);
+#pragma unroll
+                            for (int i = 0; i < VEC; ++i) f[j][i] = f[j][i] * inv_rms * w[i];
+                            const uint64_t goff = (static_cast<uint64_t>(grow) * a.N + static_cast<uint64_t>(c) * VEC) * 2;
+                            ptx::multimem_st_v4(a.out_mc + goff, pack16<__nv_bfloat16>(f[j]));
+                        }
+                    }
+                    ++rows_done;
+                }
+            }
+        } else
         for (uint32_t lr = cta; lr < my_rows; lr += nctas) {
             const uint32_t grow = row_lo + lr;
             // Every load of the row (W partial vectors, residual, weight, for each of this thread's

@@ -30,6 +30,12 @@ struct alignas(64) GemmArArgs {
     uint32_t cnt_inc;         // arrivals per source that complete this rank's partial rows in this call
     uint32_t done_inc[kMaxRanks];  // per owner: rows it delivers to every rank's output in this call
     float eps;
+    // NVLS form of the two-shot (nvls != 0): every rank keeps its partial rows in its OWN landing
+    // zone, the owner of a row sums all ranks' copies in the switch (multimem.ld_reduce) and
+    // writes the normalised row to every rank with one multimem.st through these addresses.
+    uint32_t nvls;
+    char* out_mc;           // multicast address of out
+    char* residual_out_mc;  // multicast address of residual_out, or nullptr
     unsigned long long* trace;  // optional: 8 x %globaltimer of CTA 0 at the phase boundaries (debugging aid)
 };
 

@@ -1,5 +1,7 @@
 #include "fused_linear.h"
 
+#include "../core/env.h"
+
 #include <algorithm>
 #include <cstring>
 
@@ -90,6 +92,36 @@ Result FusedLinearAllReduceRmsNorm(Communicator& comm, const FusedLinearDesc* de
         }
     }
 
+    // NVLS form of the two-shot: needs the multicast mapping and out / residual_out at one common
+    // heap offset on every rank (tensors from SymmAlloc are), and the [T, N] image must fit the
+    // landing region of one call parity.
+    bool nvls = false;
+    uint64_t mc_out_off = 0, mc_res_out_off = 0;
+    // Measured on 2 x B200 the switch form loses to the peer pushes (which overlap the GEMM), so
+    // it is the default only from 4 ranks, where it moves (W-1) times fewer bytes per rank.
+    const long long nvls_env = env::GetInt("YALI_GEMM_NVLS", -1);
+    const int nvls_want = opt.nvls >= 0 ? opt.nvls : (nvls_env >= 0 ? static_cast<int>(nvls_env != 0) : (W >= 4 ? -1 : 0));
+    if (!oneshot && !comm.emulated() && W > 1 && nvls_want != 0) {
+        nvls = comm.View(0).mc_heap != nullptr && static_cast<uint64_t>(T) * row_bytes <= lay.gemm_cap * W;
+        for (int i = 0; i < nlocal && nvls; ++i) {
+            const char* base = comm.View(i).heap[comm.rank_of(i)];
+            if (!comm.IsSymmetric(i, descs[i].out, static_cast<uint64_t>(T) * row_bytes)) nvls = false;
+            const uint64_t off = static_cast<const char*>(descs[i].out) - base;
+            if (i == 0) mc_out_off = off;
+            else if (off != mc_out_off) nvls = false;
+            if (descs[i].residual_out) {
+                if (!comm.IsSymmetric(i, descs[i].residual_out, static_cast<uint64_t>(T) * row_bytes)) nvls = false;
+                const uint64_t roff = static_cast<const char*>(descs[i].residual_out) - base;
+                if (i == 0) mc_res_out_off = roff;
+                else if (roff != mc_res_out_off) nvls = false;
+            }
+        }
+        if (!nvls && nvls_want == 1)
+            return fail(Result::Unsupported, "NVLS fused linear needs the multicast mapping and symmetric out tensors");
+    } else if (nvls_want == 1) {
+        return fail(Result::Unsupported, "NVLS fused linear is a two-shot form for real multi-GPU communicators");
+    }
+
     const uint32_t ntm = (T + kGemmTileM - 1) / kGemmTileM, ntn = N / kGemmTileN;
     // Arrivals owner q expects from every source in this call, and rows owner q delivers.
     uint32_t arrivals[kMaxRanks] = {}, rows_of[kMaxRanks] = {};
@@ -171,6 +203,11 @@ Result FusedLinearAllReduceRmsNorm(Communicator& comm, const FusedLinearDesc* de
         a.cnt_inc = arrivals[rank];
         for (int q = 0; q < W; ++q) a.done_inc[q] = rows_of[q];
         a.eps = opt.eps;
+        a.nvls = nvls ? 1u : 0u;
+        if (nvls) {
+            a.out_mc = a.cv.mc_heap + mc_out_off;
+            a.residual_out_mc = d.residual_out ? a.cv.mc_heap + mc_res_out_off : nullptr;
+        }
         a.trace = opt.trace ? opt.trace[i] : nullptr;
     }
     if (comm.emulated()) {

@@ -25,6 +25,7 @@ struct FusedLinearOptions {
     int force_oneshot = -1;  // -1: by size; 0: two-shot; 1: one-shot
     int ctas = 0;            // 0: as many as are resident
     float eps = 1e-5f;
+    int nvls = -1;           // two-shot through the NVSwitch multicast object: -1 when available, 0 never, 1 required
     unsigned long long* const* trace = nullptr;  // per local rank: device buffer of 8 timestamps, or nullptr
 };
 

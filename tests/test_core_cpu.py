@@ -56,7 +56,7 @@ def test_tuning_functions_sane(native_lib):
             assert 1 <= s_lanes <= 256
             slot = lib.yali_c_auto_slot_bytes(b, world)
             assert 8 * 1024 <= slot <= 256 * 1024 and slot % 256 == 0
-    assert lib.yali_c_flash_crossover_bytes(FP32, 2) == 64 * MiB  # same crossover as the reference at two ranks
+    assert 32 * MiB <= lib.yali_c_flash_crossover_bytes(FP32, 2) < 64 * MiB  # measured: two-shot wins from 64 MiB
     assert lib.yali_c_clamp_slot_bytes(100, 1 << 20) == 256
     assert lib.yali_c_clamp_slot_bytes(1 << 30, 1 << 16) == 1 << 16
     assert lib.yali_c_auto_ctas_per_lane(0, 16, 1 << 20, 2048) == 1

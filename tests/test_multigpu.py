@@ -92,7 +92,9 @@ def _rank_main(rank, world, port, q, scenario):
         import yali_b200 as yl
         from yali_b200 import _native as nat
         ext = nat.ext()
-        comm = yl.Comm.from_env(heap_bytes=2 << 30, timeout_ms=3000)
+        # A rank that leaves must not hold memory bound to an NVSwitch multicast object.
+        comm = yl.Comm.from_env(heap_bytes=2 << 30, timeout_ms=3000,
+                                want_multicast=scenario != "leave_between_steps")
         dev = f"cuda:{comm.device}"
         info = {"kind": comm.heap_kind, "mc": comm.has_multicast}
         ok = True
@@ -122,6 +124,38 @@ def _rank_main(rank, world, port, q, scenario):
             full = comm.all_gather(sh, n)
             comm.sync()
             ok &= ext.validate_sum(full, torch.float32, 1, 99, world)["mismatches"] == 0
+        elif scenario == "fused_linear":
+            # Row-parallel GEMM + all-reduce + residual + RMSNorm in one kernel per rank: the push
+            # forms and (with a multicast object) the in-switch form against an fp32 reference.
+            N, K = 1024, 256
+            for T in (1, 100, 300, 1000):
+                gens = [torch.Generator().manual_seed(4321 + 17 * q + T) for q in range(world)]
+                xs = [torch.randn(T, K, generator=g).to(torch.bfloat16) for g in gens]
+                ws = [(torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16) for g in gens]
+                res = torch.randn(T, N, generator=torch.Generator().manual_seed(5)).to(torch.bfloat16)
+                nw = (1 + 0.1 * torch.randn(N, generator=torch.Generator().manual_seed(6))).to(torch.bfloat16)
+                h = sum(x.float() @ w.float().T for x, w in zip(xs, ws)) + res.float()
+                want = h * torch.rsqrt(h.pow(2).mean(-1, keepdim=True) + 1e-5) * nw.float()
+                x, w = xs[rank].to(dev), ws[rank].to(dev)
+                forms = [(True, False), (False, False)] + ([(False, True)] if comm.has_multicast else [])
+                for oneshot, nvls in forms:
+                    out = comm.symm_empty([T, N], torch.bfloat16)
+                    ro = comm.symm_empty([T, N], torch.bfloat16)
+                    for _ in range(3):  # both call parities, and a repeat
+                        out.zero_()
+                        comm.sync()
+                        comm.barrier()
+                        comm.fused_linear_rmsnorm(x, w, nw.to(dev), res.to(dev), out=out, residual_out=ro,
+                                                  oneshot=oneshot, nvls=nvls)
+                        comm.sync()
+                        err = (out.float().cpu() - want).abs().max().item()
+                        err_h = (ro.float().cpu() - h).abs().max().item()
+                        good = err < 0.08 and err_h < 0.06 * max(1.0, h.abs().max().item())
+                        if not good:
+                            info[f"T{T}_one{int(oneshot)}_nvls{int(nvls)}"] = (err, err_h)
+                        ok &= good
+                        comm.barrier()  # nobody clears `out` while a peer still writes rows into it
+                comm.symm_reset()
         elif scenario == "leave_between_steps":
             x = torch.empty(65536, dtype=torch.float32, device=dev)
             ext.fill_random(x, 0, 1234 + rank)
@@ -180,6 +214,13 @@ def test_one_process_per_gpu(world, free_port):
     assert len(res) == world, res
     assert all(ok for ok, _ in res.values()), res
     assert all(info["kind"] in ("cumem-fd", "cuda-ipc") for _, info in res.values())
+
+
+@pytest.mark.parametrize("world", _worlds())
+def test_fused_linear_one_process_per_gpu(world, free_port):
+    res = _spawn(world, "fused_linear", free_port + 2)
+    assert len(res) == world, res
+    assert all(ok for ok, _ in res.values()), res
 
 
 def test_rank_that_stops_between_steps_times_out_the_others(free_port, monkeypatch):

@@ -170,12 +170,15 @@ class Comm:
     def fused_linear_rmsnorm(self, x: TensorOrList, w: TensorOrList, norm_weight: TensorOrList,
                              residual: Optional[TensorOrList] = None, *, eps: float = 1e-5,
                              out: Optional[TensorOrList] = None, residual_out: Optional[TensorOrList] = None,
-                             oneshot: Optional[bool] = None, ctas: int = 0, trace: Optional[TensorOrList] = None):
+                             oneshot: Optional[bool] = None, ctas: int = 0, trace: Optional[TensorOrList] = None,
+                             nvls: Optional[bool] = None):
         """out = RMSNorm(residual + sum over ranks of x @ w.T) * norm_weight in ONE kernel per rank
         (tcgen05 GEMM whose epilogue pushes partial rows to their owner over NVLink, then reduce + norm).
         x: [T, K], w: [N, K] (this rank's slice, nn.Linear layout), bf16.  With one GPU per process the
         two-shot form (T above a few dozen rows) needs `out` from symm_empty().  `trace`: int64 CUDA
-        tensor(s) of 8 elements that receive CTA 0's %globaltimer at the phase boundaries."""
+        tensor(s) of 8 elements that receive CTA 0's %globaltimer at the phase boundaries.  `nvls`: the
+        two-shot form sums and delivers rows through the NVSwitch multicast object when it exists and
+        `out` is symmetric (None), never (False), or must (True)."""
         xs, ws, nws = self._as_list(x, "x"), self._as_list(w, "w"), self._as_list(norm_weight, "norm_weight")
         if out is None:
             T, N = xs[0].shape[0], ws[0].shape[0]
@@ -189,7 +192,8 @@ class Comm:
         ro = None if residual_out is None else self._as_list(residual_out, "residual_out")
         try:
             tr = None if trace is None else self._as_list(trace, "trace")
-            self._impl.fused_linear(xs, ws, nws, outs, res, ro, eps, -1 if oneshot is None else int(oneshot), ctas, tr)
+            self._impl.fused_linear(xs, ws, nws, outs, res, ro, eps, -1 if oneshot is None else int(oneshot), ctas, tr,
+                                    -1 if nvls is None else int(nvls))
         except RuntimeError as e:
             raise _translate(e) from None
         return self._like_input(x, outs)
