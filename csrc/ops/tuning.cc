@@ -245,6 +245,10 @@ Result MakePlan(int world, uint64_t count, Dtype in, Dtype out, int epilogue, Ke
     else if (forced == KernelMode::Stream) v = Variant::Stream;
     else if (forced == KernelMode::NVLS) v = bytes <= (128ull << 10) ? Variant::NvlsOneShot : Variant::NvlsTwoShot;
     else if (row) v = row->variant;
+    // Measured on 8 x B200 with symmetric buffers: the in-switch one-shot beats the peer-to-peer
+    // one-shot above a few KiB (7 peers to push to), so only the smallest messages stay with Flash.
+    else if (nvls_ok && caps.symmetric && world > 4 && bytes > (4ull << 10))
+        v = bytes <= (128ull << 10) ? Variant::NvlsOneShot : Variant::NvlsTwoShot;
     else if (bytes <= FlashCrossoverBytes(in, world)) v = Variant::Flash;
     else if (nvls_ok && world > 2) v = Variant::NvlsTwoShot;
     else v = Variant::Stream;
@@ -288,7 +292,9 @@ Result MakePlan(int world, uint64_t count, Dtype in, Dtype out, int epilogue, Ke
                 bytes <= LowLatencyMaxBytes(world)) {
                 p.flags |= kFlagLowLatency;
                 if (!(row && row->ctas) && dev_ctas <= 0)
-                    c = static_cast<uint32_t>(std::min<uint64_t>(std::max<uint64_t>(CeilDiv(bytes, 16ull << 10), 1), 64));
+                    // about 16 KiB of pushes per CTA (each CTA pushes its slice to world-1 peers)
+                    c = static_cast<uint32_t>(
+                        std::min<uint64_t>(std::max<uint64_t>(CeilDiv(bytes * (world - 1), 16ull << 10), 1), 64));
             }
             p.ctas = std::max<uint32_t>(1, std::min<uint32_t>(std::min<uint32_t>(c, max_ctas), kMaxFlashCtas));
             break;
