@@ -239,17 +239,16 @@ def run_own(args) -> dict:
     for h, t in zip(h_in, aslist(send)):
         h.copy_(t)
 
+    # The user's call for data that lives on the host: every step copies the whole input in from
+    # pinned memory and the whole result out; the copies of both directions and the all-reduce
+    # overlap chunk by chunk inside the call.
     def e2e_step(_i):
-        for h, t in zip(h_in, aslist(send)):
-            t.copy_(h, non_blocking=True)
-        comm.all_reduce(send, recv)
-        for h, t in zip(h_out, aslist(recv)):
-            h.copy_(t, non_blocking=True)
+        comm.all_reduce_host(h_in if n_local > 1 else h_in[0], h_out if n_local > 1 else h_out[0])
 
     e2e_steps = max(3, min(args.steps, 20))
     e2e_ms, _ = time_steps(comm, torch, e2e_step, e2e_steps, 3)
     e2e_busbw = MESSAGE_BYTES * bus_factor(ranks) / (e2e_ms / e2e_steps * 1e-3) / 1e9
-    ok = ok and bool(torch.equal(h_out[0], aslist(recv)[0].cpu()))
+    ok = ok and bool(torch.allclose(h_out[0], aslist(recv)[0].cpu(), rtol=1e-5, atol=1e-5))
     # Keep the GPU under the headline load until the sampler has a few readings.
     # (Same count on every rank: it is derived from the max-over-ranks step time.)
     for _ in range(max(1, min(5000, int(0.4 / max(ms_per_step * 1e-3, 1e-6))))):
@@ -289,7 +288,9 @@ def run_own(args) -> dict:
                             "avg_cuda_graph": round(graph_us, 2),
                             "note": "p50/p99: one event pair per call; the averages: one pair around all calls"},
         "e2e": {"value": round(e2e_busbw, 2), "unit": "GB/s", "h2d_bytes_per_step": MESSAGE_BYTES * n_local,
-                "d2h_bytes_per_step": MESSAGE_BYTES * n_local, "steps": e2e_steps},
+                "d2h_bytes_per_step": MESSAGE_BYTES * n_local, "steps": e2e_steps,
+                "api": "Comm.all_reduce_host(pinned_in, pinned_out): H2D, all-reduce and D2H of 8 MiB chunks "
+                       "overlap on three streams"},
         "gpu_launches": int(launches),
         "clocks": clocks,
     }

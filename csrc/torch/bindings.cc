@@ -17,6 +17,7 @@
 #include "comm/topology.h"
 #include "ops/buffer_ops.h"
 #include "ops/fused_linear.h"
+#include "ops/host_pipeline.h"
 #include "ops/tuning.h"
 
 namespace py = pybind11;
@@ -98,6 +99,7 @@ class PyComm {
 
     void Close() {
         py::gil_scoped_release nogil;
+        host_pipe_.reset();
         c_.reset();
     }
     Communicator& c() {
@@ -347,7 +349,44 @@ class PyComm {
         }
         return out;
     }
-    void SymmReset() { c().SymmReset(); }
+    void SymmReset() {
+        if (host_pipe_) host_pipe_->Invalidate();
+        c().SymmReset();
+    }
+
+    // dst = scale * sum over ranks of src, both in pinned host memory; copies and all-reduce
+    // overlap chunk by chunk (ops/host_pipeline.h).
+    void AllReduceHost(std::vector<at::Tensor> src, std::vector<at::Tensor> dst, int64_t chunk_bytes,
+                       c10::optional<double> scale, const std::string& mode) {
+        const int nl = c().nlocal();
+        TORCH_CHECK(static_cast<int>(src.size()) == nl && static_cast<int>(dst.size()) == nl,
+                    "yali: one src and one dst tensor per local rank");
+        const at::ScalarType d = src[0].scalar_type();
+        const int64_t n = src[0].numel();
+        std::vector<const void*> s(nl);
+        std::vector<void*> r(nl);
+        for (int i = 0; i < nl; ++i) {
+            for (const at::Tensor& t : {src[i], dst[i]}) {
+                TORCH_CHECK(!t.is_cuda() && t.is_pinned() && t.is_contiguous(),
+                            "yali: all_reduce_host takes contiguous tensors in pinned host memory");
+                TORCH_CHECK(t.scalar_type() == d && t.numel() == n, "yali: src and dst must agree in size and dtype");
+            }
+            s[i] = src[i].data_ptr();
+            r[i] = dst[i].data_ptr();
+        }
+        OpOptions o;
+        o.mode = ToMode(mode);
+        if (scale.has_value()) {
+            o.epilogue = kEpiScaleCast;
+            o.scale = static_cast<float>(*scale);
+        }
+        if (!host_pipe_) host_pipe_ = std::make_unique<HostPipeline>(c());
+        auto st = Streams();
+        c10::cuda::OptionalCUDAGuard guard(c().device_of(0));
+        Throw(host_pipe_->AllReduce(s.data(), r.data(), static_cast<uint64_t>(n), ToDtype(d), o,
+                                    static_cast<uint64_t>(std::max<int64_t>(chunk_bytes, 4096)), st.data()),
+              c().last_error());
+    }
 
     void Sync() {
         auto st = Streams();
@@ -392,6 +431,7 @@ class PyComm {
     }
 
     std::unique_ptr<Communicator> c_;
+    std::unique_ptr<HostPipeline> host_pipe_;
 };
 
 void FillRandomT(at::Tensor t, int dist, uint64_t seed) {
@@ -496,6 +536,8 @@ PYBIND11_MODULE(_C, m) {
              py::arg("nvls") = -1)
         .def("symm_empty", &PyComm::SymmEmpty, py::arg("shape"), py::arg("dtype"))
         .def("symm_reset", &PyComm::SymmReset)
+        .def("all_reduce_host", &PyComm::AllReduceHost, py::arg("src"), py::arg("dst"), py::arg("chunk_bytes") = 8 << 20,
+             py::arg("scale") = py::none(), py::arg("mode") = "auto")
         .def("sync", &PyComm::Sync)
         .def("check", &PyComm::Check)
         .def("reset", &PyComm::Reset)

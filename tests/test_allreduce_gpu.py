@@ -305,3 +305,23 @@ def test_rmsnorm_beyond_the_one_shot_capacity_uses_two_launches(comm):
     ref, _ = yali.reference.residual_rmsnorm(yali.reference.all_reduce_sum(xs), weight.cpu().double(), None, 1e-5)
     torch.testing.assert_close(outs[0][:256].cpu().double(), ref[:256], rtol=3e-2, atol=3e-2)
     torch.testing.assert_close(outs[-1][-256:].cpu().double(), ref[-256:], rtol=3e-2, atol=3e-2)
+
+
+@pytest.mark.parametrize("n,chunk_bytes", [(1000, 8 << 20), (3 * 65536 + 77, 65536 * 4), (1 << 20, 1 << 20)])
+def test_host_to_host_all_reduce_overlaps_copies_chunk_by_chunk(comm, n, chunk_bytes):
+    # pinned host tensors in, pinned host tensors out; more chunks than staging slots in the second case
+    g = torch.Generator(device="cpu").manual_seed(77)
+    srcs = [torch.rand(n, generator=g).sub_(0.5).pin_memory() for _ in range(comm.world)]
+    dsts = [torch.zeros(n).pin_memory() for _ in range(comm.world)]
+    want = torch.stack([s.double() for s in srcs]).sum(0)
+    for _ in range(2):  # the staging ring is reused by the second call
+        for d in dsts:
+            d.zero_()
+        comm.all_reduce_host(srcs, dsts, chunk_bytes=chunk_bytes)
+        torch.cuda.synchronize()
+        comm.check()
+        for d in dsts:
+            torch.testing.assert_close(d.double(), want, rtol=1e-5, atol=1e-5)
+    with pytest.raises(ValueError):
+        comm.all_reduce_host([torch.zeros(8) for _ in range(comm.world)])  # pageable memory
+    comm.symm_reset()

@@ -35,6 +35,9 @@ def _worker(rank, world, port, q):
     ok &= torch.allclose(shard.double()[:min(s, n - rank * s)], expect[rank * s:rank * s + s], rtol=1e-6, atol=1e-6)
     full = yali.all_gather(shard, n)
     ok &= torch.allclose(full.double(), expect, rtol=1e-6, atol=1e-6)
+    # host-to-host call: same surface as on a GPU box, nothing to stage on CPU
+    hh = yali.all_reduce_host(inputs[rank])
+    ok &= torch.allclose(hh.double(), expect, rtol=1e-6, atol=1e-6)
     # the torch.ops surface dispatches CPU tensors to the same path
     import yali_b200.ops.registry  # noqa: F401
     out2 = torch.ops.yali.all_reduce(inputs[rank])

@@ -41,6 +41,7 @@ LIB_SOURCES = [
     "ops/yali_api.cc",
     "sim/protocol_sim.cc",
     "ops/fused_linear.cc",
+    "ops/host_pipeline.cc",
     "capi/yali_c.cc",
     "kernels/flash_oneshot.cu",
     "kernels/stream_twoshot.cu",

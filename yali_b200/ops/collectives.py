@@ -28,6 +28,13 @@ def all_reduce_rmsnorm(x: torch.Tensor, weight: torch.Tensor, residual: Optional
     return _pick(comm).all_reduce_rmsnorm(x, weight, residual, eps=eps, out=out, residual_out=residual_out, mode=mode)
 
 
+def all_reduce_host(src: torch.Tensor, dst: Optional[torch.Tensor] = None, *, comm=None,
+                    chunk_bytes: int = 8 << 20, scale: Optional[float] = None) -> torch.Tensor:
+    """Sum over all ranks of a tensor in pinned host memory, result in pinned host memory; the copies in
+    both directions and the all-reduce overlap chunk by chunk (Comm.all_reduce_host)."""
+    return _pick(comm).all_reduce_host(src, dst, chunk_bytes=chunk_bytes, scale=scale)
+
+
 def reduce_scatter(x: torch.Tensor, *, comm=None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     return _pick(comm).reduce_scatter(x, out)
 

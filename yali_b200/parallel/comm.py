@@ -198,6 +198,30 @@ class Comm:
             raise _translate(e) from None
         return self._like_input(x, outs)
 
+    def all_reduce_host(self, src: TensorOrList, dst: Optional[TensorOrList] = None, *,
+                        chunk_bytes: int = 8 << 20, scale: Optional[float] = None, mode: str = "auto"):
+        """All-reduce of tensors that live in pinned host memory: dst = scale * sum over ranks of src.
+
+        The message is cut into chunks that move through three streams per GPU: host-to-device copy,
+        all-reduce, device-to-host copy.  Chunk i+1 is copied in while chunk i is reduced and chunk i-1
+        is copied out, so both PCIe directions and NVLink are busy at the same time and a call costs
+        about one direction's copy time instead of the sum of the three phases.  Staging is a ring of
+        three symmetric chunk buffers per direction, allocated on first use (every rank must make the
+        same calls).  The call returns with the work queued; the caller's current stream waits for it."""
+        srcs = self._as_list(src, "src")
+        if dst is None:
+            dsts = [torch.empty_like(t).pin_memory() for t in srcs]
+        else:
+            dsts = self._as_list(dst, "dst")
+        for t in list(srcs) + list(dsts):
+            if t.is_cuda or not t.is_pinned() or not t.is_contiguous():
+                raise ValueError("all_reduce_host takes contiguous tensors in pinned host memory")
+        try:
+            self._impl.all_reduce_host(srcs, dsts, int(chunk_bytes), scale, mode)
+        except RuntimeError as e:
+            raise _translate(e) from None
+        return self._like_input(src, dsts)
+
     def shard_elems(self, count: int) -> int:
         return _native.ext().shard_elems(count, self.world)
 
@@ -343,6 +367,11 @@ class GlooComm:
             return full
         recv.copy_(full)
         return recv
+
+    def all_reduce_host(self, src: torch.Tensor, dst: Optional[torch.Tensor] = None, *, chunk_bytes: int = 8 << 20,
+                        scale: Optional[float] = None, mode: str = "auto") -> torch.Tensor:
+        """Same call as Comm.all_reduce_host; on CPU the data is in host memory already."""
+        return self.all_reduce(src, dst, scale=scale)
 
     def sync(self) -> None:
         pass
