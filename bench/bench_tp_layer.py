@@ -112,8 +112,8 @@ def main():
         one = (lambda v: v if nl > 1 else v[0])
         arms = {}
         has_nvls = bool(comm.has_multicast) and not comm.emulated_ranks
-        for label, oneshot, nvls in (("fused_oneshot", True, False), ("fused_twoshot", False, False),
-                                     ("fused_twoshot_nvls", False, True)):
+        for label, oneshot, nvls in (("fused_oneshot", True, 0), ("fused_twoshot", False, 0),
+                                     ("fused_twoshot_nvls", False, 1), ("fused_twoshot_mcast", False, 2)):
             if oneshot and T * N * 2 > comm.layout()["gemm_cap"]:
                 continue
             if not oneshot and -(-T // W) * N * 2 > comm.layout()["gemm_cap"]:

@@ -15,8 +15,10 @@
 // warps 2..5 read a finished accumulator back with tcgen05.ld while the next tile's
 // MMAs run into the other one, round to bf16, transpose through swizzled shared
 // memory and PUSH every row straight into the landing zone of the rank that owns
-// that row (peer stores over NVLink), then bump that rank's arrival counter with
-// red.release.sys.
+// that row (peer stores over NVLink).  Warp 6 announces each pushed tile to the
+// owners with red.release.sys on their arrival counters: the fence in front of that
+// reduction waits for the peer stores to land, so it sits in a warp of its own and
+// the epilogue warps go straight on to the next tile.
 // Phase 2 (reduce): the same CTAs wait (bounded) until all ranks' partial rows for
 // the rows this rank owns have landed, add them in fp32 in rank order, add the
 // residual, normalise the row and write the bf16 result into EVERY rank's output
@@ -89,6 +91,7 @@ __device__ __forceinline__ void gemm_ar_body(const GemmArArgs& a, const CUtensor
                                              uint32_t cta, uint32_t nctas) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t full_bar[kStages], empty_bar[kStages], tmem_full_bar[2], tmem_empty_bar[2];
+    __shared__ __align__(8) uint64_t pushed_bar[2], announced_bar[2];  // epilogue warps -> announcer warp and back
     __shared__ uint32_t s_tmem;
     __shared__ volatile int s_abort;
     __shared__ float s_red[32];
@@ -124,6 +127,8 @@ __device__ __forceinline__ void gemm_ar_body(const GemmArArgs& a, const CUtensor
         for (int b = 0; b < 2; ++b) {
             ptx::mbar_init(&tmem_full_bar[b], 1);
             ptx::mbar_init(&tmem_empty_bar[b], kEpilogueWarps);
+            ptx::mbar_init(&pushed_bar[b], kEpilogueWarps);
+            ptx::mbar_init(&announced_bar[b], 1);
         }
         ptx::mbar_fence_init();
         ptx::tma_prefetch_desc(tmap_a);
@@ -148,7 +153,8 @@ __device__ __forceinline__ void gemm_ar_body(const GemmArArgs& a, const CUtensor
     const uint32_t mt_shift = a.oneshot ? 0u : (((static_cast<uint32_t>(r) + 1u) % W) * Rs / BM) % ntm;
 
     // ------------------------------------------------------------------ phase 1: GEMM tiles, warp-specialised
-    // warp 0: TMA producer; warp 1: MMA issuer; warps 2..5: epilogue (TMEM -> bf16 -> peers).
+    // warp 0: TMA producer; warp 1: MMA issuer; warps 2..5: epilogue (TMEM -> bf16 -> peers);
+    // warp 6: announcer (arrival counters of the owners).
     // Two TMEM accumulators of 128 columns alternate, so the MMAs of tile i+1 run while tile i
     // is read back and pushed.
     if (warp == 0) {
@@ -202,15 +208,36 @@ __device__ __forceinline__ void gemm_ar_body(const GemmArArgs& a, const CUtensor
                 ptx::tc_commit(&tmem_full_bar[b]);  // accumulator complete
             }
         }
+    } else if (warp == 6) {
+        // Announcer: when the four epilogue warps have issued the pushes of a tile, tell every owner
+        // that received rows of it.  red.release.sys orders the pushes (made visible to this warp by
+        // the mbarrier) before the counter; waiting for them costs an NVLink round trip, which this
+        // warp absorbs instead of the epilogue warps.
+        uint32_t it = 0;
+        for (uint32_t tile = cta; tile < ntiles; tile += nctas, ++it) {
+            const uint32_t mt = (tile / ntn + mt_shift) % ntm, b = it & 1u;
+            if (!mbar_wait_deadline(&pushed_bar[b], (it >> 1) & 1u, deadline)) {
+                if (lane == 0 && !s_abort) report_timeout(cv, kSiteMbar, r, cta, 5, it);
+                s_abort = 1;
+                break;
+            }
+            if (lane < W) {
+                const uint32_t row_lo = mt * BM, row_hi = min(a.T, row_lo + BM);
+                bool touched = a.oneshot != 0;
+                if (!touched)
+                    touched = static_cast<uint32_t>(lane) * Rs < row_hi && (static_cast<uint32_t>(lane) + 1) * Rs > row_lo;
+                if (touched) ptx::red_release_sys_add(flag_word(cv, lane, kGemmCntOff + r), 1u);
+            }
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(&announced_bar[b]);
+            if (it == 0) YALI_STAMP(3, 192);  // first tile pushed and announced
+        }
     } else {
         const int q = warp & 3;                       // TMEM lane quarter this warp may read
-        const int etid = tid - 2 * 32;                // 0..127 among the epilogue threads
         uint8_t* stage = smem + kStages * kStageBytes + q * (32 * BN * 2);  // 32 rows x 256 bytes per warp
         uint32_t it = 0;
         for (uint32_t tile = cta; tile < ntiles; tile += nctas, ++it) {
             const uint32_t mt = (tile / ntn + mt_shift) % ntm, nt = tile % ntn, b = it & 1u;
-            // (Only this wait decides whether the epilogue warps go on: all four see the same
-            // barrier, so they leave together and nobody is left alone at the named barrier below.)
             if (!mbar_wait_deadline(&tmem_full_bar[b], (it >> 1) & 1u, deadline)) {
                 if (lane == 0 && !s_abort) report_timeout(cv, kSiteMbar, r, cta, 3, it);
                 s_abort = 1;
@@ -263,17 +290,16 @@ __device__ __forceinline__ void gemm_ar_body(const GemmArArgs& a, const CUtensor
                     }
                 }
             }
-            // All four epilogue warps have issued their pushes of this tile (and are done with
-            // the staging buffer): one arrival per destination that received rows of it.
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            if (etid < W) {
-                const uint32_t row_lo = mt * BM, row_hi = min(a.T, row_lo + BM);
-                bool touched = a.oneshot != 0;
-                if (!touched)
-                    touched = static_cast<uint32_t>(etid) * Rs < row_hi && (static_cast<uint32_t>(etid) + 1) * Rs > row_lo;
-                if (touched) ptx::red_release_sys_add(flag_word(cv, etid, kGemmCntOff + r), 1u);
+            // This warp's pushes of the tile are issued: hand the tile to the announcer warp.  Its
+            // barrier for this parity must have been consumed for the tile before last (it has, unless
+            // the announcer lags two tiles behind).
+            if (it >= 2 && !mbar_wait_deadline(&announced_bar[b], ((it >> 1) - 1u) & 1u, deadline)) {
+                if (lane == 0 && !s_abort) report_timeout(cv, kSiteMbar, r, cta, 6, it);
+                s_abort = 1;
+                break;
             }
-            if (it == 0) YALI_STAMP(3, 64);  // first tile pushed and announced
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(&pushed_bar[b]);
         }
     }
 
@@ -409,6 +435,8 @@ __device__ __forceinline__ void gemm_ar_body(const GemmArArgs& a, const CUtensor
                         const uint4 pre = pack16<__nv_bfloat16>(f[j]);
                         if (a.oneshot) {
                             ptx::st_v4(res_out + goff, pre);
+                        } else if (a.residual_out_mc) {  // one store through the switch fills every rank's copy
+                            ptx::multimem_st_v4(a.residual_out_mc + goff, pre);
                         } else {  // the owner of the row fills every rank's copy
                             for (int k = 0; k < W; ++k) {
                                 char* dst = static_cast<char*>(a.residual_out_all[(r + k) % W]);
@@ -435,6 +463,8 @@ __device__ __forceinline__ void gemm_ar_body(const GemmArArgs& a, const CUtensor
                     const uint64_t goff = (static_cast<uint64_t>(grow) * a.N + static_cast<uint64_t>(c) * VEC) * 2;
                     if (a.oneshot) {
                         ptx::st_v4(static_cast<char*>(a.out[r]) + goff, y);
+                    } else if (a.out_mc) {
+                        ptx::multimem_st_v4(a.out_mc + goff, y);
                     } else {
                         for (int k = 0; k < W; ++k) {
                             const int d = (r + k) % W;

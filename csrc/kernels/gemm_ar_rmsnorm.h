@@ -12,8 +12,8 @@ namespace yali {
 
 constexpr int kGemmTileM = 128;
 constexpr int kGemmTileN = 128;
-constexpr int kGemmThreads = 192;  // TMA warp, MMA warp, four epilogue warps
-constexpr int kGemmMaxVecPerThread = 3;  // N <= 3 * 192 threads * 8 bf16 = 4608 (the host caps N at 4096)
+constexpr int kGemmThreads = 224;  // TMA warp, MMA warp, four epilogue warps, announcer warp
+constexpr int kGemmMaxVecPerThread = 3;  // N <= 3 * 224 threads * 8 bf16 = 5376 (the host caps N at 4096)
 
 struct alignas(64) GemmArArgs {
     CUtensorMap tmap_a;  // x  [T, K] bf16, box 64 x 128, 128-byte swizzle
@@ -33,8 +33,9 @@ struct alignas(64) GemmArArgs {
     // NVLS form of the two-shot (nvls != 0): every rank keeps its partial rows in its OWN landing
     // zone, the owner of a row sums all ranks' copies in the switch (multimem.ld_reduce) and
     // writes the normalised row to every rank with one multimem.st through these addresses.
+    // out_mc alone (nvls == 0) keeps the peer pushes of phase 1 and only delivers through the switch.
     uint32_t nvls;
-    char* out_mc;           // multicast address of out
+    char* out_mc;           // multicast address of out, or nullptr: write every rank's copy with peer stores
     char* residual_out_mc;  // multicast address of residual_out, or nullptr
     unsigned long long* trace;  // optional: 8 x %globaltimer of CTA 0 at the phase boundaries (debugging aid)
 };

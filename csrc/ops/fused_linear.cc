@@ -33,6 +33,10 @@ bool EncodeTileMap(const DriverApi* d, CUtensorMap* map, const void* base, uint6
 
 uint32_t FusedLinearOneShotMaxRows(int world) { return world <= 2 ? 256u : 32u; }
 
+// Which multicast form the two-shot takes by default (0 none, 1 in-switch reduce + multicast store,
+// 2 peer pushes + multicast store), from measurements on 2, 4 and 8 B200.
+int FusedLinearAutoMulticastMode(int world, uint32_t /*T*/) { return world >= 4 ? 1 : 0; }
+
 Result FusedLinearAllReduceRmsNorm(Communicator& comm, const FusedLinearDesc* descs, uint32_t T, uint32_t N,
                                    uint32_t K, const FusedLinearOptions& opt, const cudaStream_t* streams) {
     auto fail = [&](Result r, const std::string& what) {
@@ -92,35 +96,41 @@ Result FusedLinearAllReduceRmsNorm(Communicator& comm, const FusedLinearDesc* de
         }
     }
 
-    // NVLS form of the two-shot: needs the multicast mapping and out / residual_out at one common
-    // heap offset on every rank (tensors from SymmAlloc are), and the [T, N] image must fit the
-    // landing region of one call parity.
-    bool nvls = false;
+    // Forms of the two-shot that go through the NVSwitch multicast object: they need the multicast
+    // mapping and out / residual_out at one common heap offset on every rank (tensors from SymmAlloc
+    // are); the in-switch reduce also needs the [T, N] image to fit the landing region of one call
+    // parity.  Mode 1: in-switch reduce + multicast store; mode 2: peer pushes + multicast store.
+    int mc_mode = 0;
     uint64_t mc_out_off = 0, mc_res_out_off = 0;
-    // Measured on 2 x B200 the switch form loses to the peer pushes (which overlap the GEMM), so
-    // it is the default only from 4 ranks, where it moves (W-1) times fewer bytes per rank.
-    const long long nvls_env = env::GetInt("YALI_GEMM_NVLS", -1);
-    const int nvls_want = opt.nvls >= 0 ? opt.nvls : (nvls_env >= 0 ? static_cast<int>(nvls_env != 0) : (W >= 4 ? -1 : 0));
-    if (!oneshot && !comm.emulated() && W > 1 && nvls_want != 0) {
-        nvls = comm.View(0).mc_heap != nullptr && static_cast<uint64_t>(T) * row_bytes <= lay.gemm_cap * W;
-        for (int i = 0; i < nlocal && nvls; ++i) {
+    {
+        const long long nvls_env = env::GetInt("YALI_GEMM_NVLS", -1);
+        const int want = opt.nvls >= 0 ? opt.nvls : (nvls_env >= 0 ? static_cast<int>(nvls_env) : -1);
+        bool possible = !oneshot && !comm.emulated() && W > 1 && want != 0 && comm.View(0).mc_heap != nullptr;
+        for (int i = 0; i < nlocal && possible; ++i) {
             const char* base = comm.View(i).heap[comm.rank_of(i)];
-            if (!comm.IsSymmetric(i, descs[i].out, static_cast<uint64_t>(T) * row_bytes)) nvls = false;
+            if (!comm.IsSymmetric(i, descs[i].out, static_cast<uint64_t>(T) * row_bytes)) possible = false;
             const uint64_t off = static_cast<const char*>(descs[i].out) - base;
             if (i == 0) mc_out_off = off;
-            else if (off != mc_out_off) nvls = false;
+            else if (off != mc_out_off) possible = false;
             if (descs[i].residual_out) {
-                if (!comm.IsSymmetric(i, descs[i].residual_out, static_cast<uint64_t>(T) * row_bytes)) nvls = false;
+                if (!comm.IsSymmetric(i, descs[i].residual_out, static_cast<uint64_t>(T) * row_bytes)) possible = false;
                 const uint64_t roff = static_cast<const char*>(descs[i].residual_out) - base;
                 if (i == 0) mc_res_out_off = roff;
-                else if (roff != mc_res_out_off) nvls = false;
+                else if (roff != mc_res_out_off) possible = false;
             }
         }
-        if (!nvls && nvls_want == 1)
-            return fail(Result::Unsupported, "NVLS fused linear needs the multicast mapping and symmetric out tensors");
-    } else if (nvls_want == 1) {
-        return fail(Result::Unsupported, "NVLS fused linear is a two-shot form for real multi-GPU communicators");
+        const bool image_fits = static_cast<uint64_t>(T) * row_bytes <= lay.gemm_cap * W;
+        if (want > 0) {
+            if (!possible || (want == 1 && !image_fits))
+                return fail(Result::Unsupported,
+                            "the multicast forms of the fused linear need two-shot, the multicast mapping and symmetric out tensors");
+            mc_mode = want == 1 ? 1 : 2;
+        } else if (possible) {
+            mc_mode = FusedLinearAutoMulticastMode(W, T);
+            if (mc_mode == 1 && !image_fits) mc_mode = 2;
+        }
     }
+    const bool nvls = mc_mode == 1;
 
     const uint32_t ntm = (T + kGemmTileM - 1) / kGemmTileM, ntn = N / kGemmTileN;
     // Arrivals owner q expects from every source in this call, and rows owner q delivers.
@@ -204,7 +214,7 @@ Result FusedLinearAllReduceRmsNorm(Communicator& comm, const FusedLinearDesc* de
         for (int q = 0; q < W; ++q) a.done_inc[q] = rows_of[q];
         a.eps = opt.eps;
         a.nvls = nvls ? 1u : 0u;
-        if (nvls) {
+        if (mc_mode != 0) {
             a.out_mc = a.cv.mc_heap + mc_out_off;
             a.residual_out_mc = d.residual_out ? a.cv.mc_heap + mc_res_out_off : nullptr;
         }

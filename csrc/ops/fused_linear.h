@@ -25,7 +25,10 @@ struct FusedLinearOptions {
     int force_oneshot = -1;  // -1: by size; 0: two-shot; 1: one-shot
     int ctas = 0;            // 0: as many as are resident
     float eps = 1e-5f;
-    int nvls = -1;           // two-shot through the NVSwitch multicast object: -1 when available, 0 never, 1 required
+    // Use of the NVSwitch multicast object by the two-shot form: -1 by measurement, 0 none (peer
+    // pushes, peer stores), 1 in-switch reduce + multicast store, 2 peer pushes + multicast store.
+    // 1 and 2 fail with Unsupported when the multicast mapping or symmetric outputs are missing.
+    int nvls = -1;
     unsigned long long* const* trace = nullptr;  // per local rank: device buffer of 8 timestamps, or nullptr
 };
 
@@ -35,5 +38,6 @@ Result FusedLinearAllReduceRmsNorm(Communicator& comm, const FusedLinearDesc* de
 
 // Rows from which the two-shot form is used when `force_oneshot` is -1.
 uint32_t FusedLinearOneShotMaxRows(int world);
+int FusedLinearAutoMulticastMode(int world, uint32_t T);
 
 }  // namespace yali

@@ -245,9 +245,9 @@ Result MakePlan(int world, uint64_t count, Dtype in, Dtype out, int epilogue, Ke
     else if (forced == KernelMode::Stream) v = Variant::Stream;
     else if (forced == KernelMode::NVLS) v = bytes <= (128ull << 10) ? Variant::NvlsOneShot : Variant::NvlsTwoShot;
     else if (row) v = row->variant;
-    // Measured on 8 x B200 with symmetric buffers: the in-switch one-shot beats the peer-to-peer
-    // one-shot above a few KiB (7 peers to push to), so only the smallest messages stay with Flash.
-    else if (nvls_ok && caps.symmetric && world > 4 && bytes > (4ull << 10))
+    // Measured on 8 x B200 with symmetric buffers: the flag-in-data one-shot wins up to 64 KiB
+    // (8.3-13.5 us against 11-15 us), the in-switch forms from 128 KiB (16 us against 16-21 us).
+    else if (nvls_ok && caps.symmetric && world > 4 && bytes > (64ull << 10))
         v = bytes <= (128ull << 10) ? Variant::NvlsOneShot : Variant::NvlsTwoShot;
     else if (bytes <= FlashCrossoverBytes(in, world)) v = Variant::Flash;
     else if (nvls_ok && world > 2) v = Variant::NvlsTwoShot;

@@ -101,9 +101,9 @@ def test_plan_auto_selection(native_lib):
     assert rc == 0 and p.variant == 1  # 256 MiB does not fit the NVLS staging: ring kernel
     rc, p, _ = make_plan(lib, 8, 1024)
     assert rc == 0 and p.variant == 0 and p.ctas <= 2 and p.flags & 64  # flag-in-data form for tiny messages
-    rc, p, _ = make_plan(lib, 8, 16384, cp=caps(8, has_multicast=1, symmetric=1))
-    assert rc == 0 and p.variant == 2  # 64 KiB at 8 ranks, symmetric buffers: in-switch one-shot
-    rc, p, _ = make_plan(lib, 8, 16384, cp=caps(8, has_multicast=1, symmetric=0))
+    rc, p, _ = make_plan(lib, 8, 32768, cp=caps(8, has_multicast=1, symmetric=1))
+    assert rc == 0 and p.variant == 2  # 128 KiB at 8 ranks, symmetric buffers: in-switch one-shot
+    rc, p, _ = make_plan(lib, 8, 32768, cp=caps(8, has_multicast=1, symmetric=0))
     assert rc == 0 and p.variant == 0  # plain buffers stay with the peer-to-peer one-shot
     rc, p, _ = make_plan(lib, 8, 1024, cp=caps(8, vec_ok=0))
     assert rc == 0 and not p.flags & 64  # needs aligned buffers

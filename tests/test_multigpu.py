@@ -137,7 +137,7 @@ def _rank_main(rank, world, port, q, scenario):
                 h = sum(x.float() @ w.float().T for x, w in zip(xs, ws)) + res.float()
                 want = h * torch.rsqrt(h.pow(2).mean(-1, keepdim=True) + 1e-5) * nw.float()
                 x, w = xs[rank].to(dev), ws[rank].to(dev)
-                forms = [(True, False), (False, False)] + ([(False, True)] if comm.has_multicast else [])
+                forms = [(True, 0), (False, 0)] + ([(False, 1), (False, 2)] if comm.has_multicast else [])
                 for oneshot, nvls in forms:
                     out = comm.symm_empty([T, N], torch.bfloat16)
                     ro = comm.symm_empty([T, N], torch.bfloat16)

@@ -171,14 +171,15 @@ class Comm:
                              residual: Optional[TensorOrList] = None, *, eps: float = 1e-5,
                              out: Optional[TensorOrList] = None, residual_out: Optional[TensorOrList] = None,
                              oneshot: Optional[bool] = None, ctas: int = 0, trace: Optional[TensorOrList] = None,
-                             nvls: Optional[bool] = None):
+                             nvls: Union[None, bool, int] = None):
         """out = RMSNorm(residual + sum over ranks of x @ w.T) * norm_weight in ONE kernel per rank
         (tcgen05 GEMM whose epilogue pushes partial rows to their owner over NVLink, then reduce + norm).
         x: [T, K], w: [N, K] (this rank's slice, nn.Linear layout), bf16.  With one GPU per process the
         two-shot form (T above a few dozen rows) needs `out` from symm_empty().  `trace`: int64 CUDA
-        tensor(s) of 8 elements that receive CTA 0's %globaltimer at the phase boundaries.  `nvls`: the
-        two-shot form sums and delivers rows through the NVSwitch multicast object when it exists and
-        `out` is symmetric (None), never (False), or must (True)."""
+        tensor(s) of 8 elements that receive CTA 0's %globaltimer at the phase boundaries.  `nvls`: how the
+        two-shot form uses the NVSwitch multicast object: None = by measurement, 0/False = not at all
+        (peer pushes and peer stores), 1/True = in-switch reduce + multicast store, 2 = peer pushes +
+        multicast store; 1 and 2 need the multicast object and `out` from symm_empty()."""
         xs, ws, nws = self._as_list(x, "x"), self._as_list(w, "w"), self._as_list(norm_weight, "norm_weight")
         if out is None:
             T, N = xs[0].shape[0], ws[0].shape[0]
