@@ -35,7 +35,13 @@ uint32_t FusedLinearOneShotMaxRows(int world) { return world <= 2 ? 256u : 32u; 
 
 // Which multicast form the two-shot takes by default (0 none, 1 in-switch reduce + multicast store,
 // 2 peer pushes + multicast store), from measurements on 2, 4 and 8 B200.
-int FusedLinearAutoMulticastMode(int world, uint32_t /*T*/) { return world >= 4 ? 1 : 0; }
+// 8 x B200, K = 512 per rank, N = 4096, CUDA-graph timing (us, modes 0 / 1 / 2): T = 128: 31.4 / 28.9 /
+// 29.5; T = 512: 37.4 / 36.0 / 35.6; T = 2048: 80.1 / 78.7 / 78.1.  2 x B200 (K = 2048): mode 1 loses
+// (109 against 90 us at T = 2048, the switch adds a hop and saves no bytes), mode 2 ties with mode 0.
+int FusedLinearAutoMulticastMode(int world, uint32_t T) {
+    if (world < 4) return 0;
+    return T < 512 ? 1 : 2;
+}
 
 Result FusedLinearAllReduceRmsNorm(Communicator& comm, const FusedLinearDesc* descs, uint32_t T, uint32_t N,
                                    uint32_t K, const FusedLinearOptions& opt, const cudaStream_t* streams) {
