@@ -54,7 +54,8 @@ $(BIN)/test_%: tests/cpp/test_%.cu tests/cpp/test_framework.h $(LIB) | $(BIN)
 run-cpptests: cpptests
 	@set -e; for t in $(CPPTESTS); do echo "== $$t"; $$t; done
 
+# make reference REFERENCE_DIR=<checkout of the reference>
 reference:
-	bash baseline/build_reference.sh
+	bash baseline/build_reference.sh $(REFERENCE_DIR)
 clean:
 	rm -rf build yali_b200/lib yali_b200/_C.so

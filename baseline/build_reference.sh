@@ -6,7 +6,7 @@
 # compiled directly with nvcc.  The three NCCL-internal headers it includes are
 # replaced by a shim that forwards to the system <nccl.h>.
 set -euo pipefail
-REF="${1:-/root/reference}"
+REF="${1:-${YALI_REFERENCE_DIR:?usage: baseline/build_reference.sh <checkout of the reference>}}"
 HERE="$(cd "$(dirname "${BASH_SOURCE[0]}")" && pwd)"
 OUT="$HERE/_ref"
 mkdir -p "$OUT/shim"
