@@ -86,6 +86,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--graph", action="store_true", help="time one CUDA-graph replay of all calls")
     ap.add_argument("--arms", default="", help="comma list to restrict the arms")
+    ap.add_argument("--trace", action="store_true",
+                    help="also print the in-kernel timeline of the fused arms (CTA 0 of rank 0: microseconds from "
+                         "kernel entry to barriers ready, first accumulator, first tile announced, all tiles done, "
+                         "partial rows present, own rows reduced, output complete)")
     ap.add_argument("--out", default="")
     args = ap.parse_args()
     emu = args.emulate > 0
@@ -145,6 +149,17 @@ def main():
             row = {"T": T, "world": W, "arm": label, "us": round(us, 2), "roofline_us": round(roof, 3),
                    "fraction_of_roofline": round(roof / us, 4), "peaks": src, "emulated": emu,
                    "timing": "graph" if args.graph else "events"}
+            if args.trace and label.startswith("fused_"):
+                mode = {"fused_oneshot": (True, 0), "fused_twoshot": (False, 0), "fused_twoshot_nvls": (False, 1),
+                        "fused_twoshot_mcast": (False, 2)}[label]
+                tr = [torch.zeros(8, dtype=torch.int64, device=dev[i]) for i in range(nl)]
+                for _ in range(3):
+                    comm.fused_linear_rmsnorm(one(xs), one(ws), one(nw), one(res), out=one(outs), oneshot=mode[0],
+                                              nvls=mode[1], trace=one(tr))
+                comm.sync()
+                comm.barrier()
+                t = tr[0].cpu().tolist()
+                row["timeline_us"] = [round((v - t[0]) / 1e3, 1) for v in t]
             rows.append(row)
             if rank == 0:
                 print(json.dumps(row), flush=True)
