@@ -29,8 +29,10 @@
 // epilogue keeps the partial rows in this rank's OWN landing zone, so phase 1 has no
 // peer stores at all; the owner of a row reads the sum over all ranks with one
 // multimem.ld_reduce per 16 bytes (fp32 accumulation in the switch) and delivers the
-// normalised row to every rank with one multimem.st.  Per rank that moves T*N*2/W
-// bytes in and out instead of (W-1)/W * T*N*2 each way.
+// normalised row to every rank with one multimem.st.  An SM then issues 1/W of the
+// loads and stores; on the links the switch still pulls (W-1)/W * T*N*2 bytes out of
+// every rank for the sums, while delivery sends only T*N*2/W per rank.  A third form
+// keeps the peer pushes of phase 1 and uses the switch for delivery alone.
 //
 // Parity: none in the reference (it has no GEMM, no fused op and no tensor-core
 // code; see its src/kernels and src/all_reduce).  The unfused composition (library
