@@ -12,6 +12,8 @@ NVFLAGS := -std=c++17 -O3 -lineinfo --expt-relaxed-constexpr $(ARCH) -Icsrc -Ibe
 LIB := yali_b200/lib/libyali_b200.so
 LINK := -Lyali_b200/lib -lyali_b200 -Xlinker -rpath -Xlinker '$$ORIGIN/../../yali_b200/lib'
 BIN := build/bin
+# public headers: every binary that includes them is rebuilt when one changes (class layouts)
+HDRS := $(wildcard csrc/*/*.h) $(wildcard csrc/*/*.cuh)
 
 .PHONY: all lib bench examples cpptests run-cpptests reference clean
 all: lib
@@ -25,31 +27,31 @@ $(BIN):
 BENCH := $(BIN)/benchmark_yali $(BIN)/benchmark_yali_mpi $(BIN)/p2p_bandwidth
 BENCH_NCCL := $(BIN)/benchmark_nccl $(BIN)/benchmark_nccl_mpi
 bench: $(BENCH) $(BENCH_NCCL)
-$(BIN)/benchmark_yali: bench/benchmark_yali.cu bench/bench_common.h $(LIB) | $(BIN)
+$(BIN)/benchmark_yali: bench/benchmark_yali.cu bench/bench_common.h $(HDRS) $(LIB) | $(BIN)
 	$(NVCC) $(NVFLAGS) $< -o $@ $(LINK)
-$(BIN)/benchmark_yali_mpi: bench/benchmark_yali_mpi.cu bench/bench_common.h $(LIB) | $(BIN)
+$(BIN)/benchmark_yali_mpi: bench/benchmark_yali_mpi.cu bench/bench_common.h $(HDRS) $(LIB) | $(BIN)
 	$(NVCC) $(NVFLAGS) $< -o $@ $(LINK)
 $(BIN)/p2p_bandwidth: bench/p2p_bandwidth.cu | $(BIN)
 	$(NVCC) $(NVFLAGS) $< -o $@
-$(BIN)/benchmark_nccl: bench/benchmark_nccl.cu bench/bench_common.h $(LIB) | $(BIN)
+$(BIN)/benchmark_nccl: bench/benchmark_nccl.cu bench/bench_common.h $(HDRS) $(LIB) | $(BIN)
 	$(NVCC) $(NVFLAGS) $< -o $@ $(LINK) -lnccl
-$(BIN)/benchmark_nccl_mpi: bench/benchmark_nccl_mpi.cu bench/bench_common.h $(LIB) | $(BIN)
+$(BIN)/benchmark_nccl_mpi: bench/benchmark_nccl_mpi.cu bench/bench_common.h $(HDRS) $(LIB) | $(BIN)
 	$(NVCC) $(NVFLAGS) $< -o $@ $(LINK) -lnccl
 
 EXAMPLES := $(BIN)/example_simple $(BIN)/example_multilane $(BIN)/example_simple_mpi $(BIN)/example_multilane_mpi
 examples: $(EXAMPLES)
-$(BIN)/example_simple: examples/01_single_process/01_allreduce/simple.cu $(LIB) | $(BIN)
+$(BIN)/example_simple: examples/01_single_process/01_allreduce/simple.cu $(HDRS) $(LIB) | $(BIN)
 	$(NVCC) $(NVFLAGS) $< -o $@ $(LINK)
-$(BIN)/example_multilane: examples/01_single_process/01_allreduce/multilane.cu $(LIB) | $(BIN)
+$(BIN)/example_multilane: examples/01_single_process/01_allreduce/multilane.cu $(HDRS) $(LIB) | $(BIN)
 	$(NVCC) $(NVFLAGS) $< -o $@ $(LINK)
-$(BIN)/example_simple_mpi: examples/02_multi_process/01_allreduce/simple_mpi.cu $(LIB) | $(BIN)
+$(BIN)/example_simple_mpi: examples/02_multi_process/01_allreduce/simple_mpi.cu $(HDRS) $(LIB) | $(BIN)
 	$(NVCC) $(NVFLAGS) $< -o $@ $(LINK)
-$(BIN)/example_multilane_mpi: examples/02_multi_process/01_allreduce/multilane_mpi.cu $(LIB) | $(BIN)
+$(BIN)/example_multilane_mpi: examples/02_multi_process/01_allreduce/multilane_mpi.cu $(HDRS) $(LIB) | $(BIN)
 	$(NVCC) $(NVFLAGS) $< -o $@ $(LINK)
 
 CPPTESTS := $(patsubst tests/cpp/%.cu,$(BIN)/%,$(wildcard tests/cpp/test_*.cu))
 cpptests: $(CPPTESTS)
-$(BIN)/test_%: tests/cpp/test_%.cu tests/cpp/test_framework.h $(LIB) | $(BIN)
+$(BIN)/test_%: tests/cpp/test_%.cu tests/cpp/test_framework.h $(HDRS) $(LIB) | $(BIN)
 	$(NVCC) $(NVFLAGS) -Itests/cpp $< -o $@ $(LINK)
 run-cpptests: cpptests
 	@set -e; for t in $(CPPTESTS); do echo "== $$t"; $$t; done

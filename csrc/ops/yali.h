@@ -19,6 +19,7 @@
 #include <vector>
 
 #include "../comm/communicator.h"
+#include "host_pipeline.h"
 #include "../core/status.h"
 
 namespace yali {
@@ -64,10 +65,13 @@ class Comm {
     Result reset() { return impl_->Reset(); }
     const std::string& error() const { return err_; }
     Communicator* impl() const { return impl_.get(); }
+    // Pipeline behind allreduce_host (created on first use).
+    HostPipeline& host_pipeline();
 
    private:
     Comm() = default;
     std::unique_ptr<Communicator> impl_;
+    std::unique_ptr<HostPipeline> host_pipe_;  // declared after impl_: destroyed before it
     std::string err_;
 };
 
@@ -126,6 +130,19 @@ cudaError_t allreduce_residual_rmsnorm(Comm& comm, const T* const* send, T* cons
                          rows * static_cast<size_t>(hidden), DtypeOf<T>::value, streams, sync, opt);
 }
 
+// Host-resident data: send / recv are page-locked host buffers (one per rank).  The copies of both
+// directions and the all-reduce overlap chunk by chunk (ops/host_pipeline.h); no counterpart in the
+// reference, whose ops take device pointers only.
+cudaError_t allreduce_host_raw(Comm& comm, const void* const* send, void* const* recv, size_t count, Dtype dt,
+                               const cudaStream_t* streams, bool sync, size_t chunk_bytes);
+template <typename T>
+cudaError_t allreduce_host(Comm& comm, const T* const* send, T* const* recv, size_t count,
+                           const cudaStream_t* streams = nullptr, bool sync = true, size_t chunk_bytes = 8u << 20) {
+    if (!comm.ok()) return cudaErrorInvalidValue;
+    return allreduce_host_raw(comm, reinterpret_cast<const void* const*>(send), reinterpret_cast<void* const*>(recv),
+                              count, DtypeOf<T>::value, streams, sync, chunk_bytes);
+}
+
 // ---------------------------------------------------------------- one GPU per process
 class MPIComm {
    public:
@@ -156,9 +173,11 @@ class MPIComm {
     cudaError_t exchange_buffer(const void* buf, size_t bytes);
     const std::string& error() const { return err_; }
     Communicator* impl() const { return impl_.get(); }
+    HostPipeline& host_pipeline();
 
    private:
     std::unique_ptr<Communicator> impl_;
+    std::unique_ptr<HostPipeline> host_pipe_;  // declared after impl_: destroyed before it
     int rank_ = 0, world_ = 1, local_rank_ = 0;
     std::string err_;
 };
@@ -179,6 +198,15 @@ cudaError_t allreduce(MPIComm& comm, const T* send, T* recv, size_t count, cudaS
     e = cudaStreamSynchronize(stream ? stream : comm.stream());
     if (e != cudaSuccess) return e;
     return ToCudaError(comm.impl()->Check());
+}
+cudaError_t allreduce_host_raw(MPIComm& comm, const void* send, void* recv, size_t count, Dtype dt,
+                               cudaStream_t stream, bool sync, size_t chunk_bytes);
+// Page-locked host buffers in and out; synchronises `stream` (0: the communicator's) unless sync is false.
+template <typename T>
+cudaError_t allreduce_host(MPIComm& comm, const T* send, T* recv, size_t count, cudaStream_t stream = nullptr,
+                           bool sync = true, size_t chunk_bytes = 8u << 20) {
+    if (!comm.ok()) return cudaErrorInvalidValue;
+    return allreduce_host_raw(comm, send, recv, count, DtypeOf<T>::value, stream, sync, chunk_bytes);
 }
 template <typename T>
 cudaError_t allreduce_async(MPIComm& comm, const T* send, T* recv, size_t count, cudaStream_t stream = nullptr) {

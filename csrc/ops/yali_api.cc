@@ -37,8 +37,29 @@ Comm Comm::Emulated(int world, int device, const CommOptions& opt) {
 }
 
 Comm::Comm(Comm&&) noexcept = default;
-Comm& Comm::operator=(Comm&&) noexcept = default;
+Comm& Comm::operator=(Comm&& o) noexcept {
+    if (this != &o) {
+        host_pipe_.reset();  // refers to the communicator that is about to go
+        impl_ = std::move(o.impl_);
+        host_pipe_ = std::move(o.host_pipe_);
+        err_ = std::move(o.err_);
+    }
+    return *this;
+}
 Comm::~Comm() = default;
+
+HostPipeline& Comm::host_pipeline() {
+    if (!host_pipe_) host_pipe_ = std::make_unique<HostPipeline>(*impl_);
+    return *host_pipe_;
+}
+
+cudaError_t allreduce_host_raw(Comm& comm, const void* const* send, void* const* recv, size_t count, Dtype dt,
+                               const cudaStream_t* streams, bool sync, size_t chunk_bytes) {
+    if (!comm.ok()) return cudaErrorInvalidValue;
+    Result r = comm.host_pipeline().AllReduce(send, recv, count, dt, OpOptions(), chunk_bytes, streams);
+    if (r != Result::Success) return ToCudaError(r);
+    return sync ? ToCudaError(comm.impl()->Sync(streams)) : cudaSuccess;
+}
 
 cudaError_t Comm::sync() {
     if (!impl_) return cudaErrorInitializationError;
@@ -88,8 +109,38 @@ MPIComm::MPIComm(int* argc, char*** argv, const CommOptions& opt) {
 }
 
 MPIComm::MPIComm(MPIComm&&) noexcept = default;
-MPIComm& MPIComm::operator=(MPIComm&&) noexcept = default;
+MPIComm& MPIComm::operator=(MPIComm&& o) noexcept {
+    if (this != &o) {
+        host_pipe_.reset();  // refers to the communicator that is about to go
+        impl_ = std::move(o.impl_);
+        host_pipe_ = std::move(o.host_pipe_);
+        rank_ = o.rank_;
+        world_ = o.world_;
+        local_rank_ = o.local_rank_;
+        err_ = std::move(o.err_);
+    }
+    return *this;
+}
 MPIComm::~MPIComm() = default;
+
+HostPipeline& MPIComm::host_pipeline() {
+    if (!host_pipe_) host_pipe_ = std::make_unique<HostPipeline>(*impl_);
+    return *host_pipe_;
+}
+
+cudaError_t allreduce_host_raw(MPIComm& comm, const void* send, void* recv, size_t count, Dtype dt,
+                               cudaStream_t stream, bool sync, size_t chunk_bytes) {
+    if (!comm.ok()) return cudaErrorInvalidValue;
+    const void* s[1] = {send};
+    void* r[1] = {recv};
+    cudaStream_t st[1] = {stream};
+    Result res = comm.host_pipeline().AllReduce(s, r, count, dt, OpOptions(), chunk_bytes, st);
+    if (res != Result::Success) return ToCudaError(res);
+    if (!sync) return cudaSuccess;
+    cudaError_t e = cudaStreamSynchronize(stream ? stream : comm.stream());
+    if (e != cudaSuccess) return e;
+    return ToCudaError(comm.impl()->Check());
+}
 
 cudaError_t MPIComm::barrier() {
     if (!impl_) return cudaErrorInitializationError;

@@ -8,6 +8,8 @@
 #include <cuda_fp16.h>
 
 #include <chrono>
+#include <algorithm>
+#include <cmath>
 #include <vector>
 
 #include "comm/topology.h"
@@ -128,6 +130,39 @@ TEST(n_gpu_api_random_data) {
         RandomN<__nv_bfloat16>(comm, 1 << 20, Dtype::BF16, false);
         RandomN<__half>(comm, 300001, Dtype::FP16, true);
         RandomN<float>(comm, (32u << 20) + 12, Dtype::FP32, false);  // 128 MiB: the two-shot path
+    }
+}
+
+// Page-locked host buffers in and out: the chunked three-stream pipeline must give the plain sum.
+TEST(host_to_host_allreduce) {
+    if (!ytest::HasNGPUs(1)) SKIP_TEST("needs a GPU");
+    for (int world : {2, 4}) {
+        Comm comm = MakeComm(world);
+        EXPECT_TRUE(comm.ok());
+        if (!comm.ok()) continue;
+        const size_t n = 5 * 65536 + 123;  // six chunks of 256 KiB: more chunks than staging slots
+        std::vector<float*> src(world), dst(world);
+        for (int i = 0; i < world; ++i) {
+            EXPECT_TRUE(cudaMallocHost(&src[i], n * sizeof(float)) == cudaSuccess);
+            EXPECT_TRUE(cudaMallocHost(&dst[i], n * sizeof(float)) == cudaSuccess);
+            for (size_t k = 0; k < n; ++k) src[i][k] = static_cast<float>((k * 7 + i * 13) % 101) * 0.25f - 3.0f;
+        }
+        for (int rep = 0; rep < 2; ++rep) {
+            for (int i = 0; i < world; ++i) std::fill(dst[i], dst[i] + n, -1.0f);
+            cudaError_t e = allreduce_host<float>(comm, src.data(), dst.data(), n, nullptr, true, 256u << 10);
+            EXPECT_TRUE(e == cudaSuccess);
+            size_t bad = 0;
+            for (size_t k = 0; k < n; ++k) {
+                float want = 0.f;
+                for (int i = 0; i < world; ++i) want += src[i][k];
+                for (int i = 0; i < world; ++i) bad += std::fabs(dst[i][k] - want) > 1e-4f;
+            }
+            EXPECT_EQ(bad, static_cast<size_t>(0));
+        }
+        for (int i = 0; i < world; ++i) {
+            cudaFreeHost(src[i]);
+            cudaFreeHost(dst[i]);
+        }
     }
 }
 
