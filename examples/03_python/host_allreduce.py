@@ -7,10 +7,13 @@
 i+1, the all-reduce of chunk i and the device-to-host copy of chunk i-1 on three streams.
 """
 import argparse
+import sys
+from pathlib import Path
 
 import torch
 
-import yali_b200 as yali
+sys.path.insert(0, str(Path(__file__).resolve().parents[2]))  # run from a checkout without installing
+import yali_b200 as yali  # noqa: E402
 
 
 def main() -> None:

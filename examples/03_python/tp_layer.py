@@ -9,10 +9,13 @@ rank's `out`.  The reference has no such layer; this is the fused path that the 
 modules of `yali_b200.parallel.tensor_parallel` use.
 """
 import argparse
+import sys
+from pathlib import Path
 
 import torch
 
-import yali_b200 as yali
+sys.path.insert(0, str(Path(__file__).resolve().parents[2]))  # run from a checkout without installing
+import yali_b200 as yali  # noqa: E402
 
 
 def main() -> None:
