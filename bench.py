@@ -279,6 +279,9 @@ def run_own(args) -> dict:
             "parallelism": ("1 GPU: 2 ranks emulated in one cooperative launch (HBM-bound, no NVLink)" if emulated
                             else f"{ranks} ranks, one GPU per process"),
             "l2": "inputs (128 MiB per rank) larger than L2; 1 MiB latency rotates over 320 MiB of buffers",
+            "metric_note": "busBw = bytes per rank x 2(N-1)/N / time: a per-link rate that ideal scaling keeps "
+                           "CONSTANT as N grows (the job reduces N x 128 MiB per step); the 1-GPU figure moves "
+                           "no bytes over NVLink and is bound by HBM",
             "kernel": variant,
             "baseline": "reference README: 79.2 GB/s at 128 MB fp32 on 2x A100 NV4",
         },
