@@ -7,7 +7,7 @@
 // [N, K] (this rank's slice of the row-parallel weight, K contiguous, the layout of
 // torch.nn.Linear.weight), both bf16; the sum runs over the ranks.
 //
-// Phase 1 (GEMM): a persistent grid (one 6-warp CTA per SM) walks 128x128 output
+// Phase 1 (GEMM): a persistent grid (one 7-warp CTA per SM) walks 128x128 output
 // tiles, warp-specialised.  Warp 0 feeds a 5-stage shared-memory pipeline with TMA
 // (cp.async.bulk.tensor, 128-byte swizzle, no multicast); warp 1 issues tcgen05.mma
 // (bf16 x bf16 -> fp32) into one of two 128-column TMEM accumulators and signals
