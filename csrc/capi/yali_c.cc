@@ -1,5 +1,7 @@
 #include "yali_c.h"
 
+#include "../ops/fused_linear.h"
+
 #include <cstdio>
 #include <cstring>
 #include <string>
@@ -146,6 +148,11 @@ void yali_c_oracle_residual_rmsnorm(const double* sum, const float* residual, co
                                     size_t hidden, double eps, double* y, double* pre_norm) {
     oracle::ResidualRmsNorm(sum, residual, weight, rows, hidden, eps, y, pre_norm);
 }
+void yali_c_fused_linear_counts(uint32_t T, uint32_t N, int world, int oneshot, uint32_t* arrivals, uint32_t* rows_of) {
+    FusedLinearCounts(T, N, world, oneshot != 0, arrivals, rows_of);
+}
+uint32_t yali_c_fused_linear_oneshot_max_rows(int world) { return FusedLinearOneShotMaxRows(world); }
+int yali_c_fused_linear_multicast_mode(int world, uint32_t T) { return FusedLinearAutoMulticastMode(world, T); }
 void yali_c_oracle_gemm(const float* a, const float* b, size_t m, size_t n, size_t k, double* c) {
     oracle::Gemm(a, b, m, n, k, c);
 }

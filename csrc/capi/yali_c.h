@@ -75,6 +75,10 @@ float yali_c_round_fp16(float x);
 void yali_c_oracle_allreduce(const float* const* in, int world, size_t n, double scale, double* out);
 void yali_c_oracle_residual_rmsnorm(const double* sum, const float* residual, const float* weight, size_t rows,
                                     size_t hidden, double eps, double* y, double* pre_norm);
+// Fused linear layer: counter targets per owner (arrays of `world`), default one-shot limit and multicast form.
+void yali_c_fused_linear_counts(uint32_t T, uint32_t N, int world, int oneshot, uint32_t* arrivals, uint32_t* rows_of);
+uint32_t yali_c_fused_linear_oneshot_max_rows(int world);
+int yali_c_fused_linear_multicast_mode(int world, uint32_t T);
 void yali_c_oracle_gemm(const float* a, const float* b, size_t m, size_t n, size_t k, double* c);
 int yali_c_verify_allreduce_sum(const float* host, size_t n, float expected, float tol, size_t* first_mismatch,
                                 size_t* mismatch_count);

@@ -33,6 +33,27 @@ bool EncodeTileMap(const DriverApi* d, CUtensorMap* map, const void* base, uint6
 
 uint32_t FusedLinearOneShotMaxRows(int world) { return world <= 2 ? 256u : 32u; }
 
+// Counter targets of one call: every source announces each 128x128 tile once to every owner
+// that has rows in the tile's row block (one-shot: to everybody), and every owner reports the
+// rows it delivered.  The kernel's announcer warp applies the same rule tile by tile.
+void FusedLinearCounts(uint32_t T, uint32_t N, int W, bool oneshot, uint32_t* arrivals, uint32_t* rows_of) {
+    const uint32_t ntm = (T + kGemmTileM - 1) / kGemmTileM, ntn = N / kGemmTileN;
+    const uint32_t Rs = oneshot ? T : (T + W - 1) / W;
+    for (int q = 0; q < W; ++q) {
+        arrivals[q] = rows_of[q] = 0;
+        if (oneshot) {
+            arrivals[q] = ntm * ntn;
+        } else {
+            const uint32_t lo = std::min<uint32_t>(T, q * Rs), hi = std::min<uint32_t>(T, lo + Rs);
+            if (hi > lo) {
+                const uint32_t first = lo / kGemmTileM, last = (hi - 1) / kGemmTileM;
+                arrivals[q] = (last - first + 1) * ntn;
+            }
+            rows_of[q] = hi - lo;
+        }
+    }
+}
+
 // Which multicast form the two-shot takes by default (0 none, 1 in-switch reduce + multicast store,
 // 2 peer pushes + multicast store), from measurements on 2, 4 and 8 B200.
 // 8 x B200, K = 512 per rank, N = 4096, CUDA-graph timing (us, modes 0 / 1 / 2): T = 128: 31.4 / 28.9 /
@@ -141,19 +162,7 @@ Result FusedLinearAllReduceRmsNorm(Communicator& comm, const FusedLinearDesc* de
     const uint32_t ntm = (T + kGemmTileM - 1) / kGemmTileM, ntn = N / kGemmTileN;
     // Arrivals owner q expects from every source in this call, and rows owner q delivers.
     uint32_t arrivals[kMaxRanks] = {}, rows_of[kMaxRanks] = {};
-    for (int q = 0; q < W; ++q) {
-        if (oneshot) {
-            arrivals[q] = ntm * ntn;
-            rows_of[q] = 0;
-        } else {
-            const uint32_t lo = std::min<uint32_t>(T, q * Rs), hi = std::min<uint32_t>(T, lo + Rs);
-            if (hi > lo) {
-                const uint32_t first = lo / kGemmTileM, last = (hi - 1) / kGemmTileM;
-                arrivals[q] = (last - first + 1) * ntn;
-            }
-            rows_of[q] = hi - lo;
-        }
-    }
+    FusedLinearCounts(T, N, W, oneshot, arrivals, rows_of);
     const void* fn = GemmArKernel(comm.emulated());
     const uint32_t smem = GemmArSmemBytes();
     static bool attr_set[2] = {false, false};

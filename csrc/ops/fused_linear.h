@@ -39,5 +39,7 @@ Result FusedLinearAllReduceRmsNorm(Communicator& comm, const FusedLinearDesc* de
 // Rows from which the two-shot form is used when `force_oneshot` is -1.
 uint32_t FusedLinearOneShotMaxRows(int world);
 int FusedLinearAutoMulticastMode(int world, uint32_t T);
+// Per owner q: tile announcements it receives from EACH source, and rows it delivers (arrays of W).
+void FusedLinearCounts(uint32_t T, uint32_t N, int W, bool oneshot, uint32_t* arrivals, uint32_t* rows_of);
 
 }  // namespace yali

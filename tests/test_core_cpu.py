@@ -250,3 +250,33 @@ def test_verify_allreduce_sum(native_lib):
     assert native_lib.yali_c_verify_allreduce_sum(near.ctypes.data, 10, 3.0, 1e-3, None, None) == 1
     assert native_lib.yali_c_verify_allreduce_sum(near.ctypes.data, 10, 3.0, 1e-4, None, None) == 0
     assert native_lib.yali_c_verify_allreduce_sum(None, 0, 3.0, 1e-4, None, None) == 1
+
+
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
+def test_fused_linear_counter_targets_match_the_kernels_announcements(native_lib, world):
+    """The host's counter targets must equal what the kernel's announcer warp and row owners add up to:
+    a mismatch would end in a bounded-wait timeout on the device."""
+    import ctypes
+    lib = native_lib
+    BM = BN = 128
+    N = 4096
+    for T in [1, 2, 7, 16, 100, 127, 128, 129, 255, 256, 300, 1000, 1024, 2047, 2048, 4099]:
+        for oneshot in (0, 1):
+            arr = (ctypes.c_uint32 * 8)()
+            rows = (ctypes.c_uint32 * 8)()
+            lib.yali_c_fused_linear_counts(T, N, world, oneshot, arr, rows)
+            ntm, ntn = -(-T // BM), N // BN
+            rs = T if oneshot else -(-T // world)
+            want = [0] * world
+            for mt in range(ntm):  # the announcer's rule, tile by tile (one source)
+                lo, hi = mt * BM, min(T, mt * BM + BM)
+                for _nt in range(ntn):
+                    for q in range(world):
+                        if oneshot or (q * rs < hi and (q + 1) * rs > lo):
+                            want[q] += 1
+            assert list(arr[:world]) == want, (T, oneshot)
+            own = [0 if oneshot else max(0, min(T, q * rs + rs) - min(T, q * rs)) for q in range(world)]
+            assert list(rows[:world]) == own and (oneshot or sum(own) == T)
+    assert lib.yali_c_fused_linear_oneshot_max_rows(2) >= lib.yali_c_fused_linear_oneshot_max_rows(8) >= 1
+    assert lib.yali_c_fused_linear_multicast_mode(2, 2048) == 0
+    assert lib.yali_c_fused_linear_multicast_mode(8, 128) in (1, 2) and lib.yali_c_fused_linear_multicast_mode(8, 2048) in (1, 2)
