@@ -109,6 +109,22 @@ typedef struct YaliSimReport {
 } YaliSimReport;
 int yali_c_simulate(const YaliSimConfig* cfg, YaliSimReport* rep);
 
+/* Host-thread model of the fused GEMM layer's cross-rank protocol (sim/gemm_protocol_sim.cc):
+ * `world` x `ctas` threads, `calls` back-to-back calls of a [rows, col_tiles x 128] layer, two-shot or
+ * one-shot.  fault: 0 none, 1 rank `fault_rank` stops launching from call `fault_call`, 2 one tile
+ * announcement of that rank is lost.  slow_rank (-1: none) sleeps before its reduce phase, so that the
+ * other ranks run ahead.  single_parity = 1 removes the double buffering of the landing zones (a
+ * negative control: the stamps must then catch the reuse in one-shot mode).  Same return codes and
+ * report as yali_c_simulate; flag_writes counts counter updates. */
+typedef struct YaliFusedSimConfig {
+    int world, ctas, calls, oneshot;
+    uint32_t rows, col_tiles;
+    int fault, fault_rank, fault_call;
+    int slow_rank, single_parity;
+    int timeout_ms;
+} YaliFusedSimConfig;
+int yali_c_simulate_fused(const YaliFusedSimConfig* cfg, YaliSimReport* rep);
+
 #ifdef __cplusplus
 }
 #endif

@@ -40,6 +40,7 @@ LIB_SOURCES = [
     "ops/host_oracle.cc",
     "ops/yali_api.cc",
     "sim/protocol_sim.cc",
+    "sim/gemm_protocol_sim.cc",
     "ops/fused_linear.cc",
     "ops/host_pipeline.cc",
     "capi/yali_c.cc",

@@ -32,6 +32,13 @@ class SimConfig(ctypes.Structure):
                 ("timeout_ms", ctypes.c_int), ("seed", ctypes.c_uint64)]
 
 
+class FusedSimConfig(ctypes.Structure):
+    _fields_ = [("world", ctypes.c_int), ("ctas", ctypes.c_int), ("calls", ctypes.c_int), ("oneshot", ctypes.c_int),
+                ("rows", ctypes.c_uint32), ("col_tiles", ctypes.c_uint32),
+                ("fault", ctypes.c_int), ("fault_rank", ctypes.c_int), ("fault_call", ctypes.c_int),
+                ("slow_rank", ctypes.c_int), ("single_parity", ctypes.c_int), ("timeout_ms", ctypes.c_int)]
+
+
 class SimReport(ctypes.Structure):
     _fields_ = [("status", ctypes.c_int), ("mismatches", ctypes.c_uint64), ("timeouts", ctypes.c_uint64),
                 ("max_outstanding_slots", ctypes.c_uint64), ("flag_writes", ctypes.c_uint64),
@@ -82,6 +89,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "yali_c_verify_allreduce_sum": (i32, [vp, c.c_size_t, f32, f32, c.POINTER(c.c_size_t),
                                               c.POINTER(c.c_size_t)]),
         "yali_c_simulate": (i32, [c.POINTER(SimConfig), c.POINTER(SimReport)]),
+        "yali_c_simulate_fused": (i32, [c.POINTER(FusedSimConfig), c.POINTER(SimReport)]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(lib, name)
