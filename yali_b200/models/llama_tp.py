@@ -13,7 +13,7 @@ ranks: all).  Weights are random-initialised; there are no checkpoints here."""
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import List, Optional, Sequence, Tuple
+from typing import List, Sequence, Tuple
 
 import torch
 import torch.nn.functional as F
