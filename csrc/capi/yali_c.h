@@ -114,7 +114,8 @@ int yali_c_simulate(const YaliSimConfig* cfg, YaliSimReport* rep);
  * one-shot.  fault: 0 none, 1 rank `fault_rank` stops launching from call `fault_call`, 2 one tile
  * announcement of that rank is lost.  slow_rank (-1: none) sleeps before its reduce phase, so that the
  * other ranks run ahead.  single_parity = 1 removes the double buffering of the landing zones (a
- * negative control: the stamps must then catch the reuse in one-shot mode).  Same return codes and
+ * negative control: the stamps must then catch the reuse in one-shot mode).  in_switch = 1 models the
+ * two-shot form whose owners read every rank's own image.  Same return codes and
  * report as yali_c_simulate; flag_writes counts counter updates. */
 typedef struct YaliFusedSimConfig {
     int world, ctas, calls, oneshot;
@@ -122,6 +123,7 @@ typedef struct YaliFusedSimConfig {
     int fault, fault_rank, fault_call;
     int slow_rank, single_parity;
     int timeout_ms;
+    int in_switch; /* 1: partial rows stay in the producer's own image and the owner reads all ranks' images */
 } YaliFusedSimConfig;
 int yali_c_simulate_fused(const YaliFusedSimConfig* cfg, YaliSimReport* rep);
 

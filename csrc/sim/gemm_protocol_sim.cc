@@ -79,6 +79,9 @@ struct FusedShared {
     std::atomic<int> t_rank{-1}, t_peer{-1}, t_site{0};
     std::atomic<bool> abort{false};
 
+    size_t ImageIndex(uint32_t parity, uint32_t row, uint32_t nt) const {
+        return (static_cast<size_t>(parity) * T + row) * ntn + nt;
+    }
     size_t LandingIndex(uint32_t parity, int src, uint32_t row_local, uint32_t nt) const {
         return ((static_cast<size_t>(parity) * W + src) * Rs + row_local) * ntn + nt;
     }
@@ -136,6 +139,14 @@ void FusedCta(FusedShared& s, std::vector<RankStop>& stop, int r, int c) {
             const uint32_t lo = mt * bm, hi = std::min(T, lo + bm);
             for (uint32_t row = lo; row < hi; ++row) {
                 const float v = Partial(r, call, row, nt);
+                if (s.cfg.in_switch) {
+                    // In-switch form: the partial row stays in this rank's own image of the call parity.
+                    Cell& cell = s.landing[r][s.ImageIndex(parity, row, nt)];
+                    if (cell.stamp.load(std::memory_order_acquire) != 0) s.violations.fetch_add(1);  // still unread
+                    cell.value = v;
+                    cell.stamp.store(stamp, std::memory_order_release);
+                    continue;
+                }
                 for (int d = 0; d < W; ++d) {
                     if (!oneshot && static_cast<uint32_t>(d) != row / Rs) continue;
                     Cell& cell = s.landing[d][s.LandingIndex(parity, r, oneshot ? row : row - d * Rs, nt)];
@@ -166,7 +177,9 @@ void FusedCta(FusedShared& s, std::vector<RankStop>& stop, int r, int c) {
                 for (uint32_t nt = 0; nt < ntn; ++nt) {
                     float sum = 0.f;
                     for (int src = 0; src < W; ++src) {
-                        Cell& cell = s.landing[r][s.LandingIndex(parity, src, lr, nt)];
+                        // in-switch form: the switch reads every rank's own image at the row's offset
+                        Cell& cell = s.cfg.in_switch ? s.landing[src][s.ImageIndex(parity, grow, nt)]
+                                                     : s.landing[r][s.LandingIndex(parity, src, lr, nt)];
                         if (cell.stamp.load(std::memory_order_acquire) != stamp) s.violations.fetch_add(1);
                         sum += cell.value;
                         cell.stamp.store(0, std::memory_order_release);
@@ -233,7 +246,9 @@ extern "C" int yali_c_simulate_fused(const YaliFusedSimConfig* cfg, YaliSimRepor
     s.bm = yali::kGemmTileM;
     s.ntm = (s.T + s.bm - 1) / s.bm;
     s.Rs = cfg->oneshot ? s.T : (s.T + s.W - 1) / s.W;
-    const size_t nland = 2ull * s.W * s.Rs * s.ntn, nout = static_cast<size_t>(s.T) * s.ntn;
+    if (cfg->in_switch && cfg->oneshot) return -1;  // the in-switch form is a two-shot form
+    const size_t nland = std::max<size_t>(2ull * s.W * s.Rs * s.ntn, 2ull * s.T * s.ntn);
+    const size_t nout = static_cast<size_t>(s.T) * s.ntn;
     s.words.reset(new FusedShared::Words[s.W]);
     for (int r = 0; r < s.W; ++r) {
         s.landing.emplace_back(new Cell[nland]);

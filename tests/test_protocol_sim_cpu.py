@@ -77,7 +77,7 @@ from yali_b200._native import FusedSimConfig  # noqa: E402
 
 def simulate_fused(**kw):
     cfg = FusedSimConfig(world=2, ctas=3, calls=4, oneshot=0, rows=300, col_tiles=2, fault=0, fault_rank=0,
-                         fault_call=0, slow_rank=-1, single_parity=0, timeout_ms=5000)
+                         fault_call=0, slow_rank=-1, single_parity=0, timeout_ms=5000, in_switch=0)
     for k, v in kw.items():
         setattr(cfg, k, v)
     rep = SimReport()
@@ -93,6 +93,14 @@ def test_fused_layer_protocol_back_to_back_calls(world, oneshot):
         rc, rep = simulate_fused(world=world, oneshot=oneshot, rows=rows, calls=5)
         assert rc == 0 and rep.mismatches == 0 and rep.timeouts == 0, (rows, rc, rep.mismatches, rep.timeout_site)
         assert rep.flag_writes > 0
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_fused_layer_in_switch_form(world):
+    # partial rows stay in the producer's image; an owner reads every rank's image (multimem.ld_reduce)
+    for rows, slow in ((7, -1), (300, -1), (1000, 1), (260, 0)):
+        rc, rep = simulate_fused(world=world, rows=rows, calls=6, in_switch=1, slow_rank=slow)
+        assert rc == 0 and rep.mismatches == 0 and rep.timeouts == 0, (rows, rc, rep.mismatches)
 
 
 @pytest.mark.parametrize("oneshot", [0, 1])

@@ -36,7 +36,8 @@ class FusedSimConfig(ctypes.Structure):
     _fields_ = [("world", ctypes.c_int), ("ctas", ctypes.c_int), ("calls", ctypes.c_int), ("oneshot", ctypes.c_int),
                 ("rows", ctypes.c_uint32), ("col_tiles", ctypes.c_uint32),
                 ("fault", ctypes.c_int), ("fault_rank", ctypes.c_int), ("fault_call", ctypes.c_int),
-                ("slow_rank", ctypes.c_int), ("single_parity", ctypes.c_int), ("timeout_ms", ctypes.c_int)]
+                ("slow_rank", ctypes.c_int), ("single_parity", ctypes.c_int), ("timeout_ms", ctypes.c_int),
+                ("in_switch", ctypes.c_int)]
 
 
 class SimReport(ctypes.Structure):
