@@ -15,7 +15,9 @@ BIN := build/bin
 # public headers: every binary that includes them is rebuilt when one changes (class layouts)
 HDRS := $(wildcard csrc/*/*.h) $(wildcard csrc/*/*.cuh)
 
-.PHONY: all lib bench examples cpptests run-cpptests reference clean
+.PHONY: all lib bench examples cpptests run-cpptests reference clean test-cpu test-gpu test run-examples \
+        run-examples-mp run-nccl-baseline hw-info hw-baseline sweep-quick sweep-standard sweep-full \
+        quick-benchmark tp-layer ptxas format
 all: lib
 lib:
 	$(PY) -m yali_b200._build
@@ -55,6 +57,47 @@ $(BIN)/test_%: tests/cpp/test_%.cu tests/cpp/test_framework.h $(HDRS) $(LIB) | $
 	$(NVCC) $(NVFLAGS) -Itests/cpp $< -o $@ $(LINK)
 run-cpptests: cpptests
 	@set -e; for t in $(CPPTESTS); do echo "== $$t"; $$t; done
+
+# ---- tests
+test-cpu:
+	$(PY) -m pytest tests -q -m "not gpu"
+test-gpu: lib cpptests examples bench
+	$(PY) -m pytest tests -q -m gpu
+test: test-cpu test-gpu
+
+# ---- examples and baselines (GPUS=2|4|8)
+GPUS ?= 2
+PORT ?= 29531
+TORCHRUN := $(PY) -m torch.distributed.run --nnodes=1 --nproc-per-node $(GPUS) --master-addr 127.0.0.1 --master-port $(PORT)
+run-examples: examples
+	$(BIN)/example_simple
+	YALI_GPUS=$(GPUS) $(BIN)/example_multilane
+run-examples-mp: examples
+	$(PY) -m yali_b200.launch -np $(GPUS) $(BIN)/example_simple_mpi
+	$(PY) -m yali_b200.launch -np $(GPUS) $(BIN)/example_multilane_mpi
+run-nccl-baseline: bench
+	$(PY) bench/validate_baselines.py --run --gpus $(GPUS)
+	$(PY) -m yali_b200.launch -np $(GPUS) $(BIN)/benchmark_nccl_mpi 33554432 200 0 auto 0 cuda-events fp32
+
+# ---- hardware
+hw-info:
+	$(PY) -c "from yali_b200.utils import hw_info; import json; print(json.dumps(hw_info.system_info(), indent=1))"
+hw-baseline: $(BIN)/p2p_bandwidth
+	$(BIN)/p2p_bandwidth
+
+# ---- sweeps (results/<mode>: raw lines, CSVs, summary.md)
+sweep-quick sweep-standard sweep-full: sweep-%:
+	$(PY) bench/run_sweep.py --gpus $(GPUS) --mode $* --out results/$*
+quick-benchmark: bench
+	$(PY) bench/quick_benchmark.py --gpus $(GPUS)
+tp-layer:
+	$(TORCHRUN) bench/bench_tp_layer.py --graph
+
+# ---- developer aids
+ptxas:
+	$(PY) -m yali_b200._build ptxas
+format:
+	clang-format -i $$(git ls-files 'csrc/*' 'bench/*.cu' 'bench/*.h' 'tests/cpp/*' 'examples/*.cu' | grep -E '\.(h|cc|cu|cuh)$$')
 
 # make reference REFERENCE_DIR=<checkout of the reference>
 reference:
