@@ -80,3 +80,43 @@ def test_nccl_header_matches_library():
     sys.path.insert(0, str(ROOT / "bench"))
     import validate_baselines as vb
     assert vb.header_version() == vb.library_version()
+
+
+def test_make_tuning_table_from_sweep_lines(tmp_path):
+    """bench/make_tuning_table.py: fastest forced variant per size, hysteresis against noise, merged rows; the
+    planner loads the result (the committed table of the B200 runs included)."""
+    import ctypes
+    import importlib.util
+    import json as _json
+    from pathlib import Path as _Path
+
+    from yali_b200 import _native
+    root = _Path(__file__).resolve().parents[1]
+    spec = importlib.util.spec_from_file_location("make_tuning_table", root / "bench" / "make_tuning_table.py")
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+
+    def line(size, kernel, us, world=2):
+        return {"impl": "yali_b200", "world": world, "dtype": "fp32", "bytes": size, "variant": kernel[:5],
+                "kernel": kernel, "us": us, "busbw_gbps": size / us / 1e3}
+    rows = [line(4096, "flash", 4.0), line(4096, "stream", 10.0),
+            line(8192, "flash", 5.0), line(8192, "stream", 4.95),      # 1 % better: the incumbent stays
+            line(16384, "flash", 9.0), line(16384, "stream", 6.0),     # a real crossover
+            line(32768, "stream", 7.0), line(32768, "flash", 12.0),
+            {"impl": "nccl", "world": 2, "dtype": "fp32", "bytes": 4096, "variant": "nccl", "us": 1.0, "busbw_gbps": 1.0},
+            dict(line(4096, "stream", 0.1), variant="auto")]           # auto rows never vote
+    table = mod.build(rows)
+    assert [(r["max_bytes"], r["variant"]) for r in table] == [(8192, "flash"), (1 << 40, "stream")]
+
+    committed = root / "docs" / "benchmark" / "artifacts" / "2026-11-25-b200" / "tuning_b200_nvswitch.json"
+    text = committed.read_text()
+    assert len(_json.loads(text)["rows"]) >= 6
+    # The planner follows the committed table: 64 MiB fp32 at 2 ranks is the ring kernel there.
+    lib = _native.lib()
+    from tests.test_core_cpu import Plan, caps  # the ctypes mirrors of the C structs
+    plan, err = Plan(), ctypes.create_string_buffer(256)
+    c = caps(2)
+    rc = lib.yali_c_make_plan(2, (64 << 20) // 4, 0, 0, 0, 0, ctypes.byref(c), text.encode(), ctypes.byref(plan), err, 256)
+    assert rc == 0 and plan.variant == 1, err.value
+    rc = lib.yali_c_make_plan(2, (1 << 20) // 4, 0, 0, 0, 0, ctypes.byref(c), text.encode(), ctypes.byref(plan), err, 256)
+    assert rc == 0 and plan.variant == 0
