@@ -60,6 +60,8 @@ struct Shared {
     std::vector<std::unique_ptr<std::atomic<uint64_t>[]>> ring_stamp;  // per rank, one per slot; 0 = FREE
     std::vector<std::vector<float>> stage;         // one-shot staging per rank: [2][W-1][count]
     std::vector<std::unique_ptr<std::atomic<uint64_t>[]>> stage_stamp;  // [2][W-1][ctas]
+    // flag-in-data form: one 64-bit word per element = {call number, value bits}, [2][W-1][count] per rank
+    std::vector<std::unique_ptr<std::atomic<uint64_t>[]>> ll;
     std::vector<std::vector<float>> send, recv;
     std::vector<std::unique_ptr<Barrier>> rank_barrier;
     std::unique_ptr<std::atomic<int>[]> rank_abort;  // agreed between the lanes of a rank at the barrier
@@ -261,6 +263,83 @@ void FlashCta(Shared& s, int r, int cta) {
     }
 }
 
+// Flag-in-data form of the one-shot (small messages): no flags at all.  Every pushed word carries the
+// call number beside the payload, and a reader polls the word itself until the number is the current
+// call's.  Two staging parities; what keeps a writer two calls ahead from overwriting unread words is
+// only that it cannot finish the call in between without this rank's data for it.
+void FlashLLCta(Shared& s, int r, int cta) {
+    const YaliSimConfig& c = s.cfg;
+    const int W = s.W;
+    for (int call = 0; call < c.calls; ++call) {
+        if (c.fault == 1 && r == c.fault_rank && call >= c.fault_call) return;
+        const uint32_t epoch = call + 1, parity = epoch & 1u;
+        uint64_t vb, ve, tb, te;
+        yali::oracle::FlashSlice(c.count, 4, s.L, cta, true, &vb, &ve, &tb, &te);
+        const uint64_t eb = vb * 4, ee = (cta == s.L - 1) ? c.count : ve * 4;
+        const float* send = s.send[r].data();
+        for (int k = 1; k < W; ++k) {
+            const int p = (r + k) % W;
+            const size_t sidx = (static_cast<size_t>(parity) * (W - 1) + yali::SrcSlot(r, p));
+            uint64_t expect = 0;
+            if (!s.stage_stamp[p][sidx * s.L + cta].compare_exchange_strong(expect, epoch)) s.violations.fetch_add(1);
+            const bool lose = c.fault == 2 && r == c.fault_rank && call == c.fault_call && k == 1 && cta == 0;
+            for (uint64_t e = eb; e < ee; ++e) {
+                if (lose && e == eb) continue;  // one pushed word never arrives
+                uint32_t bits;
+                std::memcpy(&bits, send + e, 4);
+                s.ll[p][sidx * c.count + e].store((static_cast<uint64_t>(epoch) << 32) | bits, std::memory_order_release);
+            }
+            s.flag_writes.fetch_add(ee - eb, std::memory_order_relaxed);
+        }
+        bool ok = true;
+        float* recv = s.recv[r].data();
+        const auto deadline = Clock::now() + std::chrono::milliseconds(c.timeout_ms);
+        for (uint64_t e = eb; e < ee && ok; ++e) {
+            float acc = 0.f;
+            for (int q = 0; q < W && ok; ++q) {
+                if (q == r) {
+                    acc += send[e];
+                    continue;
+                }
+                std::atomic<uint64_t>& w = s.ll[r][(static_cast<size_t>(parity) * (W - 1) + yali::SrcSlot(q, r)) * c.count + e];
+                uint64_t v;
+                uint32_t spins = 0;
+                while (static_cast<uint32_t>((v = w.load(std::memory_order_acquire)) >> 32) != epoch) {
+                    if ((++spins & 255u) == 0) {
+                        if (s.abort.load() || Clock::now() > deadline) {
+                            if (s.timeouts.fetch_add(1) == 0) {
+                                s.t_rank = r;
+                                s.t_peer = q;
+                                s.t_site = 3;
+                            }
+                            s.abort = true;
+                            ok = false;
+                            break;
+                        }
+                        std::this_thread::yield();
+                    }
+                }
+                if (!ok) break;
+                const uint32_t bits = static_cast<uint32_t>(v);
+                float f;
+                std::memcpy(&f, &bits, 4);
+                acc += f;
+            }
+            if (ok) recv[e] = acc;
+        }
+        if (ok)
+            for (int q = 0; q < W; ++q) {
+                if (q == r) continue;
+                const size_t sidx = (static_cast<size_t>(parity) * (W - 1) + yali::SrcSlot(q, r));
+                uint64_t expect = epoch;
+                if (!s.stage_stamp[r][sidx * s.L + cta].compare_exchange_strong(expect, 0)) s.violations.fetch_add(1);
+            }
+        if (s.abort.load()) s.rank_abort[r].store(1);
+        s.rank_barrier[r]->wait();
+        if (s.rank_abort[r].load()) return;
+    }
+}
+
 }  // namespace
 
 extern "C" int yali_c_simulate(const YaliSimConfig* cfg, YaliSimReport* rep) {
@@ -288,6 +367,11 @@ extern "C" int yali_c_simulate(const YaliSimConfig* cfg, YaliSimReport* rep) {
             s.ring_stamp.emplace_back(new std::atomic<uint64_t>[nslots]);
             for (size_t i = 0; i < nslots; ++i) s.ring_stamp[r][i].store(0);
         } else {
+            if (cfg->mode == 2) {
+                const size_t nw = 2ull * (W - 1) * cfg->count;
+                s.ll.emplace_back(new std::atomic<uint64_t>[nw]);
+                for (size_t i = 0; i < nw; ++i) s.ll[r][i].store(0);
+            }
             s.stage.emplace_back(2ull * (W - 1) * cfg->count);
             s.stage_stamp.emplace_back(new std::atomic<uint64_t>[2ull * (W - 1) * s.L]);
             for (size_t i = 0; i < 2ull * (W - 1) * s.L; ++i) s.stage_stamp[r][i].store(0);
@@ -299,7 +383,7 @@ extern "C" int yali_c_simulate(const YaliSimConfig* cfg, YaliSimReport* rep) {
     std::vector<std::thread> threads;
     for (int r = 0; r < W; ++r)
         for (int l = 0; l < s.L; ++l)
-            threads.emplace_back(cfg->mode == 1 ? StreamLane : FlashCta, std::ref(s), r, l);
+            threads.emplace_back(cfg->mode == 1 ? StreamLane : (cfg->mode == 2 ? FlashLLCta : FlashCta), std::ref(s), r, l);
     // A rank that stops launching leaves its lanes' barrier short-handed only for itself.
     for (auto& t : threads) t.join();
 

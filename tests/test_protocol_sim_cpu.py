@@ -129,3 +129,20 @@ def test_fused_layer_rank_that_stops_launching_times_out_its_peers():
 def test_fused_layer_lost_announcement_times_out():
     rc, rep = simulate_fused(world=2, rows=300, calls=3, fault=2, fault_rank=0, fault_call=1, timeout_ms=300)
     assert rc == 2 and rep.timeout_peer == 0 and rep.timeout_site == 1
+
+
+# ---- flag-in-data form of the one-shot (mode 2): the call number travels inside every pushed word ----
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_flag_in_data_protocol_back_to_back(world):
+    for count, ctas in [(1, 1), (17, 2), (4099, 3), (20000, 5)]:
+        rc, rep = simulate(mode=2, world=world, lanes=ctas, calls=6, count=count)
+        assert rc == 0 and rep.mismatches == 0 and rep.timeouts == 0, (count, ctas, rc, rep.mismatches)
+
+
+def test_flag_in_data_lost_word_and_missing_rank_time_out():
+    rc, rep = simulate(mode=2, world=2, lanes=2, calls=3, count=5000, fault=2, fault_rank=0, fault_call=1,
+                       timeout_ms=300)
+    assert rc == 2 and rep.timeout_rank == 1 and rep.timeout_peer == 0 and rep.timeout_site == 3
+    rc, rep = simulate(mode=2, world=4, lanes=2, calls=4, count=5000, fault=1, fault_rank=2, fault_call=2,
+                       timeout_ms=300)
+    assert rc == 2 and rep.timeout_peer == 2
