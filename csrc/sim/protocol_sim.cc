@@ -340,6 +340,78 @@ void FlashLLCta(Shared& s, int r, int cta) {
     }
 }
 
+// Two-shot through the switch on staged (non-symmetric) buffers: copy in, per-CTA barrier across the
+// ranks, every rank sums its shard over all ranks' staging and writes the result back into EVERY rank's
+// staging (multimem.ld_reduce / multimem.st), second barrier, copy out.  The staging half alternates per
+// call.  Every staged element has a stamp: 2*call+1 = input, 2*call+2 = result, 0 = free.
+void NvlsCta(Shared& s, int r, int cta) {
+    const YaliSimConfig& c = s.cfg;
+    const int W = s.W, C = s.L;
+    const uint64_t S = ((c.count + W - 1) / W + 3) / 4 * 4;  // shard elements
+    const uint64_t per = (S + C - 1) / C;
+    auto slice = [&](int q, uint64_t* b, uint64_t* e) {
+        *b = std::min<uint64_t>(c.count, q * S + std::min(S, cta * per));
+        *e = std::max(*b, std::min<uint64_t>(c.count, q * S + std::min(S, cta * per + per)));
+    };
+    auto stamp_at = [&](int rank, uint32_t parity, uint64_t e) -> std::atomic<uint64_t>& {
+        return s.ll[rank][static_cast<size_t>(parity) * c.count + e];
+    };
+    auto stage_at = [&](int rank, uint32_t parity, uint64_t e) -> float& {
+        return s.stage[rank][static_cast<size_t>(parity) * c.count + e];
+    };
+    for (int call = 0; call < c.calls; ++call) {
+        if (c.fault == 1 && r == c.fault_rank && call >= c.fault_call) return;
+        const uint32_t epoch = 2u * call, parity = call & 1u;
+        const uint64_t in_stamp = 2ull * call + 1, out_stamp = 2ull * call + 2;
+        for (int q = 0; q < W; ++q) {  // copy in: slice `cta` of every shard
+            uint64_t b, e;
+            slice(q, &b, &e);
+            for (uint64_t i = b; i < e; ++i) {
+                uint64_t expect = 0;
+                if (!stamp_at(r, parity, i).compare_exchange_strong(expect, in_stamp)) s.violations.fetch_add(1);
+                stage_at(r, parity, i) = s.send[r][i];
+            }
+        }
+        SignalPeers(s, r, kFlash, cta, epoch + 1, call);
+        bool ok = WaitPeers(s, r, kFlash, cta, epoch + 1, 1);
+        if (ok) {
+            uint64_t b, e;
+            slice(r, &b, &e);
+            for (uint64_t i = b; i < e; ++i) {
+                float acc = 0.f;
+                for (int q = 0; q < W; ++q) {
+                    if (stamp_at(q, parity, i).load(std::memory_order_acquire) != in_stamp) s.violations.fetch_add(1);
+                    acc += stage_at(q, parity, i);
+                }
+                for (int q = 0; q < W; ++q) {
+                    stage_at(q, parity, i) = acc;
+                    stamp_at(q, parity, i).store(out_stamp, std::memory_order_release);
+                }
+            }
+            // the second barrier uses the other flag word of the pair in the kernels; here a second kind
+            for (int p = 0; p < W; ++p)
+                if (p != r) Flag(s, p, kAg, cta, r).store(epoch + 2, std::memory_order_release);
+            ok = WaitPeers(s, r, kAg, cta, epoch + 2, 2);
+        }
+        if (ok) {
+            for (int q = 0; q < W; ++q) {  // copy out
+                uint64_t b, e;
+                slice(q, &b, &e);
+                for (uint64_t i = b; i < e; ++i) {
+                    uint64_t expect = out_stamp;
+                    if (!stamp_at(r, parity, i).compare_exchange_strong(expect, 0)) s.violations.fetch_add(1);
+                    s.recv[r][i] = stage_at(r, parity, i);
+                }
+            }
+        } else {
+            s.abort = true;
+        }
+        if (s.abort.load()) s.rank_abort[r].store(1);
+        s.rank_barrier[r]->wait();
+        if (s.rank_abort[r].load()) return;
+    }
+}
+
 }  // namespace
 
 extern "C" int yali_c_simulate(const YaliSimConfig* cfg, YaliSimReport* rep) {
@@ -367,8 +439,8 @@ extern "C" int yali_c_simulate(const YaliSimConfig* cfg, YaliSimReport* rep) {
             s.ring_stamp.emplace_back(new std::atomic<uint64_t>[nslots]);
             for (size_t i = 0; i < nslots; ++i) s.ring_stamp[r][i].store(0);
         } else {
-            if (cfg->mode == 2) {
-                const size_t nw = 2ull * (W - 1) * cfg->count;
+            if (cfg->mode == 2 || cfg->mode == 3) {
+                const size_t nw = 2ull * std::max(W - 1, 1) * cfg->count;
                 s.ll.emplace_back(new std::atomic<uint64_t>[nw]);
                 for (size_t i = 0; i < nw; ++i) s.ll[r][i].store(0);
             }
@@ -383,7 +455,8 @@ extern "C" int yali_c_simulate(const YaliSimConfig* cfg, YaliSimReport* rep) {
     std::vector<std::thread> threads;
     for (int r = 0; r < W; ++r)
         for (int l = 0; l < s.L; ++l)
-            threads.emplace_back(cfg->mode == 1 ? StreamLane : (cfg->mode == 2 ? FlashLLCta : FlashCta), std::ref(s), r, l);
+            threads.emplace_back(cfg->mode == 1 ? StreamLane : (cfg->mode == 2 ? FlashLLCta : (cfg->mode == 3 ? NvlsCta : FlashCta)),
+                                 std::ref(s), r, l);
     // A rank that stops launching leaves its lanes' barrier short-handed only for itself.
     for (auto& t : threads) t.join();
 

@@ -146,3 +146,14 @@ def test_flag_in_data_lost_word_and_missing_rank_time_out():
     rc, rep = simulate(mode=2, world=4, lanes=2, calls=4, count=5000, fault=1, fault_rank=2, fault_call=2,
                        timeout_ms=300)
     assert rc == 2 and rep.timeout_peer == 2
+
+
+# ---- staged two-shot through the switch (mode 3): per-CTA barriers, sums written back to every rank ----
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_in_switch_two_shot_protocol(world):
+    for count, ctas in [(1, 1), (33, 2), (4099, 3), (20000, 4)]:
+        rc, rep = simulate(mode=3, world=world, lanes=ctas, calls=5, count=count)
+        assert rc == 0 and rep.mismatches == 0 and rep.timeouts == 0, (count, ctas, rc, rep.mismatches)
+    rc, rep = simulate(mode=3, world=world, lanes=2, calls=4, count=3000, fault=1, fault_rank=world - 1, fault_call=1,
+                       timeout_ms=300)
+    assert rc == 2 and rep.timeout_peer == world - 1
