@@ -35,6 +35,17 @@ def _worker(rank, world, port, q):
     ok &= torch.allclose(shard.double()[:min(s, n - rank * s)], expect[rank * s:rank * s + s], rtol=1e-6, atol=1e-6)
     full = yali.all_gather(shard, n)
     ok &= torch.allclose(full.double(), expect, rtol=1e-6, atol=1e-6)
+    # the fused tensor-parallel layer through the same call as on a GPU
+    T, K, N = 5, 16, 64
+    xs = [torch.randn(T, K, generator=torch.Generator().manual_seed(50 + r)) for r in range(world)]
+    wts = [torch.randn(N, K, generator=torch.Generator().manual_seed(60 + r)) * 0.1 for r in range(world)]
+    g = torch.rand(N, generator=torch.Generator().manual_seed(70)) + 0.5
+    resid = torch.randn(T, N, generator=torch.Generator().manual_seed(71))
+    buf = comm.symm_empty([T, N], torch.float32)
+    got = comm.fused_linear_rmsnorm(xs[rank], wts[rank], g, resid, out=buf)
+    hsum = sum(a.double() @ b.double().T for a, b in zip(xs, wts)) + resid.double()
+    want = hsum * torch.rsqrt(hsum.pow(2).mean(-1, keepdim=True) + 1e-5) * g.double()
+    ok &= got is buf and torch.allclose(got.double(), want, rtol=1e-4, atol=1e-4)
     # host-to-host call: same surface as on a GPU box, nothing to stage on CPU
     hh = yali.all_reduce_host(inputs[rank])
     ok &= torch.allclose(hh.double(), expect, rtol=1e-6, atol=1e-6)

@@ -347,6 +347,27 @@ class GlooComm:
         out.copy_(y.to(out.dtype))
         return out
 
+    def fused_linear_rmsnorm(self, x, w, norm_weight, residual=None, *, eps: float = 1e-5, out=None,
+                             residual_out=None, oneshot=None, ctas: int = 0, trace=None, nvls=None):
+        """Same call as Comm.fused_linear_rmsnorm: RMSNorm(residual + sum over ranks of x @ w.T) * norm_weight.
+        On CPU: fp32 matmul, all-reduce, norm (the options that pick a GPU form are accepted and ignored)."""
+        partial = x.detach().to(torch.float32) @ w.detach().to(torch.float32).T
+        y = self.all_reduce_rmsnorm(partial, norm_weight, residual, eps=eps, residual_out=residual_out)
+        if out is None:
+            return y.to(x.dtype)
+        out.copy_(y.to(out.dtype))
+        return out
+
+    def symm_empty(self, shape, dtype: torch.dtype = torch.float32) -> torch.Tensor:
+        """Plain host tensor: there is no symmetric heap on CPU, every buffer is as good as any other."""
+        return torch.empty([shape] if isinstance(shape, int) else list(shape), dtype=dtype)
+
+    def symm_reset(self) -> None:
+        pass
+
+    def reset(self) -> None:
+        self._dist.barrier(group=self._group)
+
     def shard_elems(self, count: int) -> int:
         return _native.lib().yali_c_shard_elems(count, self.world)
 
