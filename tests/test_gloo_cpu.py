@@ -46,6 +46,9 @@ def _worker(rank, world, port, q):
     hsum = sum(a.double() @ b.double().T for a, b in zip(xs, wts)) + resid.double()
     want = hsum * torch.rsqrt(hsum.pow(2).mean(-1, keepdim=True) + 1e-5) * g.double()
     ok &= got is buf and torch.allclose(got.double(), want, rtol=1e-4, atol=1e-4)
+    import yali_b200.ops.registry  # noqa: F401
+    got2 = torch.ops.yali.fused_linear_rmsnorm(xs[rank], wts[rank], g, resid)
+    ok &= torch.allclose(got2.double(), want, rtol=1e-4, atol=1e-4)
     # host-to-host call: same surface as on a GPU box, nothing to stage on CPU
     hh = yali.all_reduce_host(inputs[rank])
     ok &= torch.allclose(hh.double(), expect, rtol=1e-6, atol=1e-6)

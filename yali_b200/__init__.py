@@ -7,7 +7,8 @@ a thin PyTorch layer.
     y = yali.all_reduce(x)                    # CUDA tensor: native kernels; CPU tensor: gloo
 """
 from .parallel.comm import (Comm, destroy_process_group, get_default_comm, init_process_group)  # noqa: F401
-from .ops.collectives import (all_gather, all_reduce, all_reduce_host, all_reduce_rmsnorm, reduce_scatter)  # noqa: F401
+from .ops.collectives import (all_gather, all_reduce, all_reduce_host, all_reduce_rmsnorm,  # noqa: F401
+                              fused_linear_rmsnorm, reduce_scatter)  # noqa: F401
 from .ops import reference  # noqa: F401
 
 __version__ = "0.1.0"

@@ -89,7 +89,7 @@ def run_block(comm, ranks: Sequence[TPBlockRank], normed: Sequence[torch.Tensor]
     n = len(ranks)
     ctx = [ranks[i].attention_local(normed[i]) for i in range(n)]
     res2d = [r.reshape(B * S, H) for r in residual]
-    res_mid = [torch.empty_like(r) for r in res2d]
+    res_mid = _residual_buffers(comm, res2d, "res_mid")
     run = tp.fused_row_parallel if fused else None
     if fused:
         h = run(comm, ctx, [m.o_proj.weight for m in ranks], [m.o_proj.norm_weight for m in ranks], res2d,
@@ -98,7 +98,7 @@ def run_block(comm, ranks: Sequence[TPBlockRank], normed: Sequence[torch.Tensor]
         h, res_mid = _unfused(comm, ctx, [m.o_proj.weight for m in ranks], [m.o_proj.norm_weight for m in ranks],
                               res2d, ranks[0].cfg.eps)
     act = [ranks[i].mlp_local(h[i]) for i in range(n)]
-    res_out = [torch.empty_like(r) for r in res2d]
+    res_out = _residual_buffers(comm, res2d, "res_out")
     if fused:
         y = run(comm, act, [m.down_proj.weight for m in ranks], [m.down_proj.norm_weight for m in ranks], res_mid,
                 eps=ranks[0].cfg.eps, residual_out=res_out)
@@ -106,6 +106,21 @@ def run_block(comm, ranks: Sequence[TPBlockRank], normed: Sequence[torch.Tensor]
         y, res_out = _unfused(comm, act, [m.down_proj.weight for m in ranks],
                               [m.down_proj.norm_weight for m in ranks], res_mid, ranks[0].cfg.eps)
     return [t.reshape(B, S, H) for t in y], [t.reshape(B, S, H) for t in res_out]
+
+
+def _residual_buffers(comm, like: Sequence[torch.Tensor], tag: str) -> List[torch.Tensor]:
+    """Where a fused layer writes the updated residual stream.  With one GPU per process the row owners
+    write every rank's copy, so the buffer must sit at the same offset of every rank's symmetric heap:
+    one cached buffer per (tag, shape), reused by every block (the next block has consumed it by then,
+    in stream order on this rank and, through the layer's own counters, on the peers)."""
+    one_gpu_per_process = getattr(comm, "nlocal", 1) == 1 and getattr(comm, "world", 1) > 1 and like[0].is_cuda
+    if not one_gpu_per_process or not hasattr(comm, "symm_empty"):
+        return [torch.empty_like(r) for r in like]
+    cache = comm.__dict__.setdefault("_fused_out", {})  # cleared by symm_reset()
+    key = (tag, tuple(like[0].shape), like[0].dtype)
+    if key not in cache:
+        cache[key] = comm.symm_empty(list(like[0].shape), like[0].dtype)
+    return [cache[key]]
 
 
 def _unfused(comm, xs, ws, nws, res, eps):

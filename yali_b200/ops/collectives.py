@@ -28,6 +28,17 @@ def all_reduce_rmsnorm(x: torch.Tensor, weight: torch.Tensor, residual: Optional
     return _pick(comm).all_reduce_rmsnorm(x, weight, residual, eps=eps, out=out, residual_out=residual_out, mode=mode)
 
 
+def fused_linear_rmsnorm(x: torch.Tensor, w: torch.Tensor, norm_weight: torch.Tensor,
+                         residual: Optional[torch.Tensor] = None, *, eps: float = 1e-5, comm=None,
+                         out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """RMSNorm(residual + sum over ranks of x @ w.T) * norm_weight in one kernel per rank (x: [T, K] and
+    w: [N, K] are this rank's slices).  Without `out` the result is a fresh tensor (copied out of the
+    communicator's symmetric output buffer, which the next call reuses)."""
+    c = _pick(comm)
+    y = c.fused_linear_rmsnorm(x, w, norm_weight, residual, eps=eps, out=out)
+    return y if out is not None or not y.is_cuda else y.clone()
+
+
 def all_reduce_host(src: torch.Tensor, dst: Optional[torch.Tensor] = None, *, comm=None,
                     chunk_bytes: int = 8 << 20, scale: Optional[float] = None) -> torch.Tensor:
     """Sum over all ranks of a tensor in pinned host memory, result in pinned host memory; the copies in

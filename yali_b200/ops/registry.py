@@ -3,6 +3,7 @@
     torch.ops.yali.all_reduce(x)                       -> Tensor
     torch.ops.yali.all_reduce_scaled(x, scale, dtype)  -> Tensor
     torch.ops.yali.all_reduce_rmsnorm(x, weight, residual, eps) -> Tensor
+    torch.ops.yali.fused_linear_rmsnorm(x, w, norm_weight, residual, eps) -> Tensor
 
 All of them act on the default communicator (`yali_b200.init_process_group`).  CUDA
 tensors run the native sm_100a kernels; CPU tensors run over gloo."""
@@ -18,6 +19,7 @@ _lib = torch.library.Library("yali", "DEF")
 _lib.define("all_reduce(Tensor x) -> Tensor")
 _lib.define("all_reduce_scaled(Tensor x, float scale, ScalarType? out_dtype=None) -> Tensor")
 _lib.define("all_reduce_rmsnorm(Tensor x, Tensor weight, Tensor? residual=None, float eps=1e-05) -> Tensor")
+_lib.define("fused_linear_rmsnorm(Tensor x, Tensor w, Tensor norm_weight, Tensor? residual=None, float eps=1e-05) -> Tensor")
 _lib.define("reduce_scatter(Tensor x) -> Tensor")
 _lib.define("all_gather(Tensor shard, int count) -> Tensor")
 
@@ -35,6 +37,11 @@ def _all_reduce_rmsnorm(x: torch.Tensor, weight: torch.Tensor, residual: Optiona
     return collectives.all_reduce_rmsnorm(x, weight, residual, eps=eps)
 
 
+def _fused_linear_rmsnorm(x: torch.Tensor, w: torch.Tensor, norm_weight: torch.Tensor,
+                          residual: Optional[torch.Tensor] = None, eps: float = 1e-5) -> torch.Tensor:
+    return collectives.fused_linear_rmsnorm(x, w, norm_weight, residual, eps=eps)
+
+
 def _reduce_scatter(x: torch.Tensor) -> torch.Tensor:
     return collectives.reduce_scatter(x)
 
@@ -47,5 +54,6 @@ for _key in ("CPU", "CUDA"):
     _lib.impl("all_reduce", _all_reduce, _key)
     _lib.impl("all_reduce_scaled", _all_reduce_scaled, _key)
     _lib.impl("all_reduce_rmsnorm", _all_reduce_rmsnorm, _key)
+    _lib.impl("fused_linear_rmsnorm", _fused_linear_rmsnorm, _key)
     _lib.impl("reduce_scatter", _reduce_scatter, _key)
     _lib.impl("all_gather", _all_gather, _key)

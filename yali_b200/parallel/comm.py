@@ -175,7 +175,8 @@ class Comm:
         """out = RMSNorm(residual + sum over ranks of x @ w.T) * norm_weight in ONE kernel per rank
         (tcgen05 GEMM whose epilogue pushes partial rows to their owner over NVLink, then reduce + norm).
         x: [T, K], w: [N, K] (this rank's slice, nn.Linear layout), bf16.  With one GPU per process the
-        two-shot form (T above a few dozen rows) needs `out` from symm_empty().  `trace`: int64 CUDA
+        two-shot form (T above a few dozen rows) needs `out` from symm_empty(); without `out` the call
+        returns a per-shape symmetric buffer of its own that the next call of that shape overwrites.  `trace`: int64 CUDA
         tensor(s) of 8 elements that receive CTA 0's %globaltimer at the phase boundaries.  `nvls`: how the
         two-shot form uses the NVSwitch multicast object: None = by measurement, 0/False = not at all
         (peer pushes and peer stores), 1/True = in-switch reduce + multicast store, 2 = peer pushes +
@@ -184,7 +185,12 @@ class Comm:
         if out is None:
             T, N = xs[0].shape[0], ws[0].shape[0]
             if self.nlocal == 1 and self.world > 1:
-                outs = [self.symm_empty([T, N], torch.bfloat16)]
+                # Symmetric memory is never freed piecemeal: keep ONE output per shape and hand it out again.
+                # The tensor returned by a call is therefore overwritten by the next call of that shape.
+                cache = self.__dict__.setdefault("_fused_out", {})
+                if (T, N) not in cache:
+                    cache[(T, N)] = self.symm_empty([T, N], torch.bfloat16)
+                outs = [cache[(T, N)]]
             else:
                 outs = [torch.empty(T, N, dtype=torch.bfloat16, device=t.device) for t in xs]
         else:
@@ -260,6 +266,7 @@ class Comm:
         return ts[0] if self.nlocal == 1 else ts
 
     def symm_reset(self) -> None:
+        self.__dict__.pop("_fused_out", None)  # cached outputs lived in the symmetric heap
         self._impl.symm_reset()
 
     # ---- control --------------------------------------------------------------------------
