@@ -1,5 +1,7 @@
 #include "communicator.h"
 
+#include "../core/nvtx.h"
+
 #include <algorithm>
 #include <cstdio>
 #include <cstring>
@@ -461,6 +463,7 @@ Result Communicator::Collective(const void* const* send, void* const* recv, uint
 
 Result Communicator::AllReduce(const void* const* send, void* const* recv, uint64_t count, Dtype in, Dtype out,
                                const OpOptions& opt, const cudaStream_t* streams) {
+    YALI_NVTX_RANGE("yali::AllReduce");
     // The row-wise epilogue is fused into the one-shot kernel only.  A message beyond its
     // staging capacity is reduced by the bandwidth kernels first and normalised by a local
     // kernel afterwards (two launches per rank).
@@ -488,12 +491,14 @@ Result Communicator::AllReduce(const void* const* send, void* const* recv, uint6
 
 Result Communicator::ReduceScatter(const void* const* send, void* const* recv, uint64_t count, Dtype dt,
                                    const OpOptions& opt, const cudaStream_t* streams) {
+    YALI_NVTX_RANGE("yali::ReduceScatter");
     if (world_ == 1) return Collective(send, recv, count, dt, dt, opt, streams, 0);
     return Collective(send, recv, count, dt, dt, opt, streams, kFlagReduceScatterOnly);
 }
 
 Result Communicator::AllGather(const void* const* send, void* const* recv, uint64_t count, Dtype dt,
                                const OpOptions& opt, const cudaStream_t* streams) {
+    YALI_NVTX_RANGE("yali::AllGather");
     if (world_ == 1) return Collective(send, recv, count, dt, dt, opt, streams, 0);
     return Collective(send, recv, count, dt, dt, opt, streams, kFlagAllGatherOnly);
 }
@@ -509,6 +514,7 @@ Result Communicator::Check() {
 }
 
 Result Communicator::Sync(const cudaStream_t* streams) {
+    YALI_NVTX_RANGE("yali::Sync");
     for (int i = 0; i < nlocal(); ++i) {
         if (nlocal() > 1) cudaSetDevice(local_[i].device);
         cudaStream_t s = streams && streams[i] ? streams[i] : local_[i].stream;
@@ -551,6 +557,7 @@ std::string Communicator::DescribeStatus() const {
 }
 
 Result Communicator::Barrier() {
+    YALI_NVTX_RANGE("yali::Barrier");
     for (const Local& l : local_) {
         cudaSetDevice(l.device);
         cudaError_t e = cudaDeviceSynchronize();
@@ -561,6 +568,7 @@ Result Communicator::Barrier() {
 }
 
 Result Communicator::Reset() {
+    YALI_NVTX_RANGE("yali::Reset");
     Result r = Barrier();
     if (r != Result::Success) return r;
     for (const Local& l : local_) {

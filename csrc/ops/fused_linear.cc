@@ -1,6 +1,7 @@
 #include "fused_linear.h"
 
 #include "../core/env.h"
+#include "../core/nvtx.h"
 
 #include <algorithm>
 #include <cstring>
@@ -66,6 +67,7 @@ int FusedLinearAutoMulticastMode(int world, uint32_t T) {
 
 Result FusedLinearAllReduceRmsNorm(Communicator& comm, const FusedLinearDesc* descs, uint32_t T, uint32_t N,
                                    uint32_t K, const FusedLinearOptions& opt, const cudaStream_t* streams) {
+    YALI_NVTX_RANGE("yali::FusedLinear");
     auto fail = [&](Result r, const std::string& what) {
         comm.set_error(what);
         return r;

@@ -1,5 +1,7 @@
 #include "host_pipeline.h"
 
+#include "../core/nvtx.h"
+
 #include <algorithm>
 #include <string>
 
@@ -63,6 +65,7 @@ Result HostPipeline::Prepare(uint64_t chunk_elems, Dtype dt) {
 
 Result HostPipeline::AllReduce(const void* const* src, void* const* dst, uint64_t count, Dtype dt,
                                const OpOptions& opt, uint64_t chunk_bytes, const cudaStream_t* user_streams) {
+    YALI_NVTX_RANGE("yali::AllReduceHost");
     if (count == 0) return Result::Success;
     const int nl = comm_.nlocal();
     const uint64_t esz = DtypeSize(dt);

@@ -71,6 +71,11 @@ def _run(cmd: list[str], log: Path | None = None) -> str:
     return out
 
 
+def _extra_flags() -> list[str]:
+    # YALI_BUILD_NVTX=1: NVTX ranges around the host API calls (core/nvtx.h); off by default.
+    return ["-DYALI_NVTX"] if os.environ.get("YALI_BUILD_NVTX") == "1" else []
+
+
 def _compile(src: Path, flags: list[str], hdr_digest: str, verbose: bool) -> Path:
     key = hashlib.sha256((src.read_text() + hdr_digest + " ".join(flags)).encode()).hexdigest()[:16]
     obj = BUILD / (src.relative_to(CSRC).as_posix().replace("/", "_") + "." + key + ".o")
@@ -94,7 +99,7 @@ def build_library(verbose: bool = True, sources: list[str] | None = None) -> Pat
     hdr = _headers_digest()
     srcs = [CSRC / s for s in (sources or LIB_SOURCES) if (CSRC / s).exists()]
     with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 2)) as ex:
-        objs = list(ex.map(lambda s: _compile(s, [], hdr, verbose), srcs))
+        objs = list(ex.map(lambda s: _compile(s, _extra_flags(), hdr, verbose), srcs))
     lib = LIBDIR / "libyali_b200.so"
     stamp = hashlib.sha256(" ".join(sorted(o.name for o in objs)).encode()).hexdigest()
     stamp_file = BUILD / "lib.stamp"
