@@ -120,3 +120,47 @@ def test_make_tuning_table_from_sweep_lines(tmp_path):
     assert rc == 0 and plan.variant == 1, err.value
     rc = lib.yali_c_make_plan(2, (1 << 20) // 4, 0, 0, 0, 0, ctypes.byref(c), text.encode(), ctypes.byref(plan), err, 256)
     assert rc == 0 and plan.variant == 0
+
+
+def test_fused_layer_output_buffer_is_cached_per_shape():
+    """With one GPU per process the fused layer's default output comes from the symmetric heap, which is
+    never freed piecemeal: one buffer per shape, handed out again, forgotten by symm_reset()."""
+    import torch
+
+    from yali_b200.parallel.comm import Comm
+
+    class FakeImpl:
+        world, nlocal = 4, 1
+
+        def __init__(self):
+            self.allocs, self.calls, self.resets = 0, [], 0
+
+        def symm_empty(self, shape, dtype):
+            self.allocs += 1
+            return [torch.empty(shape, dtype=dtype)]
+
+        def fused_linear(self, xs, ws, nws, outs, res, ro, eps, oneshot, ctas, tr, nvls):
+            self.calls.append((outs[0], oneshot, nvls))
+
+        def symm_reset(self):
+            self.resets += 1
+
+        def close(self):
+            pass
+
+    impl = FakeImpl()
+    comm = Comm(impl)
+    x, w, g = torch.zeros(6, 8, dtype=torch.bfloat16), torch.zeros(16, 8, dtype=torch.bfloat16), torch.ones(16)
+    y1 = comm.fused_linear_rmsnorm(x, w, g)
+    y2 = comm.fused_linear_rmsnorm(x, w, g, nvls=2)
+    assert y1 is y2 and impl.allocs == 1 and tuple(y1.shape) == (6, 16)
+    assert impl.calls[0][1:] == (-1, -1) and impl.calls[1][2] == 2
+    y3 = comm.fused_linear_rmsnorm(torch.zeros(3, 8, dtype=torch.bfloat16), w, g)  # another shape: another buffer
+    assert y3 is not y1 and impl.allocs == 2
+    mine = torch.empty(6, 16, dtype=torch.bfloat16)
+    assert comm.fused_linear_rmsnorm(x, w, g, out=mine) is mine and impl.allocs == 2
+    comm.symm_reset()
+    assert impl.resets == 1
+    y4 = comm.fused_linear_rmsnorm(x, w, g)
+    assert y4 is not y1 and impl.allocs == 3
+    comm.close()
