@@ -40,7 +40,8 @@ $(BIN)/benchmark_nccl: bench/benchmark_nccl.cu bench/bench_common.h $(HDRS) $(LI
 $(BIN)/benchmark_nccl_mpi: bench/benchmark_nccl_mpi.cu bench/bench_common.h $(HDRS) $(LIB) | $(BIN)
 	$(NVCC) $(NVFLAGS) $< -o $@ $(LINK) -lnccl
 
-EXAMPLES := $(BIN)/example_simple $(BIN)/example_multilane $(BIN)/example_simple_mpi $(BIN)/example_multilane_mpi
+EXAMPLES := $(BIN)/example_simple $(BIN)/example_multilane $(BIN)/example_simple_mpi $(BIN)/example_multilane_mpi \
+            $(BIN)/example_manual_ipc
 examples: $(EXAMPLES)
 $(BIN)/example_simple: examples/01_single_process/01_allreduce/simple.cu $(HDRS) $(LIB) | $(BIN)
 	$(NVCC) $(NVFLAGS) $< -o $@ $(LINK)
@@ -49,6 +50,8 @@ $(BIN)/example_multilane: examples/01_single_process/01_allreduce/multilane.cu $
 $(BIN)/example_simple_mpi: examples/02_multi_process/01_allreduce/simple_mpi.cu $(HDRS) $(LIB) | $(BIN)
 	$(NVCC) $(NVFLAGS) $< -o $@ $(LINK)
 $(BIN)/example_multilane_mpi: examples/02_multi_process/01_allreduce/multilane_mpi.cu $(HDRS) $(LIB) | $(BIN)
+	$(NVCC) $(NVFLAGS) $< -o $@ $(LINK)
+$(BIN)/example_manual_ipc: examples/02_multi_process/01_allreduce/manual_ipc.cu $(HDRS) $(LIB) | $(BIN)
 	$(NVCC) $(NVFLAGS) $< -o $@ $(LINK)
 
 CPPTESTS := $(patsubst tests/cpp/%.cu,$(BIN)/%,$(wildcard tests/cpp/test_*.cu))
@@ -75,6 +78,7 @@ run-examples: examples
 run-examples-mp: examples
 	$(PY) -m yali_b200.launch -np $(GPUS) $(BIN)/example_simple_mpi
 	$(PY) -m yali_b200.launch -np $(GPUS) $(BIN)/example_multilane_mpi
+	$(PY) -m yali_b200.launch -np $(GPUS) $(BIN)/example_manual_ipc
 run-nccl-baseline: bench
 	$(PY) bench/validate_baselines.py --run --gpus $(GPUS)
 	$(PY) -m yali_b200.launch -np $(GPUS) $(BIN)/benchmark_nccl_mpi 33554432 200 0 auto 0 cuda-events fp32

@@ -13,8 +13,10 @@
 #include <string>
 #include <vector>
 
+#include "comm/layout.h"
 #include "comm/topology.h"
 #include "core/status.h"
+#include "ops/tuning.h"
 
 namespace bench {
 
@@ -81,6 +83,19 @@ inline void Usage(const char* prog, const char* what) {
     std::printf("  dtype      fp32 | fp16 | bf16 (or YALI_DTYPE)\n");
     std::printf("  gpus       ranks, one GPU each (default 2, or YALI_GPUS)\n");
     std::printf("  symmetric  1: buffers from the communicator's symmetric heap (default), 0: cudaMalloc\n");
+}
+
+// Kernel name of the result line ("YALI (Flash-fp32, ...)" in the reference's format).
+inline const char* KernelLabel(yali::Variant v, uint32_t flags) {
+    switch (v) {
+        case yali::Variant::Flash: return (flags & yali::kFlagLowLatency) ? "FlashLL" : "Flash";
+        case yali::Variant::Stream: return "Stream";
+        case yali::Variant::NvlsOneShot: return "NVLS1";
+        case yali::Variant::NvlsTwoShot: return "NVLS2";
+        case yali::Variant::FlashPull: return "FlashPull";
+        case yali::Variant::StreamDirect: return "StreamDirect";
+    }
+    return "?";
 }
 
 struct Stats {

@@ -102,8 +102,12 @@ int main(int argc, char** argv) {
     for (int i = 0; i < a.warmup; ++i) call();
     sync_all();
 
+    if (a.timing == bench::TimingMode::Graph) {
+        std::fprintf(stderr, "timing 'graph' needs one graph per process: use benchmark_yali_mpi (one GPU per rank)\n");
+        return 2;
+    }
     double avg_us = 0;
-    bench::Stats per_call;
+    bench::Stats per_call, dev_calls, dev_cadence;
     const int nev = emulate ? 1 : W;
     if (a.timing == bench::TimingMode::CudaEvents) {
         std::vector<std::vector<cudaEvent_t>> ev(nev, std::vector<cudaEvent_t>(a.calls + 1));
@@ -142,12 +146,35 @@ int main(int argc, char** argv) {
             CK(cudaEventCreate(&b1[i]));
             CK(cudaEventRecord(b0[i], st[i]));
         }
+        comm->SetTrace(true);  // the kernels stamp their own start and end: per-call times without host jitter
         for (int c = 0; c < a.calls; ++c) call();
+        comm->SetTrace(false);
         for (int i = 0; i < nev; ++i) {
             CK(cudaSetDevice(comm->device_of(i)));
             CK(cudaEventRecord(b1[i], st[i]));
         }
         sync_all();
+        {
+            // Device timeline: duration of call c = max over ranks of (last CTA out - first CTA in);
+            // cadence = max over ranks of the distance between the ends of consecutive calls.
+            const int want = std::min(a.calls, 4096);
+            std::vector<double> dur(want, 0.0), cad(want > 1 ? want - 1 : 0, 0.0);
+            std::vector<uint64_t> buf(static_cast<size_t>(want) * 2);
+            bool ok = want > 0;
+            for (int i = 0; i < nev && ok; ++i) {
+                uint64_t calls_seen = 0;
+                const int n = comm->ReadTrace(i, buf.data(), want, &calls_seen);
+                ok = n == want;
+                for (int c = 0; c < n; ++c) {
+                    dur[c] = std::max(dur[c], (buf[2 * c + 1] - buf[2 * c]) * 1e-3);
+                    if (c > 0) cad[c - 1] = std::max(cad[c - 1], (buf[2 * c + 1] - buf[2 * c - 1]) * 1e-3);
+                }
+            }
+            if (ok) {
+                dev_calls = bench::Summarise(dur);
+                dev_cadence = bench::Summarise(cad);
+            }
+        }
         double batch = 0;
         for (int i = 0; i < nev; ++i) {
             float ms = 0;
@@ -173,11 +200,16 @@ int main(int argc, char** argv) {
         per_call = bench::Summarise(per);
     }
     const LastCallInfo& lc = comm->last_call();
-    char extra[160];
-    std::snprintf(extra, sizeof(extra), "\"ctas\":%u,\"slot_bytes\":%u,\"symmetric\":%d,\"emulated\":%d", lc.ctas,
-                  lc.slot_bytes, a.symmetric ? 1 : 0, emulate ? 1 : 0);
-    const char* kname = lc.variant == Variant::Flash ? "Flash" : lc.variant == Variant::Stream ? "Stream"
-                        : lc.variant == Variant::NvlsOneShot ? "NVLS1" : "NVLS2";
+    char extra[512];
+    int len = std::snprintf(extra, sizeof(extra), "\"variant\":\"%s\",\"ctas\":%u,\"slot_bytes\":%u,\"stages\":%u,"
+                            "\"symmetric\":%d,\"emulated\":%d", VariantName(lc.variant), lc.ctas, lc.slot_bytes,
+                            lc.stages, a.symmetric ? 1 : 0, emulate ? 1 : 0);
+    if (dev_calls.n)
+        std::snprintf(extra + len, sizeof(extra) - len,
+                      ",\"dev_p50_us\":%.3f,\"dev_p99_us\":%.3f,\"dev_max_us\":%.3f,\"cadence_p50_us\":%.3f,"
+                      "\"cadence_p99_us\":%.3f,\"dev_samples\":%zu",
+                      dev_calls.p50, dev_calls.p99, dev_calls.max, dev_cadence.p50, dev_cadence.p99, dev_calls.n);
+    const char* kname = bench::KernelLabel(lc.variant, lc.flags);
     bench::Report("YALI", kname, a, W, avg_us, &per_call, extra);
     int rc = 0;
     if (a.verify) {

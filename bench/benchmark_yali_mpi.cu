@@ -78,6 +78,7 @@ int main(int argc, char** argv) {
     Bootstrap* bs = comm.impl()->bootstrap();
     std::vector<double> per(a.calls, 0.0);
     double total_us = 0;
+    bool traced = false;
     if (a.timing == bench::TimingMode::CudaEvents) {
         std::vector<cudaEvent_t> ev(a.calls + 1);
         for (auto& e : ev) CK(cudaEventCreate(&e));
@@ -100,7 +101,10 @@ int main(int argc, char** argv) {
         CK(cudaEventCreate(&b0));
         CK(cudaEventCreate(&b1));
         CK(cudaEventRecord(b0, st));
+        comm.impl()->SetTrace(true);  // kernels stamp their own start and end (no host jitter)
         for (int c = 0; c < a.calls; ++c) call();
+        comm.impl()->SetTrace(false);
+        traced = true;
         CK(cudaEventRecord(b1, st));
         CK(comm.sync());
         CK(cudaEventElapsedTime(&ms, b0, b1));
@@ -110,8 +114,13 @@ int main(int argc, char** argv) {
         // second one is timed.
         cudaGraph_t graph;
         cudaGraphExec_t exec;
+        call();  // outside the capture: one-time kernel attributes
+        CK(comm.sync());
         CK(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
+        comm.impl()->SetTrace(true);
         for (int c = 0; c < a.calls; ++c) call();
+        comm.impl()->SetTrace(false);
+        traced = true;
         CK(cudaStreamEndCapture(st, &graph));
         CK(cudaGraphInstantiate(&exec, graph, 0));
         cudaEvent_t g0, g1;
@@ -155,6 +164,36 @@ int main(int argc, char** argv) {
             else total_us = m;
         }
     }
+    // Device timeline of the last batch: duration (first CTA in -> last CTA out) and cadence (end to
+    // end of consecutive calls), call by call the max over ranks.
+    bench::Stats dev_calls, dev_cadence;
+    if (traced) {
+        const int want = std::min(a.calls, 4096);
+        std::vector<uint64_t> buf(static_cast<size_t>(want) * 2);
+        uint64_t seen = 0;
+        const int n = comm.impl()->ReadTrace(0, buf.data(), want, &seen);
+        std::vector<double> mine(static_cast<size_t>(want) * 2, 0.0);
+        for (int c = 0; c < n; ++c) {
+            mine[c] = (buf[2 * c + 1] - buf[2 * c]) * 1e-3;
+            if (c > 0) mine[want + c] = (buf[2 * c + 1] - buf[2 * c - 1]) * 1e-3;
+        }
+        std::vector<double> all(mine.size() * W);
+        if (bs && W > 1) {
+            if (bs->allgather(mine.data(), all.data(), mine.size() * sizeof(double)) != Result::Success) return 4;
+        } else {
+            all = mine;
+        }
+        std::vector<double> dur(want, 0.0), cad(want > 1 ? want - 1 : 0, 0.0);
+        for (int r = 0; r < (bs && W > 1 ? W : 1); ++r)
+            for (int c = 0; c < want; ++c) {
+                dur[c] = std::max(dur[c], all[r * mine.size() + c]);
+                if (c > 0) cad[c - 1] = std::max(cad[c - 1], all[r * mine.size() + want + c]);
+            }
+        if (n == want && want > 0) {
+            dev_calls = bench::Summarise(dur);
+            dev_cadence = bench::Summarise(cad);
+        }
+    }
     int ok = 1;
     if (a.verify) ok = ValidateRandomResult(recv, a.elements, a.dtype, a.dtype, kDistUniformPm1, 1234, W, 1.0f, nullptr);
     if (bs && W > 1) {
@@ -167,11 +206,16 @@ int main(int argc, char** argv) {
                              ? bench::Stats()
                              : bench::Summarise(per);
         const LastCallInfo& lc = comm.impl()->last_call();
-        char extra[160];
-        std::snprintf(extra, sizeof(extra), "\"ctas\":%u,\"slot_bytes\":%u,\"symmetric\":%d,\"processes\":%d", lc.ctas,
-                      lc.slot_bytes, a.symmetric ? 1 : 0, W);
-        const char* kname = lc.variant == Variant::Flash ? "Flash" : lc.variant == Variant::Stream ? "Stream"
-                            : lc.variant == Variant::NvlsOneShot ? "NVLS1" : "NVLS2";
+        char extra[512];
+        int len = std::snprintf(extra, sizeof(extra), "\"variant\":\"%s\",\"ctas\":%u,\"slot_bytes\":%u,\"stages\":%u,"
+                                "\"symmetric\":%d,\"processes\":%d", VariantName(lc.variant), lc.ctas, lc.slot_bytes,
+                                lc.stages, a.symmetric ? 1 : 0, W);
+        if (dev_calls.n)
+            std::snprintf(extra + len, sizeof(extra) - len,
+                          ",\"dev_p50_us\":%.3f,\"dev_p99_us\":%.3f,\"dev_max_us\":%.3f,\"cadence_p50_us\":%.3f,"
+                          "\"cadence_p99_us\":%.3f,\"dev_samples\":%zu",
+                          dev_calls.p50, dev_calls.p99, dev_calls.max, dev_cadence.p50, dev_cadence.p99, dev_calls.n);
+        const char* kname = bench::KernelLabel(lc.variant, lc.flags);
         bench::Report("YALI", kname, a, W, total_us / a.calls, &s, extra);
         if (a.verify) std::printf("Correctness: %s\n", ok ? "PASSED" : "FAILED");
     }

@@ -82,6 +82,8 @@ int yali_c_make_plan(int world, uint64_t count, int in_dt, int out_dt, int epilo
     caps.vec_ok = c->vec_ok != 0;
     caps.max_ctas = c->max_ctas;
     caps.ll_cap = c->ll_cap;
+    caps.peer_send = c->peer_send != 0;
+    caps.in_place = c->in_place != 0;
     TuningTable table;
     const TuningTable* tp = nullptr;
     std::string e;
@@ -105,6 +107,8 @@ int yali_c_make_plan(int world, uint64_t count, int in_dt, int out_dt, int epilo
     out->max_iters = p.max_iters;
     out->flags = p.flags;
     out->shard_elems = p.shard_elems;
+    out->stages = p.stages;
+    out->smem_bytes = p.smem_bytes;
     return 0;
 }
 

@@ -49,13 +49,15 @@ typedef struct YaliPlanCaps {
     int has_multicast, symmetric, peer_recv, vec_ok;
     uint32_t max_ctas;
     uint64_t ll_cap;
+    int peer_send, in_place; /* every input peer-addressable; some rank reduces in place */
 } YaliPlanCaps;
 typedef struct YaliPlan {
-    int variant; /* 0 flash, 1 stream, 2 nvls one-shot, 3 nvls two-shot */
+    int variant; /* 0 flash, 1 stream, 2 nvls one-shot, 3 nvls two-shot, 4 pipelined one-shot pull, 5 pipelined two-shot */
     uint32_t ctas, slot_bytes, max_iters, flags;
     uint64_t shard_elems;
+    uint32_t stages, smem_bytes;
 } YaliPlan;
-/* mode: 0 auto, 1 flash, 2 stream, 3 nvls.  tuning_json may be NULL.  Returns a Result code. */
+/* mode: 0 auto, 1 flash, 2 stream, 3 nvls, 4 flash_pull, 5 stream_direct.  tuning_json may be NULL.  Returns a Result code. */
 int yali_c_make_plan(int world, uint64_t count, int in_dtype, int out_dtype, int epilogue, int mode,
                      const YaliPlanCaps* caps, const char* tuning_json, YaliPlan* plan, char* err, size_t err_len);
 int yali_c_heap_layout(int world, uint64_t requested_total, uint64_t* fields /* 14 values: the 12 region fields, then ll_off, ll_cap */);

@@ -32,6 +32,17 @@
  * and again whenever `world` differs from the previous call on the device.  Make the
  * first call before you start capturing a stream.
  *
+ * Waits: ranks wait for one another inside the kernel with a two-second limit.  All ranks
+ * run in one cooperative launch, so the limit cannot be reached in practice; should it
+ * ever be (a GPU so loaded that co-resident CTAs starve for seconds), the call still
+ * returns cudaSuccess, the outputs are incomplete and later calls on that device keep
+ * failing the same way until a call with a different `world` clears the flag words.
+ * This entry point has no status block to report through; use a communicator where that
+ * matters.
+ *
+ * Alignment: any element-aligned pointers work, and ranks may differ (a rank whose
+ * buffers are not 16-byte aligned is merely slower).
+ *
  * Sharing: all calls on a device use the same scratch array, and the array keeps
  * what the last call left there.  Calls are safe one after another in one stream (or
  * otherwise ordered); two calls that overlap on the GPU race on the scratch and give

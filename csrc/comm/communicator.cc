@@ -36,7 +36,9 @@ bool MakeHeapLayout(int world, uint64_t requested_total, uint64_t granularity, H
         l.nvls_cap = 64 * MiB;
         off += 2 * l.nvls_cap;
         l.gemm_off = off;
-        l.gemm_cap = std::max<uint64_t>(4 * MiB, 16 * MiB / world);  // 2048 rows of 4096 bf16 sharded over the ranks
+        // 2048 rows of 4096 bf16 sharded over the ranks; a whole number of MiB, so that every region
+        // after it stays aligned for any world size (16 MiB / 3 is not even a multiple of 16 bytes).
+        l.gemm_cap = std::max<uint64_t>(4 * MiB, RoundUp(16 * MiB / world, MiB));
         off += 2ull * world * l.gemm_cap;
         l.ll_off = off;
         l.ll_cap = 1 * MiB;
@@ -172,6 +174,8 @@ Result Communicator::Init(const CommOptions& opt, std::string* err) {
     // Emulated ranks share one GPU and run in one cooperative launch: every CTA of every
     // rank must be resident (two 512-thread CTAs per SM are guaranteed by the launch bounds).
     max_ctas_ = emulated_ ? std::max(1, prop.multiProcessorCount * 2 / world_) : prop.multiProcessorCount * 8;
+    sm_count_ = static_cast<uint32_t>(std::max(1, prop.multiProcessorCount));
+    args_scratch_.resize(local_.size());
 
     for (Local& l : local_) {
         if (cudaSetDevice(l.device) != cudaSuccess || cudaStreamCreate(&l.stream) != cudaSuccess ||
@@ -292,6 +296,46 @@ Result Communicator::ResolvePeers(const void* const* send, void* const* recv, ui
     return Result::Success;
 }
 
+// Kernels that use more than 48 KiB of dynamic shared memory need the limit raised once per
+// (kernel, device).
+Result Communicator::EnsureSmemAttr(const void* fn, uint32_t smem_bytes) {
+    if (smem_bytes <= 48u * 1024u) return Result::Success;
+    for (int i = 0; i < nlocal(); ++i) {
+        const std::pair<const void*, int> key(fn, local_[i].device);
+        if (std::find(smem_attr_set_.begin(), smem_attr_set_.end(), key) != smem_attr_set_.end()) continue;
+        if (nlocal() > 1 && !emulated_) cudaSetDevice(local_[i].device);
+        cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if (e != cudaSuccess) {
+            (void)cudaGetLastError();
+            return Fail(Result::CudaError, std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(e));
+        }
+        smem_attr_set_.push_back(key);
+    }
+    return Result::Success;
+}
+
+int Communicator::ReadTrace(int local_index, uint64_t* out, int max_entries, uint64_t* calls) {
+    if (local_index < 0 || local_index >= nlocal() || !out || max_entries <= 0) return 0;
+    const Local& l = local_[local_index];
+    cudaSetDevice(l.device);
+    const char* flags = heaps_->base(l.rank) + lay_.flags_off;
+    uint32_t idx = 0;
+    std::vector<uint64_t> ring(static_cast<size_t>(kTraceCap) * 2);
+    if (cudaMemcpy(&idx, flags + kCallTraceIdx * 4ull, 4, cudaMemcpyDeviceToHost) != cudaSuccess ||
+        cudaMemcpy(ring.data(), flags + kTraceOff * 4ull, ring.size() * 8, cudaMemcpyDeviceToHost) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return 0;
+    }
+    if (calls) *calls = idx;
+    const uint32_t n = std::min<uint32_t>(std::min<uint32_t>(idx, kTraceCap), static_cast<uint32_t>(max_entries));
+    for (uint32_t k = 0; k < n; ++k) {
+        const uint32_t call = idx - n + k;
+        out[2 * k] = ring[(call % kTraceCap) * 2];
+        out[2 * k + 1] = ring[(call % kTraceCap) * 2 + 1];
+    }
+    return static_cast<int>(n);
+}
+
 Result Communicator::Launch(const Plan& plan, Dtype in, Dtype out, int epilogue, CollArgs* args,
                             const cudaStream_t* streams) {
     const void* fn = nullptr;
@@ -311,6 +355,15 @@ Result Communicator::Launch(const Plan& plan, Dtype in, Dtype out, int epilogue,
             if (emulated_) return Fail(Result::Unsupported, "multicast kernels cannot run on emulated ranks");
             fn = NvlsKernelFor(in, world_, plan.variant == Variant::NvlsTwoShot);
             threads = kNvlsThreads;
+            {
+                static const long long dev_threads = env::GetInt("YALI_DEV_THREADS", 0);  // tuning sweeps only
+                if (dev_threads >= 64 && dev_threads <= kNvlsThreads) threads = static_cast<int>(dev_threads) / 32 * 32;
+            }
+            break;
+        case Variant::FlashPull:
+        case Variant::StreamDirect:
+            fn = DirectKernelFor(in, out, world_, plan.variant == Variant::FlashPull, emulated_);
+            threads = kDirectThreads;
             break;
     }
     if (!fn) return Fail(Result::Unsupported, "no kernel for this dtype / epilogue combination");
@@ -320,13 +373,18 @@ Result Communicator::Launch(const Plan& plan, Dtype in, Dtype out, int epilogue,
         const int vec_per_row = args[0].ep.hidden / vec;
         threads = std::min(kFlashThreads, std::max(32, (vec_per_row + 31) / 32 * 32));
     }
+    const uint32_t smem = plan.smem_bytes;
+    if (smem > 0) {
+        Result r = EnsureSmemAttr(fn, smem);
+        if (r != Result::Success) return r;
+    }
     if (emulated_) {
         EmuArgs e;
         std::memset(&e, 0, sizeof(e));
         for (int i = 0; i < nlocal(); ++i) e.r[local_[i].rank] = args[i];
         cudaStream_t s = streams && streams[0] ? streams[0] : local_[0].stream;
         void* params[] = {&e};
-        cudaError_t ce = cudaLaunchCooperativeKernel(fn, dim3(plan.ctas, world_), dim3(threads), params, 0, s);
+        cudaError_t ce = cudaLaunchCooperativeKernel(fn, dim3(plan.ctas, world_), dim3(threads), params, smem, s);
         if (ce != cudaSuccess) {
             (void)cudaGetLastError();
             return Fail(Result::CudaError, std::string("cooperative launch failed: ") + cudaGetErrorString(ce));
@@ -350,7 +408,7 @@ Result Communicator::Launch(const Plan& plan, Dtype in, Dtype out, int epilogue,
             }
             cudaEventRecord(l.prof_start, s);
         }
-        cudaError_t ce = cudaLaunchKernel(fn, dim3(plan.ctas), dim3(threads), params, 0, s);
+        cudaError_t ce = cudaLaunchKernel(fn, dim3(plan.ctas), dim3(threads), params, smem, s);
         if (ce != cudaSuccess) {
             (void)cudaGetLastError();
             return Fail(Result::CudaError, std::string("kernel launch failed: ") + cudaGetErrorString(ce));
@@ -378,11 +436,17 @@ Result Communicator::Collective(const void* const* send, void* const* recv, uint
     const uint64_t send_elems = ag_only ? shard : count, recv_elems = rs_only ? shard : count;
     const uint64_t send_bytes = send_elems * DtypeSize(in), recv_bytes = recv_elems * DtypeSize(out);
 
-    std::vector<CollArgs> args(nlocal());
-    std::memset(args.data(), 0, sizeof(CollArgs) * args.size());
+    CollArgs* const args = args_scratch_.data();  // reused: no allocation on the per-call path
+    std::memset(args, 0, sizeof(CollArgs) * args_scratch_.size());
     bool peer_recv = false, symmetric = false;
-    Result r = ResolvePeers(send, recv, send_bytes, recv_bytes, opt.buffers_stable, args.data(), &peer_recv, &symmetric);
+    Result r = ResolvePeers(send, recv, send_bytes, recv_bytes, opt.buffers_stable, args, &peer_recv, &symmetric);
     if (r != Result::Success) return r;
+    bool in_place = false;
+    for (int i = 0; i < nlocal(); ++i) {
+        const char* s0 = static_cast<const char*>(send[i]);
+        const char* r0 = static_cast<const char*>(recv[i]);
+        if (s0 < r0 + recv_bytes && r0 < s0 + send_bytes) in_place = true;
+    }
 
     PlanCaps caps;
     caps.flash_cap = lay_.flash_cap;
@@ -392,6 +456,10 @@ Result Communicator::Collective(const void* const* send, void* const* recv, uint
     caps.has_multicast = has_multicast();
     caps.symmetric = symmetric;
     caps.peer_recv = peer_recv && !rs_only;
+    caps.peer_send = peer_recv;  // ResolvePeers fills both tables or neither
+    caps.in_place = in_place;
+    caps.half_collective = rs_only || ag_only;
+    caps.sm_count = sm_count_;
     caps.max_ctas = max_ctas_;
     caps.force_ctas = opt.ctas > 0 ? static_cast<uint32_t>(opt.ctas) : 0u;
     caps.force_slot_bytes = opt.slot_bytes > 0 ? static_cast<uint32_t>(opt.slot_bytes) : 0u;
@@ -425,23 +493,28 @@ Result Communicator::Collective(const void* const* send, void* const* recv, uint
 
     // Call numbers (one-shot epoch, ring sequence base, barrier epoch) live in each rank's heap
     // and are advanced by the kernels; the host keeps no per-call state.
-    const uint32_t epoch = 0, seq_base = 0;
     plan.flags |= extra_flags;
+    if (trace_) plan.flags |= kFlagTrace;
+    // Only the staged one-shot kernel may treat alignment as a per-rank property: its CTA slices do
+    // not depend on it, and a rank touches nothing but its own buffers and the (aligned) staging.
+    // Every other kernel uses the flag all local ranks share: the ring kernel's direct all-gather
+    // and the pipelined kernels store 16-byte vectors into the peers' outputs.
+    const bool per_rank_alignment = plan.variant == Variant::Flash && !(plan.flags & kFlagLowLatency);
     for (int i = 0; i < nlocal(); ++i) {
         CollArgs& a = args[i];
         a.cv = View(i);
         a.send = send[i];
         a.recv = recv[i];
         a.count = count;
-        a.epoch = epoch;
-        a.seq_base = seq_base;
+        a.stages = plan.stages;
         a.ctas = plan.ctas;
         a.slot_bytes = plan.slot_bytes;
         a.shard_elems = plan.shard_elems;
         a.flags = plan.flags;
-        // Alignment is a per-rank property: it selects the vector or the scalar code path only.
-        if (!(Aligned16(send[i]) && Aligned16(recv[i]))) a.flags &= ~static_cast<uint32_t>(kFlagVecOk);
-        else a.flags |= kFlagVecOk;
+        if (per_rank_alignment) {
+            if (!(Aligned16(send[i]) && Aligned16(recv[i]))) a.flags &= ~static_cast<uint32_t>(kFlagVecOk);
+            else a.flags |= kFlagVecOk;
+        }
         if (opt.skip_rank >= 0 && local_[i].rank == opt.skip_rank) a.flags |= kFlagSkipRank;
         a.ep = ep;
         if (opt.epilogue == kEpiResidualRmsNorm) {
@@ -453,12 +526,13 @@ Result Communicator::Collective(const void* const* send, void* const* recv, uint
     last_.variant = plan.variant;
     last_.ctas = plan.ctas;
     last_.slot_bytes = plan.slot_bytes;
+    last_.stages = plan.stages;
     last_.flags = plan.flags;
-    if (env::DebugLevel() > 1 && local_[0].rank == 0)
-        std::fprintf(stderr, "[yali] %s count=%llu ctas=%u slot=%u flags=0x%x epoch=%u seq=%u\n",
-                     VariantName(plan.variant), static_cast<unsigned long long>(count), plan.ctas, plan.slot_bytes,
-                     plan.flags, epoch, seq_base);
-    return Launch(plan, in, out, opt.epilogue, args.data(), streams);
+    static const int debug_level = env::DebugLevel();
+    if (debug_level > 1 && local_[0].rank == 0)
+        std::fprintf(stderr, "[yali] %s count=%llu ctas=%u slot=%u stages=%u flags=0x%x\n", VariantName(plan.variant),
+                     static_cast<unsigned long long>(count), plan.ctas, plan.slot_bytes, plan.stages, plan.flags);
+    return Launch(plan, in, out, opt.epilogue, args, streams);
 }
 
 Result Communicator::AllReduce(const void* const* send, void* const* recv, uint64_t count, Dtype in, Dtype out,

@@ -55,6 +55,7 @@ struct LastCallInfo {
     Variant variant = Variant::Flash;
     uint32_t ctas = 0;
     uint32_t slot_bytes = 0;
+    uint32_t stages = 0;
     uint32_t flags = 0;
     uint64_t launches = 0;  // kernels launched by this process since creation
 };
@@ -132,6 +133,15 @@ class Communicator {
     void set_error(const std::string& e) { err_ = e; }
     void CountLaunch(uint64_t n = 1) { last_.launches += n; }
 
+    // Device-side timeline: while enabled, every collective stamps %globaltimer when its first
+    // CTA starts and when its last CTA checks out (kTraceOff ring in this rank's heap).
+    void SetTrace(bool on) { trace_ = on; }
+    bool trace() const { return trace_; }
+    // Copies the timeline of local rank `local_index` out (after the caller has synchronised):
+    // `calls` = traced calls so far; `out` receives the last min(calls, kTraceCap, max_entries)
+    // {start_ns, end_ns} pairs, oldest first.  Returns the number of pairs written.
+    int ReadTrace(int local_index, uint64_t* out, int max_entries, uint64_t* calls);
+
    private:
     struct Local {
         int rank = 0;
@@ -154,6 +164,7 @@ class Communicator {
                       const OpOptions& opt, const cudaStream_t* streams, uint32_t extra_flags);
     Result ResolvePeers(const void* const* send, void* const* recv, uint64_t send_bytes, uint64_t recv_bytes,
                         bool stable, CollArgs* args, bool* peer_recv, bool* symmetric);
+    Result EnsureSmemAttr(const void* fn, uint32_t smem_bytes);
     Result Fail(Result r, const std::string& what) {
         err_ = what;
         return r;
@@ -168,6 +179,10 @@ class Communicator {
     HeapLayout lay_{};
     uint64_t timeout_ns_ = 0;
     uint32_t max_ctas_ = 296;
+    uint32_t sm_count_ = 148;
+    bool trace_ = false;
+    std::vector<CollArgs> args_scratch_;  // per-call argument blocks, reused (no allocation per call)
+    std::vector<std::pair<const void*, int>> smem_attr_set_;  // (kernel, device) pairs with the smem limit raised
     // Epochs: identical on every rank because every rank performs the same calls.
     uint32_t flash_epoch_ = 0;
     uint32_t bar_epoch_ = 0;

@@ -32,6 +32,7 @@ constexpr uint32_t kCallFlashEpochHi = 5;  // upper half of the one-shot call nu
 constexpr uint32_t kCallGemmCnt = 4;      // arrivals (per source) this rank has been promised so far
 constexpr uint32_t kCallGemmDone = 8;     // [kMaxRanks] rows each owner has been asked to deliver so far
 constexpr uint32_t kCallDoneCtas = 16;    // [4] CTAs of the running launch that have finished, per kernel kind
+constexpr uint32_t kCallTraceIdx = 20;    // traced calls so far (index into the kTraceOff ring)
 constexpr uint32_t kFlashFlagOff = 32;                                       // [kMaxFlashCtas][kMaxRanks]
 constexpr uint32_t kRsSeqOff = kFlashFlagOff + kMaxFlashCtas * kMaxRanks;    // [kMaxLanes][kMaxRanks]
 constexpr uint32_t kAgSeqOff = kRsSeqOff + kMaxLanes * kMaxRanks;            // [kMaxLanes][kMaxRanks]
@@ -40,11 +41,17 @@ constexpr uint32_t kBarOff = kCreditOff + kMaxLanes * kMaxRanks;             // 
 constexpr uint32_t kGemmCntOff = kBarOff + kBarSlots * kMaxRanks;            // [kGemmRowBlocks][kMaxRanks]
 constexpr uint32_t kGemmDoneOff = kGemmCntOff + kGemmRowBlocks * kMaxRanks;  // [kGemmRowBlocks][kMaxRanks]
 constexpr uint32_t kStatusCntOff = kGemmDoneOff + kGemmRowBlocks * kMaxRanks;  // [1] timeouts seen by this rank
-constexpr uint32_t kFlagWords = kStatusCntOff + 8;
+// Device-side timeline of the collectives (kFlagTrace): call i writes %globaltimer at the entry of
+// its first CTA and at the check-out of its last CTA into entry i % kTraceCap.
+constexpr uint32_t kTraceCap = 4096;
+constexpr uint32_t kTraceOff = kStatusCntOff + 8;              // [kTraceCap][2] uint64 = 4 words per call
+constexpr uint32_t kFlagWords = kTraceOff + kTraceCap * 4;
 constexpr uint64_t kFlagRegionBytes = 1ull << 20;
 static_assert(kFlagWords * 4ull <= kFlagRegionBytes, "flag region too small");
+static_assert(kTraceOff % 2 == 0, "the timeline entries are 64-bit words");
 
 constexpr int kRingCap = 4;  // slots per (lane, source) ring
+constexpr uint32_t kMaxPipelineStages = 8;  // shared-memory stages of the pipelined kernels
 
 struct HeapLayout {
     uint64_t total_bytes;
@@ -123,10 +130,10 @@ struct CollArgs {
     const void* peer_send[kMaxRanks];   // inputs of all ranks when they are peer-addressable, else nullptr
     void* peer_recv[kMaxRanks];         // outputs of all ranks when they are peer-addressable, else nullptr
     uint64_t count;                     // elements
-    uint32_t epoch;                     // one-shot / barrier epoch of this call
-    uint32_t seq_base;                  // two-shot: sequence number before this call
-    uint32_t ctas;                      // CTAs (one-shot, NVLS) or lanes (two-shot) per rank
-    uint32_t slot_bytes;                // two-shot ring slot size
+    uint32_t stages;                    // pipelined kernels: shared-memory stages per CTA
+    uint32_t reserved;
+    uint32_t ctas;                      // CTAs (one-shot, NVLS, pipelined) or lanes (two-shot ring) per rank
+    uint32_t slot_bytes;                // two-shot ring slot size; pipelined kernels: bytes per source and stage
     uint64_t shard_elems;               // two-shot / NVLS: elements owned by each rank
     uint32_t flags;                     // CollFlags
     EpilogueParams ep;
@@ -140,6 +147,8 @@ enum CollFlags : uint32_t {
     kFlagAllGatherOnly = 1u << 4,
     kFlagLowLatency = 1u << 6,  // one-shot: flag-in-data protocol (no separate flag, no release fence)
     kFlagSkipRank = 1u << 5,    // this rank leaves at once (models a rank that never launched; tests of the timeouts)
+    kFlagTrace = 1u << 7,       // stamp %globaltimer at entry and check-out into the kTraceOff ring
+    kFlagPullOneShot = 1u << 8, // pipelined kernel: every rank pulls and sums the whole message (no pushes)
 };
 
 // All ranks of an emulated communicator in one launch (ranks = blockIdx.y).

@@ -14,13 +14,25 @@ using yali::Bootstrap;
 namespace {
 Bootstrap* BS(YaliMPComm* c) { return static_cast<Bootstrap*>(c->bootstrap); }
 
-// Imported base pointers are remembered so that closing works on interior pointers.
+// Imported base pointers are remembered so that closing works on interior pointers, and an
+// allocation that is imported more than once (several exported pointers inside one allocation
+// share its handle) is opened only once per process: a second cudaIpcOpenMemHandle of the same
+// handle is an error.
 struct Imported {
     void* user;
     void* base;
 };
+struct Opened {
+    cudaIpcMemHandle_t handle;
+    void* base;
+    int refs;
+};
 std::vector<Imported>& ImportTable() {
     static std::vector<Imported> t;
+    return t;
+}
+std::vector<Opened>& OpenTable() {
+    static std::vector<Opened> t;
     return t;
 }
 }  // namespace
@@ -122,8 +134,18 @@ cudaError_t yaliIpcExport(void* devPtr, size_t size, YaliIpcHandle* h) {
 cudaError_t yaliIpcImport(const YaliIpcHandle* h, void** devPtr) {
     if (!h || !devPtr) return cudaErrorInvalidValue;
     void* base = nullptr;
-    cudaError_t e = cudaIpcOpenMemHandle(&base, h->handle, cudaIpcMemLazyEnablePeerAccess);
-    if (e != cudaSuccess) return e;
+    for (Opened& o : OpenTable()) {
+        if (std::memcmp(&o.handle, &h->handle, sizeof(cudaIpcMemHandle_t)) == 0) {
+            base = o.base;
+            ++o.refs;
+            break;
+        }
+    }
+    if (!base) {
+        cudaError_t e = cudaIpcOpenMemHandle(&base, h->handle, cudaIpcMemLazyEnablePeerAccess);
+        if (e != cudaSuccess) return e;
+        OpenTable().push_back({h->handle, base, 1});
+    }
     *devPtr = static_cast<char*>(base) + h->offset;
     ImportTable().push_back({*devPtr, base});
     return cudaSuccess;
@@ -136,6 +158,14 @@ cudaError_t yaliIpcClose(void* importedPtr) {
         if (t[i].user == importedPtr) {
             void* base = t[i].base;
             t.erase(t.begin() + i);
+            auto& open = OpenTable();
+            for (size_t k = 0; k < open.size(); ++k) {
+                if (open[k].base == base) {
+                    if (--open[k].refs > 0) return cudaSuccess;  // other imports still use the mapping
+                    open.erase(open.begin() + k);
+                    break;
+                }
+            }
             return cudaIpcCloseMemHandle(base);
         }
     }

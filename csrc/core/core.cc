@@ -32,6 +32,8 @@ bool ParseKernelMode(const char* s, KernelMode* out) {
     else if (!strcasecmp(s, "flash")) *out = KernelMode::Flash;
     else if (!strcasecmp(s, "stream")) *out = KernelMode::Stream;
     else if (!strcasecmp(s, "nvls")) *out = KernelMode::NVLS;
+    else if (!strcasecmp(s, "flash_pull")) *out = KernelMode::FlashPull;
+    else if (!strcasecmp(s, "stream_direct")) *out = KernelMode::StreamDirect;
     else return false;
     return true;
 }

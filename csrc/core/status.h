@@ -54,7 +54,9 @@ bool ParseDtype(const char* s, Dtype* out);
 // Interface-level aliases with the spelling of the reference's all_reduce.h.
 enum class DataType : int { Float32 = 0, Float16 = 1, BFloat16 = 2 };
 enum class ReduceOp : int { Sum = 0 };
-enum class KernelMode : int { Auto = 0, Flash = 1, Stream = 2, NVLS = 3 };
+// FlashPull / StreamDirect force the pipelined kernels that read the peers' inputs in place
+// (they need buffers every rank can address); Auto picks them when they apply.
+enum class KernelMode : int { Auto = 0, Flash = 1, Stream = 2, NVLS = 3, FlashPull = 4, StreamDirect = 5 };
 
 inline Dtype ToDtype(DataType d) { return static_cast<Dtype>(static_cast<int>(d)); }
 inline DataType ToDataType(Dtype d) { return static_cast<DataType>(static_cast<int>(d)); }
@@ -65,6 +67,8 @@ inline const char* KernelModeName(KernelMode m) {
         case KernelMode::Flash: return "flash";
         case KernelMode::Stream: return "stream";
         case KernelMode::NVLS: return "nvls";
+        case KernelMode::FlashPull: return "flash_pull";
+        case KernelMode::StreamDirect: return "stream_direct";
         case KernelMode::Auto: break;
     }
     return "auto";

@@ -108,9 +108,43 @@ __device__ __forceinline__ void advance_call_word(const CommView& cv, uint32_t w
     volatile uint32_t* w = flag_word(cv, cv.rank, word);
     *w = *w + inc;
 }
+// Device-side timeline (kFlagTrace): the first CTA stamps %globaltimer when it starts, the last CTA
+// to check out stamps it again and advances the ring index.  The host reads the ring after a
+// synchronisation and obtains per-call device times that contain no host jitter.
+__device__ __forceinline__ void trace_begin(const CommView& cv, uint32_t flags, uint32_t cta) {
+    if ((flags & kFlagTrace) && cta == 0 && threadIdx.x == 0) {
+        const uint32_t idx = *reinterpret_cast<volatile uint32_t*>(flag_word(cv, cv.rank, kCallTraceIdx));
+        volatile uint64_t* ring = reinterpret_cast<volatile uint64_t*>(flag_word(cv, cv.rank, kTraceOff));
+        ring[(idx % kTraceCap) * 2] = ptx::globaltimer();
+    }
+}
+__device__ __forceinline__ void trace_end(const CommView& cv, uint32_t flags) {
+    // thread 0 of the last CTA only
+    if (flags & kFlagTrace) {
+        volatile uint32_t* iw = flag_word(cv, cv.rank, kCallTraceIdx);
+        const uint32_t idx = *iw;
+        volatile uint64_t* ring = reinterpret_cast<volatile uint64_t*>(flag_word(cv, cv.rank, kTraceOff));
+        ring[(idx % kTraceCap) * 2 + 1] = ptx::globaltimer();
+        *iw = idx + 1;
+    }
+}
 __device__ __forceinline__ void finish_call(const CommView& cv, uint32_t kind, uint32_t word, uint32_t inc,
-                                            uint32_t nctas) {
-    if (threadIdx.x == 0 && check_out_last(cv, kind, nctas)) advance_call_word(cv, word, inc);
+                                            uint32_t nctas, uint32_t flags = 0) {
+    if (threadIdx.x == 0 && check_out_last(cv, kind, nctas)) {
+        advance_call_word(cv, word, inc);
+        trace_end(cv, flags);
+    }
+}
+
+// Bounded wait on an mbarrier phase: gives up at the deadline or when another thread of the CTA
+// has raised the abort flag.
+__device__ __forceinline__ bool mbar_wait_deadline(uint64_t* bar, uint32_t parity, uint64_t deadline_ns,
+                                                   volatile int* s_abort) {
+    uint32_t tries = 0;
+    while (!ptx::mbar_try_wait(bar, parity)) {
+        if ((++tries & 15u) == 0 && (*s_abort || ptx::globaltimer() > deadline_ns)) return false;
+    }
+    return true;
 }
 
 // Block-wide sum of one float per thread (all threads get the result).

@@ -85,22 +85,29 @@ __device__ __forceinline__ void flash_body(const CollArgs& a, uint32_t cta) {
     __shared__ int s_abort;
     __shared__ uint32_t s_epoch;
     if (tid == 0) s_abort = 0;
+    trace_begin(cv, a.flags, cta);
     const uint64_t deadline = ptx::globaltimer() + cv.timeout_ns;
     const uint32_t epoch = load_call_word(cv, kCallFlashEpoch, &s_epoch) + 1;  // this call's number
     const uint32_t parity = epoch & 1u;
 
-    // Slice of this CTA: vectors [vb, ve); the last CTA also takes the scalar tail [tb, te).
-    const uint64_t nvec = (a.flags & kFlagVecOk) ? a.count / VEC : 0;
-    const uint64_t per = (nvec + a.ctas - 1) / a.ctas;
-    const uint64_t vb = min(nvec, static_cast<uint64_t>(cta) * per), ve = min(nvec, vb + per);
-    uint64_t tb, te;  // scalar elements of this CTA
+    // Slice of this CTA: elements [eb, ee).  The boundaries depend only on `count` and the CTA
+    // count, which every rank shares, never on a rank's own pointer alignment: CTA c of one
+    // rank synchronises with CTA c of its peers only, so all of them must cover the same
+    // elements.  Alignment (kFlagVecOk, a per-rank property) only chooses how the slice is
+    // accessed: whole 16-byte vectors [vb, ve) plus a scalar remainder [tb, te), or scalars.
+    const uint64_t nvec_all = (a.count + VEC - 1) / VEC;
+    const uint64_t per_v = (nvec_all + a.ctas - 1) / a.ctas;
+    const uint64_t eb = min(a.count, static_cast<uint64_t>(cta) * per_v * VEC), ee = min(a.count, eb + per_v * VEC);
+    uint64_t vb, ve, tb, te;
     if (a.flags & kFlagVecOk) {
-        tb = nvec * VEC;
-        te = (cta == a.ctas - 1) ? a.count : tb;
-    } else {  // unaligned buffers: the whole message goes element by element, spread over all CTAs
-        const uint64_t per_e = (a.count + a.ctas - 1) / a.ctas;
-        tb = min(a.count, static_cast<uint64_t>(cta) * per_e);
-        te = min(a.count, tb + per_e);
+        ve = ee / VEC;
+        vb = min(ve, (eb + VEC - 1) / VEC);  // eb is a multiple of VEC unless the slice is empty
+        tb = max(ve * VEC, eb);
+        te = ee;
+    } else {
+        vb = ve = 0;
+        tb = eb;
+        te = ee;
     }
 
     push_slice<Tin, WORLD>(a, parity, vb, ve, tb, te);
@@ -163,7 +170,7 @@ __device__ __forceinline__ void flash_body(const CollArgs& a, uint32_t cta) {
             if (q < W) s += to_f32<Tin>(__ldcg(reinterpret_cast<const Tin*>(in[q]) + e));
         out[e] = from_f32<Tout>(epi(s));
     }
-    finish_call(cv, 0, kCallFlashEpoch, 1, a.ctas);
+    finish_call(cv, 0, kCallFlashEpoch, 1, a.ctas, a.flags);
 }
 
 // One-shot all-reduce fused with residual-add + RMSNorm.  The message is
@@ -181,6 +188,7 @@ __device__ __forceinline__ void flash_rmsnorm_body(const CollArgs& a, uint32_t c
     __shared__ float s_red[32];
     __shared__ uint32_t s_epoch;
     if (tid == 0) s_abort = 0;
+    trace_begin(cv, a.flags, cta);
     const uint64_t deadline = ptx::globaltimer() + cv.timeout_ns;
     const uint32_t epoch = load_call_word(cv, kCallFlashEpoch, &s_epoch) + 1;  // this call's number
     const uint32_t parity = epoch & 1u;
@@ -243,7 +251,7 @@ __device__ __forceinline__ void flash_rmsnorm_body(const CollArgs& a, uint32_t c
             }
         }
     }
-    finish_call(cv, 0, kCallFlashEpoch, 1, a.ctas);
+    finish_call(cv, 0, kCallFlashEpoch, 1, a.ctas, a.flags);
 }
 
 // Flag-in-data form of the one-shot all-reduce for small messages.  Every 16-byte line
@@ -274,6 +282,7 @@ __device__ __forceinline__ void flash_ll_body(const CollArgs& a, uint32_t cta) {
     const int W = world_of<WORLD>(cv), r = cv.rank;
     const int tid = threadIdx.x, nt = blockDim.x;
     __shared__ uint32_t s_call[2];
+    trace_begin(cv, a.flags, cta);
     if (tid < 2)
         s_call[tid] = *reinterpret_cast<volatile uint32_t*>(flag_word(cv, r, tid == 0 ? kCallFlashEpoch : kCallFlashEpochHi));
     __syncthreads();
@@ -345,6 +354,7 @@ __device__ __forceinline__ void flash_ll_body(const CollArgs& a, uint32_t cta) {
     if (tid == 0 && check_out_last(cv, 0, a.ctas)) {
         advance_call_word(cv, kCallFlashEpoch, 1);
         if (lo == 0u) advance_call_word(cv, kCallFlashEpochHi, 1);
+        trace_end(cv, a.flags);
     }
 }
 

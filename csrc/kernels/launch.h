@@ -18,6 +18,8 @@ namespace yali {
 constexpr int kFlashThreads = 512;
 constexpr int kStreamThreads = 512;
 constexpr int kNvlsThreads = 512;
+constexpr int kDirectThreads = 288;   // one producer warp + eight consumer warps
+constexpr int kDirectMaxStages = kMaxPipelineStages;
 
 // nullptr when the combination is not built.
 const void* FlashKernelFor(Dtype in, Dtype out, int epilogue, int world, bool emu);
@@ -25,5 +27,7 @@ const void* FlashKernelFor(Dtype in, Dtype out, int epilogue, int world, bool em
 const void* FlashLLKernelFor(Dtype dt, int world, bool emu);
 const void* StreamKernelFor(Dtype in, Dtype out, int epilogue, int world, bool emu);
 const void* NvlsKernelFor(Dtype dt, int world, bool two_shot);
+// Pipelined direct kernel (all buffers peer-addressable): one-shot pull or two-shot pull + push.
+const void* DirectKernelFor(Dtype in, Dtype out, int world, bool one_shot, bool emu);
 
 }  // namespace yali

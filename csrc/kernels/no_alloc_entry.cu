@@ -50,6 +50,10 @@ extern "C" cudaError_t yaliAllReduceLocalNoAlloc(const void* const* send, void* 
         return Refuse(cudaErrorInvalidValue, "world must be between 2 and YALI_NO_ALLOC_MAX_WORLD (4)");
     if (dtype < 0 || dtype > 2) return Refuse(cudaErrorInvalidValue, "dtype must be 0 (fp32), 1 (fp16) or 2 (bf16)");
     const Dtype dt = static_cast<Dtype>(dtype);
+    // Compare in elements first: count * element size could wrap around for absurd counts.
+    if (count > YALI_NO_ALLOC_MAX_BYTES / DtypeSize(dt))
+        return Refuse(cudaErrorInvalidValue,
+                      "message larger than YALI_NO_ALLOC_MAX_BYTES (262144 bytes per rank): the scratch array is fixed");
     const size_t bytes = count * DtypeSize(dt);
     if (bytes > YALI_NO_ALLOC_MAX_BYTES)
         return Refuse(cudaErrorInvalidValue,
@@ -116,6 +120,9 @@ extern "C" cudaError_t yaliAllReduceLocalNoAlloc(const void* const* send, void* 
         a.recv = recv[r];
         a.count = count;
         a.ctas = ctas;
+        // The kernel cuts the message into CTA slices from `count` and the CTA count alone, so a
+        // rank whose own buffers are not 16-byte aligned may fall back to scalar accesses without
+        // its peers noticing.
         const bool aligned = ((reinterpret_cast<uintptr_t>(send[r]) | reinterpret_cast<uintptr_t>(recv[r])) & 15u) == 0;
         a.flags = aligned ? kFlagVecOk : 0u;
         a.ep.scale = 1.0f;

@@ -64,6 +64,34 @@ __device__ __forceinline__ void copy16(char* dst, const char* src, uint64_t vb, 
     for (; v < ve; v += nt) ptx::st_v4(dst + v * 16, ptx::ld_cg_v4(src + v * 16));
 }
 
+
+// Vectors [vb, ve): sum over all ranks in the switch (multimem.ld_reduce), optional scale, then
+// either a plain store into this rank's output or a multimem.st that writes every rank's output.
+// U loads are in flight per thread before the first store.
+template <typename T, int U, bool BROADCAST>
+__device__ __forceinline__ void reduce_range(const char* mc_in, char* out, uint64_t vb, uint64_t ve, float scale,
+                                             bool scaled) {
+    const int tid = threadIdx.x, nt = blockDim.x;
+    uint64_t v = vb + tid;
+    for (; v + static_cast<uint64_t>(U - 1) * nt < ve; v += static_cast<uint64_t>(U) * nt) {
+        uint4 x[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) x[u] = mc_ld_reduce<T>(mc_in + (v + u * nt) * 16);
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const uint4 y = scaled ? scale16<T>(x[u], scale) : x[u];
+            if (BROADCAST) ptx::multimem_st_v4(out + (v + u * nt) * 16, y);
+            else ptx::st_v4(out + (v + u * nt) * 16, y);
+        }
+    }
+    for (; v < ve; v += nt) {
+        const uint4 x = mc_ld_reduce<T>(mc_in + v * 16);
+        const uint4 y = scaled ? scale16<T>(x, scale) : x;
+        if (BROADCAST) ptx::multimem_st_v4(out + v * 16, y);
+        else ptx::st_v4(out + v * 16, y);
+    }
+}
+
 // count*sizeof(T) is a multiple of 16 and all buffers are 16-byte aligned (the
 // dispatcher falls back to the peer-to-peer kernels otherwise).
 template <typename T, bool TWO_SHOT>
@@ -77,6 +105,7 @@ __global__ void __launch_bounds__(kNvlsThreads, 2) nvls_kernel(const __grid_cons
     __shared__ int s_abort;
     __shared__ uint32_t s_epoch;
     if (tid == 0) s_abort = 0;
+    trace_begin(cv, a.flags, cta);
     const uint32_t epoch = load_call_word(cv, kCallBarEpoch, &s_epoch);  // barrier epochs used before this call
     const uint64_t deadline = ptx::globaltimer() + cv.timeout_ns;
 
@@ -100,18 +129,8 @@ __global__ void __launch_bounds__(kNvlsThreads, 2) nvls_kernel(const __grid_cons
         if (!symmetric) copy16(heap + stage_off, send, vb, ve);
         if (!cta_barrier_all_ranks(cv, cta, epoch + 1, deadline, &s_abort)) return;
         const char* mc_in = cv.mc_heap + in_off;
-        uint64_t v = vb + tid;
-        for (; v + 3ull * nt < ve; v += 4ull * nt) {
-            uint4 x[4];
-#pragma unroll
-            for (int u = 0; u < 4; ++u) x[u] = mc_ld_reduce<T>(mc_in + (v + u * nt) * 16);
-#pragma unroll
-            for (int u = 0; u < 4; ++u) ptx::st_v4(recv + (v + u * nt) * 16, scaled ? scale16<T>(x[u], scale) : x[u]);
-        }
-        for (; v < ve; v += nt) {
-            uint4 x = mc_ld_reduce<T>(mc_in + v * 16);
-            ptx::st_v4(recv + v * 16, scaled ? scale16<T>(x, scale) : x);
-        }
+        if (a.stages == 8) reduce_range<T, 8, false>(mc_in, recv, vb, ve, scale, scaled);
+        else reduce_range<T, 4, false>(mc_in, recv, vb, ve, scale, scaled);
         // In-place user buffers may be overwritten by their owner right after this
         // kernel, so nobody leaves before everybody has read.  Staged input sits in
         // the half of the staging region that is not touched again before every
@@ -136,22 +155,22 @@ __global__ void __launch_bounds__(kNvlsThreads, 2) nvls_kernel(const __grid_cons
         }
         if (!cta_barrier_all_ranks(cv, cta, epoch + 1, deadline, &s_abort)) return;
         {
-            uint64_t vb, ve;
-            slice(r, &vb, &ve);
             const char* mc_in = cv.mc_heap + in_off;
             char* mc_out = cv.mc_heap + out_off;
-            uint64_t v = vb + tid;
-            for (; v + 3ull * nt < ve; v += 4ull * nt) {
-                uint4 x[4];
-#pragma unroll
-                for (int u = 0; u < 4; ++u) x[u] = mc_ld_reduce<T>(mc_in + (v + u * nt) * 16);
-#pragma unroll
-                for (int u = 0; u < 4; ++u)
-                    ptx::multimem_st_v4(mc_out + (v + u * nt) * 16, scaled ? scale16<T>(x[u], scale) : x[u]);
-            }
-            for (; v < ve; v += nt) {
-                uint4 x = mc_ld_reduce<T>(mc_in + v * 16);
-                ptx::multimem_st_v4(mc_out + v * 16, scaled ? scale16<T>(x, scale) : x);
+            if (symmetric && a.slot_bytes) {
+                // Interleaved blocks: the CTAs of a rank sweep its shard together (block c, c + nctas, ...)
+                // instead of each streaming through a distant slice of its own.
+                const uint64_t blk = a.slot_bytes / 16;
+                const uint64_t sb = min(total_vec, static_cast<uint64_t>(r) * shard_vec), se = min(total_vec, sb + shard_vec);
+                for (uint64_t b = sb + cta * blk; b < se; b += static_cast<uint64_t>(nctas) * blk) {
+                    if (a.stages == 8) reduce_range<T, 8, true>(mc_in, mc_out, b, min(se, b + blk), scale, scaled);
+                    else reduce_range<T, 4, true>(mc_in, mc_out, b, min(se, b + blk), scale, scaled);
+                }
+            } else {
+                uint64_t vb, ve;
+                slice(r, &vb, &ve);
+                if (a.stages == 8) reduce_range<T, 8, true>(mc_in, mc_out, vb, ve, scale, scaled);
+                else reduce_range<T, 4, true>(mc_in, mc_out, vb, ve, scale, scaled);
             }
         }
         if (!cta_barrier_all_ranks(cv, cta, epoch + 2, deadline, &s_abort)) return;
@@ -163,7 +182,7 @@ __global__ void __launch_bounds__(kNvlsThreads, 2) nvls_kernel(const __grid_cons
             }
         }
     }
-    finish_call(cv, 2, kCallBarEpoch, 2, nctas);
+    finish_call(cv, 2, kCallBarEpoch, 2, nctas, a.flags);
 }
 
 template <typename T>

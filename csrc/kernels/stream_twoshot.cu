@@ -70,6 +70,7 @@ __device__ __forceinline__ void stream_body(const CollArgs& a, uint32_t lane) {
     __shared__ int s_abort;
     __shared__ uint32_t s_seq;
     if (tid == 0) s_abort = 0;
+    trace_begin(cv, a.flags, lane);
     const uint32_t seq_base = load_call_word(cv, kCallStreamSeq, &s_seq);  // sequence numbers used before this call
     const uint64_t deadline = ptx::globaltimer() + cv.timeout_ns;
 
@@ -231,7 +232,7 @@ __device__ __forceinline__ void stream_body(const CollArgs& a, uint32_t lane) {
         if (!wait_peers(cv, cr_word, seq_base + n_it, deadline, kSiteStreamDrain, lane, &s_abort)) return;
     }
     // The next call continues after the largest sequence number any lane can have used.
-    finish_call(cv, 1, kCallStreamSeq, static_cast<uint32_t>((n_pieces + nlanes - 1) / nlanes), nlanes);
+    finish_call(cv, 1, kCallStreamSeq, static_cast<uint32_t>((n_pieces + nlanes - 1) / nlanes), nlanes, a.flags);
 }
 
 template <typename Tin, typename Tout, int WORLD>

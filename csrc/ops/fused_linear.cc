@@ -5,6 +5,8 @@
 
 #include <algorithm>
 #include <cstring>
+#include <mutex>
+#include <set>
 
 #include "../comm/cuda_driver.h"
 #include "../kernels/gemm_ar_rmsnorm.h"
@@ -167,16 +169,20 @@ Result FusedLinearAllReduceRmsNorm(Communicator& comm, const FusedLinearDesc* de
     FusedLinearCounts(T, N, W, oneshot, arrivals, rows_of);
     const void* fn = GemmArKernel(comm.emulated());
     const uint32_t smem = GemmArSmemBytes();
-    static bool attr_set[2] = {false, false};
-    if (!attr_set[comm.emulated() ? 1 : 0]) {
-        // Per device in a multi-GPU process; cheap enough to repeat for each local device once.
+    // The dynamic shared-memory limit is a per-device property of the kernel: raise it once for every
+    // (kernel flavour, device) this process launches on.
+    static std::mutex attr_mu;
+    static std::set<std::pair<int, int>> attr_done;
+    {
+        std::lock_guard<std::mutex> lock(attr_mu);
         for (int i = 0; i < nlocal; ++i) {
+            const std::pair<int, int> key(comm.emulated() ? 1 : 0, comm.device_of(i));
+            if (attr_done.count(key)) continue;
             if (nlocal > 1) cudaSetDevice(comm.device_of(i));
             cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
             if (e != cudaSuccess) return fail(Result::CudaError, std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(e));
-            if (comm.emulated()) break;
+            attr_done.insert(key);
         }
-        attr_set[comm.emulated() ? 1 : 0] = true;
     }
     // Resident CTAs per GPU (queried once per kernel flavour; all GPUs of a group are alike).
     static int cached_per_sm[2] = {0, 0}, cached_sms[2] = {0, 0};

@@ -67,17 +67,20 @@ void Gemm(const float* a, const float* b, size_t m, size_t n, size_t k, double* 
 
 void FlashSlice(uint64_t count, int vec, uint32_t ctas, uint32_t cta, bool vec_ok, uint64_t* vb, uint64_t* ve,
                 uint64_t* tb, uint64_t* te) {
-    const uint64_t nvec = vec_ok ? count / vec : 0;
-    const uint64_t per = (nvec + ctas - 1) / ctas;
-    *vb = std::min<uint64_t>(nvec, static_cast<uint64_t>(cta) * per);
-    *ve = std::min<uint64_t>(nvec, *vb + per);
+    // Element range of the CTA from values all ranks share; alignment only picks the access width.
+    const uint64_t nvec_all = (count + vec - 1) / vec;
+    const uint64_t per_v = (nvec_all + ctas - 1) / ctas;
+    const uint64_t eb = std::min<uint64_t>(count, static_cast<uint64_t>(cta) * per_v * vec);
+    const uint64_t ee = std::min<uint64_t>(count, eb + per_v * vec);
     if (vec_ok) {
-        *tb = nvec * vec;
-        *te = (cta == ctas - 1) ? count : *tb;
+        *ve = ee / vec;
+        *vb = std::min<uint64_t>(*ve, (eb + vec - 1) / vec);  // eb is a multiple of vec unless the slice is empty
+        *tb = std::max<uint64_t>(*ve * vec, eb);
+        *te = ee;
     } else {
-        const uint64_t per_e = (count + ctas - 1) / ctas;
-        *tb = std::min<uint64_t>(count, static_cast<uint64_t>(cta) * per_e);
-        *te = std::min<uint64_t>(count, *tb + per_e);
+        *vb = *ve = 0;
+        *tb = eb;
+        *te = ee;
     }
 }
 

@@ -18,6 +18,8 @@ const char* VariantName(Variant v) {
         case Variant::Stream: return "stream";
         case Variant::NvlsOneShot: return "nvls1";
         case Variant::NvlsTwoShot: return "nvls2";
+        case Variant::FlashPull: return "flash_pull";
+        case Variant::StreamDirect: return "stream_direct";
     }
     return "?";
 }
@@ -79,6 +81,33 @@ int AutoCtasPerLane(bool use_flash, int lanes, uint64_t max_lane_elems, uint64_t
     return static_cast<int>(std::min<uint64_t>(std::max<uint64_t>(CeilDiv(max_lane_elems, tile_elems), 1), 32));
 }
 
+uint64_t PullCrossoverBytes(int world) {
+    // One-shot pull receives (W-1)*S per rank, the two-shot form 2(W-1)/W*S in each direction plus
+    // one more link trip for its pushes: the pull only pays while the message is latency-bound.
+    const long long e = env::GetInt("YALI_PULL_MAX_BYTES", -1);
+    if (e >= 0) return static_cast<uint64_t>(e);
+    if (world <= 2) return 8ull << 20;
+    return 0;  // from three ranks on the staged one-shot / the in-switch forms cover the small sizes
+}
+
+void DirectPreset(uint64_t bytes, int world, bool one_shot, uint32_t sm_count, uint32_t* ctas, uint32_t* chunk_bytes,
+                  uint32_t* stages) {
+    // A stage holds one chunk of every rank's input.  About 96 KiB of stages per CTA lets two CTAs
+    // share an SM; chunks of 8 KiB (4 KiB from five ranks on) keep each bulk copy large.
+    const uint64_t budget = 96ull << 10;
+    const uint32_t chunk = world <= 4 ? (8u << 10) : (4u << 10);
+    uint32_t st = static_cast<uint32_t>(budget / (static_cast<uint64_t>(chunk) * std::max(world, 1)));
+    st = std::max<uint32_t>(2, std::min<uint32_t>(st, kMaxPipelineStages));
+    const uint64_t range = one_shot ? bytes : CeilDiv(bytes, static_cast<uint64_t>(std::max(world, 1)));
+    const uint64_t n_chunks = std::max<uint64_t>(CeilDiv(range, chunk), 1);
+    *ctas = static_cast<uint32_t>(std::min<uint64_t>(n_chunks, 2ull * std::max<uint32_t>(sm_count, 1)));
+    *chunk_bytes = chunk;
+    *stages = st;
+}
+
+uint32_t NvlsUnrollPreset(uint64_t /*bytes*/, int /*world*/) { return 4; }
+uint32_t NvlsBlockBytesPreset(uint64_t /*bytes*/, int /*world*/) { return 0; }
+
 uint64_t ShardElems(uint64_t count, int world) {
     return RoundUp(CeilDiv(count, static_cast<uint64_t>(std::max(world, 1))), 16);
 }
@@ -124,6 +153,8 @@ bool ParseVariant(const std::string& v, Variant* out) {
     else if (v == "stream") *out = Variant::Stream;
     else if (v == "nvls1") *out = Variant::NvlsOneShot;
     else if (v == "nvls2") *out = Variant::NvlsTwoShot;
+    else if (v == "flash_pull") *out = Variant::FlashPull;
+    else if (v == "stream_direct") *out = Variant::StreamDirect;
     else return false;
     return true;
 }
@@ -237,6 +268,12 @@ Result MakePlan(int world, uint64_t count, Dtype in, Dtype out, int epilogue, Ke
     const bool stream_ok = !rows && world > 1 && caps.ring_bytes > 0;
     const bool nvls_ok = !rows && world > 1 && caps.has_multicast && in == out && caps.vec_ok &&
                          (bytes % 16 == 0) && (caps.symmetric || bytes <= caps.nvls_cap);
+    // The pipelined kernels read every rank's input and (two-shot) write every rank's output in
+    // place: all of them must be addressable and 16-byte aligned.  The one-shot pull overwrites
+    // its output while peers may still read their inputs, so it cannot run in place.
+    const bool direct_ok = !rows && world > 1 && caps.peer_send && caps.peer_recv && caps.vec_ok &&
+                           !caps.half_collective;
+    const bool pull_ok = direct_ok && !caps.in_place;
 
     Variant v;
     const TuningRow* row = (table && forced == KernelMode::Auto) ? table->Find(world, static_cast<int>(in_b), bytes)
@@ -244,20 +281,31 @@ Result MakePlan(int world, uint64_t count, Dtype in, Dtype out, int epilogue, Ke
     if (forced == KernelMode::Flash) v = Variant::Flash;
     else if (forced == KernelMode::Stream) v = Variant::Stream;
     else if (forced == KernelMode::NVLS) v = bytes <= (128ull << 10) ? Variant::NvlsOneShot : Variant::NvlsTwoShot;
+    else if (forced == KernelMode::FlashPull) v = Variant::FlashPull;
+    else if (forced == KernelMode::StreamDirect) v = Variant::StreamDirect;
     else if (row) v = row->variant;
     // Measured on 8 x B200 with symmetric buffers: the flag-in-data one-shot wins up to 64 KiB
     // (8.3-13.5 us against 11-15 us), the in-switch forms from 128 KiB (16 us against 16-21 us).
     else if (nvls_ok && caps.symmetric && world > 4 && bytes > (64ull << 10))
         v = bytes <= (128ull << 10) ? Variant::NvlsOneShot : Variant::NvlsTwoShot;
-    else if (bytes <= FlashCrossoverBytes(in, world)) v = Variant::Flash;
+    else if (bytes <= LowLatencyMaxBytes(world) && bytes <= caps.ll_cap) v = Variant::Flash;
+    else if (pull_ok && bytes <= PullCrossoverBytes(world)) v = Variant::FlashPull;
+    else if (bytes <= FlashCrossoverBytes(in, world) && !(direct_ok && world == 2)) v = Variant::Flash;
     else if (nvls_ok && world > 2) v = Variant::NvlsTwoShot;
+    else if (direct_ok) v = Variant::StreamDirect;
     else v = Variant::Stream;
+
+    // In place on symmetric buffers the in-switch one-shot would overwrite operands of the peers'
+    // ld_reduce; the two-shot form reads and writes every element from one CTA of one rank only.
+    if (v == Variant::NvlsOneShot && caps.symmetric && caps.in_place) v = Variant::NvlsTwoShot;
 
     // Fall back when the chosen variant cannot run; a forced mode that cannot run is an error.
     auto runnable = [&](Variant x) {
         switch (x) {
             case Variant::Flash: return flash_ok;
             case Variant::Stream: return stream_ok;
+            case Variant::FlashPull: return pull_ok;
+            case Variant::StreamDirect: return direct_ok;
             default: return nvls_ok;
         }
     };
@@ -268,7 +316,8 @@ Result MakePlan(int world, uint64_t count, Dtype in, Dtype out, int epilogue, Ke
                        "' cannot run this call (size, alignment, epilogue or missing multicast)";
             return Result::Unsupported;
         }
-        if (stream_ok) v = Variant::Stream;
+        if (direct_ok && v != Variant::StreamDirect) v = Variant::StreamDirect;
+        else if (stream_ok) v = Variant::Stream;
         else if (flash_ok) v = Variant::Flash;
         else {
             if (why) *why = "message exceeds the one-shot staging capacity and no two-shot path is available";
@@ -322,6 +371,31 @@ Result MakePlan(int world, uint64_t count, Dtype in, Dtype out, int epilogue, Ke
             if (caps.peer_recv) p.flags |= kFlagDirectAg;
             break;
         }
+        case Variant::FlashPull:
+        case Variant::StreamDirect: {
+            const bool one_shot = v == Variant::FlashPull;
+            p.shard_elems = ShardElems(count, world);
+            uint32_t c, chunk, st;
+            DirectPreset(bytes, world, one_shot, caps.sm_count, &c, &chunk, &st);
+            if (row && row->ctas) c = row->ctas;
+            if (row && row->slot_bytes) chunk = row->slot_bytes;
+            if (dev_ctas > 0) c = dev_ctas;
+            if (dev_slot > 0) chunk = static_cast<uint32_t>(dev_slot);
+            const long long dev_stages = env::GetInt("YALI_DEV_STAGES", 0);
+            chunk = std::max<uint32_t>(1024, std::min<uint32_t>(chunk, 64u << 10)) / 1024 * 1024;
+            if (dev_stages > 0) st = static_cast<uint32_t>(dev_stages);
+            // At most 200 KiB of stages per CTA.
+            const uint32_t per_stage = chunk * static_cast<uint32_t>(world);
+            st = std::max<uint32_t>(2, std::min<uint32_t>(std::min<uint32_t>(st, kMaxPipelineStages), (200u << 10) / per_stage));
+            p.smem_bytes = st * per_stage;
+            const uint32_t per_sm = std::max<uint32_t>(1, std::min<uint32_t>(2, (220u << 10) / (p.smem_bytes + 1024)));
+            const uint32_t resident = per_sm * std::max<uint32_t>(caps.sm_count, 1);
+            p.ctas = std::max<uint32_t>(1, std::min<uint32_t>(std::min<uint32_t>(c, max_ctas), std::min<uint32_t>(resident, kBarSlots)));
+            p.slot_bytes = chunk;
+            p.stages = st;
+            if (one_shot) p.flags |= kFlagPullOneShot;
+            break;
+        }
         case Variant::NvlsOneShot:
         case Variant::NvlsTwoShot: {
             p.shard_elems = ShardElems(count, world);
@@ -335,6 +409,13 @@ Result MakePlan(int world, uint64_t count, Dtype in, Dtype out, int epilogue, Ke
             if (dev_ctas > 0) c = dev_ctas;
             p.ctas = std::max<uint32_t>(1, std::min<uint32_t>(std::min<uint32_t>(c, max_ctas), kBarSlots));
             if (caps.symmetric) p.flags |= kFlagSymmetric;
+            // Loads in flight per thread (4 or 8) and, for symmetric two-shot calls, the size of the
+            // blocks the CTAs interleave over the shard (0: one contiguous slice per CTA).
+            p.stages = NvlsUnrollPreset(bytes, world);
+            p.slot_bytes = caps.symmetric && v == Variant::NvlsTwoShot ? NvlsBlockBytesPreset(bytes, world) : 0;
+            if (env::GetInt("YALI_DEV_STAGES", 0) > 0) p.stages = env::GetInt("YALI_DEV_STAGES", 0) >= 8 ? 8 : 4;
+            if (dev_slot > 0 && caps.symmetric && v == Variant::NvlsTwoShot)
+                p.slot_bytes = static_cast<uint32_t>(dev_slot) / 16 * 16;
             break;
         }
     }

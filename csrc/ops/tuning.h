@@ -18,7 +18,7 @@
 
 namespace yali {
 
-enum class Variant : int { Flash = 0, Stream = 1, NvlsOneShot = 2, NvlsTwoShot = 3 };
+enum class Variant : int { Flash = 0, Stream = 1, NvlsOneShot = 2, NvlsTwoShot = 3, FlashPull = 4, StreamDirect = 5 };
 const char* VariantName(Variant v);
 
 // What the communicator can offer for this call.
@@ -30,6 +30,10 @@ struct PlanCaps {
     bool has_multicast = false;
     bool symmetric = false;        // send and recv of every rank live in the heap at equal offsets
     bool peer_recv = false;        // every rank's recv is peer-addressable (direct all-gather possible)
+    bool peer_send = false;        // every rank's send is peer-addressable (the pipelined kernels can pull it)
+    bool in_place = false;         // some rank's send and recv ranges overlap
+    bool half_collective = false;  // reduce-scatter-only / all-gather-only call (ring kernel only)
+    uint32_t sm_count = 148;       // SMs of the GPU (resident CTAs of the pipelined kernels)
     bool vec_ok = true;            // all pointers 16-byte aligned
     uint32_t max_ctas = 296;       // upper bound on CTAs per rank (co-residency for emulated ranks)
     uint32_t force_ctas = 0;       // >0: caller's CTA / lane count (still clamped to the limits)
@@ -42,6 +46,8 @@ struct Plan {
     uint32_t slot_bytes = 0;    // Stream
     uint64_t shard_elems = 0;   // Stream, NVLS two-shot
     uint32_t max_iters = 0;     // Stream: sequence numbers consumed by this call
+    uint32_t stages = 0;        // FlashPull / StreamDirect: shared-memory stages per CTA
+    uint32_t smem_bytes = 0;    // dynamic shared memory per CTA
     uint32_t flags = 0;         // CollFlags
 };
 
@@ -59,6 +65,17 @@ uint64_t AutoSlotBytes(uint64_t bytes, int world = 2);
 uint64_t ClampSlotBytes(uint64_t slot_bytes, uint64_t max_bytes);
 // Flash: how many CTAs serve one lane's elements (>=1); Stream: always 1.
 int AutoCtasPerLane(bool use_flash, int lanes, uint64_t max_lane_elems, uint64_t tile_elems);
+
+// Largest message (bytes) for which the one-shot pull beats the two-shot direct form.
+uint64_t PullCrossoverBytes(int world);
+// CTAs, bytes per source and stage, and stages of the pipelined kernels.
+void DirectPreset(uint64_t bytes, int world, bool one_shot, uint32_t sm_count, uint32_t* ctas, uint32_t* chunk_bytes,
+                  uint32_t* stages);
+
+// NVLS kernels: multimem loads in flight per thread (4 or 8) and the block size the CTAs of a rank
+// interleave over its shard (0: one contiguous slice per CTA).
+uint32_t NvlsUnrollPreset(uint64_t bytes, int world);
+uint32_t NvlsBlockBytesPreset(uint64_t bytes, int world);
 
 // Elements per shard for a two-shot algorithm: ceil(count/world) rounded up to 16 elements.
 uint64_t ShardElems(uint64_t count, int world);

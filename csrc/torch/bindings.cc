@@ -132,9 +132,22 @@ class PyComm {
         d["variant"] = VariantName(l.variant);
         d["ctas"] = l.ctas;
         d["slot_bytes"] = l.slot_bytes;
+        d["stages"] = l.stages;
         d["flags"] = l.flags;
         d["launches"] = l.launches;
         return d;
+    }
+
+    void SetTrace(bool on) { c().SetTrace(on); }
+    // Device-side timeline of local rank `local_index`: (traced calls so far, [(start_ns, end_ns), ...])
+    // for the most recent calls, oldest first.  Synchronise before reading.
+    py::tuple ReadTrace(int local_index, int max_entries) {
+        std::vector<uint64_t> buf(static_cast<size_t>(std::max(max_entries, 1)) * 2);
+        uint64_t calls = 0;
+        const int n = c().ReadTrace(local_index, buf.data(), max_entries, &calls);
+        py::list out;
+        for (int k = 0; k < n; ++k) out.append(py::make_tuple(buf[2 * k], buf[2 * k + 1]));
+        return py::make_tuple(calls, out);
     }
 
     void CheckTensors(const std::vector<at::Tensor>& ts, const char* what, at::ScalarType* dt, int64_t* numel) {
@@ -521,6 +534,8 @@ PYBIND11_MODULE(_C, m) {
         .def_property_readonly("launches", &PyComm::launches)
         .def("layout", &PyComm::layout)
         .def("last_call", &PyComm::last_call)
+        .def("set_trace", &PyComm::SetTrace, py::arg("on"))
+        .def("read_trace", &PyComm::ReadTrace, py::arg("local_index") = 0, py::arg("max_entries") = 4096)
         .def("all_reduce", &PyComm::AllReduce, py::arg("send"), py::arg("recv"), py::arg("mode") = "auto",
              py::arg("scale") = py::none(), py::arg("ctas") = 0, py::arg("slot_bytes") = 0, py::arg("skip_rank") = -1)
         .def("all_reduce_rmsnorm", &PyComm::AllReduceRmsNorm, py::arg("send"), py::arg("recv"),

@@ -86,6 +86,41 @@ def test_heap_layout(native_lib):
             assert ll_off == gemm_off + 2 * world * gemm_cap
             assert user_off == ll_off + 2 * (world - 1) * 2 * ll_cap
     assert native_lib.yali_c_heap_layout(8, 1 * MiB, f) != 0  # too small for the fixed regions
+    # Every region starts on a 4 KiB boundary for every world size (vector accesses, bulk copies).
+    for world in range(1, 9):
+        assert native_lib.yali_c_heap_layout(world, 0, f) == 0
+        total, flags_off, flash_off, flash_cap, ring_off, ring_bytes, nvls_off, nvls_cap, gemm_off, gemm_cap, \
+            user_off, user_bytes, ll_off, ll_cap = list(f)
+        for off in (flash_off, ring_off, nvls_off, gemm_off, ll_off, user_off, flash_cap, gemm_cap, ll_cap):
+            assert off % 4096 == 0, (world, off)
+
+
+def test_plan_pipelined_variants_need_addressable_buffers(native_lib):
+    lib = native_lib
+    addressable = dict(peer_recv=1, peer_send=1)
+    rc, p, _ = make_plan(lib, 2, 1 << 20, cp=caps(2, **addressable))  # 4 MiB at two ranks
+    assert rc == 0 and p.variant == 4 and p.flags & 256 and p.stages >= 2 and p.smem_bytes == p.stages * 2 * p.slot_bytes
+    assert p.smem_bytes <= 100 * 1024  # two CTAs share an SM
+    rc, p, _ = make_plan(lib, 2, 1 << 20, cp=caps(2, in_place=1, **addressable))
+    assert rc == 0 and p.variant == 5  # the one-shot pull cannot run in place
+    rc, p, _ = make_plan(lib, 2, 32 * MiB, cp=caps(2, **addressable))  # 128 MiB: two-shot, all SMs twice
+    assert rc == 0 and p.variant == 5 and p.ctas == 296 and p.shard_elems == 16 * MiB
+    rc, p, _ = make_plan(lib, 2, 32 * MiB)  # plain buffers: the ring kernel
+    assert rc == 0 and p.variant == 1
+    rc, p, _ = make_plan(lib, 2, 1024, cp=caps(2, **addressable))
+    assert rc == 0 and p.variant == 0 and p.flags & 64  # tiny messages keep the flag-in-data one-shot
+    for world in (3, 5, 8):
+        rc, p, _ = make_plan(lib, world, 32 * MiB, cp=caps(world, **addressable))
+        assert rc == 0 and p.variant == 5 and p.stages * world * p.slot_bytes == p.smem_bytes <= 100 * 1024
+    rc, p, msg = make_plan(lib, 2, 4096, mode=4)  # forced pull without addressable inputs
+    assert rc != 0 and "cannot run" in msg
+    rc, p, _ = make_plan(lib, 2, 4096, mode=5, cp=caps(2, vec_ok=0, **addressable))
+    assert rc != 0  # 16-byte vectors into the peers' outputs need aligned buffers everywhere
+    # In place on symmetric buffers the in-switch one-shot becomes the two-shot form.
+    rc, p, _ = make_plan(lib, 8, 32768, cp=caps(8, has_multicast=1, symmetric=1, in_place=1))
+    assert rc == 0 and p.variant == 3
+    rc, p, _ = make_plan(lib, 8, 8192, mode=3, cp=caps(8, has_multicast=1, symmetric=1, in_place=1))
+    assert rc == 0 and p.variant == 3
 
 
 def test_plan_auto_selection(native_lib):
@@ -147,6 +182,7 @@ def test_tuning_table_override(native_lib):
 @pytest.mark.parametrize("ctas", [1, 3, 8, 37, 256])
 @pytest.mark.parametrize("vec", [4, 8])
 def test_flash_slices_partition_the_message(native_lib, count, ctas, vec):
+    ranges = {}
     for vec_ok in (1, 0):
         covered = np.zeros(count, dtype=np.int32)
         o = (ctypes.c_uint64 * 4)()
@@ -156,7 +192,12 @@ def test_flash_slices_partition_the_message(native_lib, count, ctas, vec):
             assert vb <= ve and tb <= te
             covered[vb * vec:ve * vec] += 1
             covered[tb:te] += 1
+            # CTA c of an aligned rank and CTA c of a misaligned rank cover the same elements
+            # (they synchronise only with each other).
+            lo = min(vb * vec, tb) if ve > vb else tb
+            ranges.setdefault(cta, set()).add((lo, te))
         assert (covered == 1).all()
+    assert all(len(v) == 1 for v in ranges.values())
 
 
 @pytest.mark.parametrize("world", [2, 3, 4, 8])

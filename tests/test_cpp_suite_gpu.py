@@ -50,6 +50,14 @@ def test_benchmark_self_check_emulated():
         assert "Correctness: PASSED" in out and "GB/s" in out and '"p99_us"' in out
 
 
+@pytest.mark.parametrize("nranks", [2, 3])
+def test_multi_process_c_abi(nranks):
+    """yaliMPComm* / yaliIpc* end to end, one process per rank.  The ranks meet at host barriers only,
+    so they may share a GPU (rank r uses GPU r modulo the number of GPUs)."""
+    out = _run([sys.executable, "-m", "yali_b200.launch", "-np", str(nranks), _need("test_mp_cabi")])
+    assert f"C ABI test on {nranks} ranks: PASSED" in out
+
+
 @pytest.mark.multigpu(2)
 def test_examples_and_mpi_binaries():
     assert "3.0, 3.0" in _run([_need("example_simple")])
@@ -57,6 +65,7 @@ def test_examples_and_mpi_binaries():
     launch = [sys.executable, "-m", "yali_b200.launch", "-np", "2"]
     assert "expected 3.0" in _run(launch + [_need("example_simple_mpi")])
     assert "PASSED" in _run(launch + [_need("example_multilane_mpi")], env={"YALI_ELEMS": str(1 << 20)})
+    assert "PASSED" in _run(launch + [_need("example_manual_ipc")], env={"YALI_ELEMS": str(1 << 20)})
     assert "PASSED" in _run(launch + [_need("test_ops_allreduce_mpi")])
     out = _run(launch + [_need("benchmark_yali_mpi"), "524288", "50", "1", "auto", "0", "cuda-events", "bf16"],
                env={"YALI_WARMUP": "5"})

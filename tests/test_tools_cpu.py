@@ -66,11 +66,15 @@ def test_nvlink_parsing_and_capability_table():
 
 def test_launcher_sets_rank_environment(tmp_path):
     script = tmp_path / "p.py"
-    script.write_text("import os,sys\nprint(os.environ['RANK'], os.environ['WORLD_SIZE'], os.environ['LOCAL_RANK'])\n"
+    # One write() per child: the three children share a pipe, and a line written in one system call
+    # (shorter than PIPE_BUF) cannot interleave with the others.
+    script.write_text("import os,sys\n"
+                      "os.write(1, ('%s %s %s\\n' % (os.environ['RANK'], os.environ['WORLD_SIZE'], "
+                      "os.environ['LOCAL_RANK'])).encode())\n"
                       "sys.exit(3 if os.environ['RANK']=='1' and os.environ.get('FAIL') else 0)\n")
     r = subprocess.run([sys.executable, "-m", "yali_b200.launch", "-np", "3", sys.executable, str(script)],
                        capture_output=True, text=True, cwd=str(ROOT))
-    assert r.returncode == 0 and sorted(r.stdout.split("\n")[:3]) == ["0 3 0", "1 3 1", "2 3 2"]
+    assert r.returncode == 0 and sorted(ln for ln in r.stdout.split("\n") if ln) == ["0 3 0", "1 3 1", "2 3 2"]
     r = subprocess.run([sys.executable, "-m", "yali_b200.launch", "-np", "2", sys.executable, str(script)],
                        capture_output=True, text=True, cwd=str(ROOT), env={**__import__("os").environ, "FAIL": "1"})
     assert r.returncode == 3

@@ -47,6 +47,7 @@ LIB_SOURCES = [
     "kernels/flash_oneshot.cu",
     "kernels/stream_twoshot.cu",
     "kernels/nvls.cu",
+    "kernels/direct_pipeline.cu",
     "kernels/util_kernels.cu",
     "kernels/gemm_ar_rmsnorm.cu",
     "kernels/no_alloc_entry.cu",

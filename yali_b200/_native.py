@@ -17,12 +17,14 @@ _ext = None
 class PlanCaps(ctypes.Structure):
     _fields_ = [("flash_cap", ctypes.c_uint64), ("ring_bytes", ctypes.c_uint64), ("nvls_cap", ctypes.c_uint64),
                 ("has_multicast", ctypes.c_int), ("symmetric", ctypes.c_int), ("peer_recv", ctypes.c_int),
-                ("vec_ok", ctypes.c_int), ("max_ctas", ctypes.c_uint32), ("ll_cap", ctypes.c_uint64)]
+                ("vec_ok", ctypes.c_int), ("max_ctas", ctypes.c_uint32), ("ll_cap", ctypes.c_uint64),
+                ("peer_send", ctypes.c_int), ("in_place", ctypes.c_int)]
 
 
 class Plan(ctypes.Structure):
     _fields_ = [("variant", ctypes.c_int), ("ctas", ctypes.c_uint32), ("slot_bytes", ctypes.c_uint32),
-                ("max_iters", ctypes.c_uint32), ("flags", ctypes.c_uint32), ("shard_elems", ctypes.c_uint64)]
+                ("max_iters", ctypes.c_uint32), ("flags", ctypes.c_uint32), ("shard_elems", ctypes.c_uint64),
+                ("stages", ctypes.c_uint32), ("smem_bytes", ctypes.c_uint32)]
 
 
 class SimConfig(ctypes.Structure):
