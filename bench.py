@@ -10,10 +10,13 @@ peer, so two ranks are emulated on the one GPU by a single cooperative launch of
 the same kernels (HBM-bound, no NVLink) and the line says so.  Timing: CUDA events
 per step on the launching stream after W warm-up steps, barrier + synchronize on
 both sides, max over ranks.  The line also carries p50/p99 latency of a 1 MiB
-all-reduce (rotating over buffers that together exceed L2), the end-to-end number
-(pinned host -> device copy of the step's input, all-reduce through the public
-API, device -> host copy of the result) and the clocks sampled during the timed
-region.
+all-reduce (1000 calls replayed from one CUDA graph, rotating over buffers that
+together exceed L2; every kernel stamps %globaltimer when its first CTA starts and
+when its last CTA leaves, so the samples contain no host jitter; call by call the
+max over ranks), the end-to-end number (pinned host -> device copy of the step's
+input, all-reduce through the public API, device -> host copy of the result) next
+to the same copies without the collective, an NCCL arm measured with the same
+timing code on the same GPUs, and the clocks sampled during the timed region.
 
 `--impl reference` runs the unmodified reference (its own benchmark_yali binary and
 an end-to-end harness around its yali::allreduce, built by
@@ -149,6 +152,41 @@ def percentile(xs, q):
     return s[k]
 
 
+def run_nccl_arm(comm, n_gpus: int) -> dict:
+    """NCCL on the same GPUs with the same timing code as the library's own C++ benchmark
+    (bench/benchmark_nccl_mpi.cu: one process per GPU, CUDA events / one CUDA graph, max over ranks).
+    Every rank of this job starts one rank of that binary; this job's GPUs are idle meanwhile."""
+    if n_gpus < 2:
+        return {"unavailable": "NCCL needs at least two GPUs"}
+    exe = ROOT / "build" / "bin" / "benchmark_nccl_mpi"
+    if not exe.exists():
+        if int(os.environ.get("LOCAL_RANK", "0")) == 0:
+            subprocess.run(["make", "-C", str(ROOT), "build/bin/benchmark_nccl_mpi"], capture_output=True, text=True)
+        comm.barrier()
+    if not exe.exists():
+        return {"unavailable": "build/bin/benchmark_nccl_mpi is not built (make bench)"}
+    env = dict(os.environ)
+    env["MASTER_PORT"] = str(int(os.environ.get("MASTER_PORT", "29500")) + 23)
+    env["YALI_WARMUP"] = "20"
+    out = {}
+    for key, argv in (("busbw_128MiB_fp32", [str(MESSAGE_BYTES // 4), "20", "0", "auto", "0", "cuda-events", "fp32"]),
+                      ("latency_1MiB", [str((1 << 20) // 4), "1000", "0", "auto", "0", "graph", "fp32"])):
+        comm.barrier()
+        try:
+            r = subprocess.run([str(exe)] + argv, capture_output=True, text=True, timeout=300, env=env)
+        except subprocess.TimeoutExpired:
+            out[key] = {"unavailable": "timed out"}
+            continue
+        line = next((ln for ln in r.stdout.splitlines() if ln.startswith("{")), None)
+        if r.returncode != 0 or (comm.rank == 0 and line is None):
+            out[key] = {"unavailable": (r.stderr.strip() or r.stdout.strip())[-160:].replace("\n", " ")}
+        elif line is not None:
+            d = json.loads(line)
+            out[key] = {"avg_us": d.get("avg_us"), "busbw_gbps": d.get("busbw_gbps"), "timing": d.get("timing")}
+    out["how"] = "bench/benchmark_nccl_mpi.cu (ncclAllReduce, out of place, system libnccl), one process per GPU"
+    return out
+
+
 def run_own(args) -> dict:
     import torch
 
@@ -204,20 +242,24 @@ def run_own(args) -> dict:
     def small_step(i):
         comm.all_reduce(unwrap(views_s[i % nbuf]), unwrap(views_r[i % nbuf]))
 
-    lat_steps = max(args.steps, 200)
-    _, lat = time_steps(comm, torch, small_step, lat_steps, max(args.warmup, 20))
-    p50, p99 = percentile(lat, 50), percentile(lat, 99)
-    p50 = gather_max(comm, p50)
-    p99 = gather_max(comm, p99)
-    # The same calls without an event between them (the events keep consecutive launches from
-    # overlapping), and as one CUDA-graph replay (no host launch work at all).
-    batch_ms, _ = time_steps_batched(comm, torch, small_step, lat_steps)
+    # Event pair per call (contains host launch jitter): kept for comparison only.
+    ev_steps = 200
+    _, lat = time_steps(comm, torch, small_step, ev_steps, max(args.warmup, 20))
+    ev_p50, ev_p99 = gather_max(comm, percentile(lat, 50)), gather_max(comm, percentile(lat, 99))
+    # The same calls without an event between them.
+    batch_ms, _ = time_steps_batched(comm, torch, small_step, ev_steps)
+    # 1000 calls in ONE CUDA graph (no host work between the kernels) with the device-side timeline on:
+    # per call, duration = first CTA in -> last CTA out and cadence = end of the previous call -> end of
+    # this call (what an event pair per call would see on a host without jitter).
+    lat_steps = 1000
+    comm.set_trace(True)
     graph = torch.cuda.CUDAGraph()
     side = torch.cuda.Stream()
     with torch.cuda.stream(side):
         with torch.cuda.graph(graph, stream=side):
             for i in range(lat_steps):
                 small_step(i)
+    comm.set_trace(False)
     graph.replay()
     torch.cuda.synchronize()
     comm.barrier()
@@ -229,7 +271,26 @@ def run_own(args) -> dict:
     comm.barrier()
     comm.check()
     graph_us = gather_max(comm, g0.elapsed_time(g1) * 1e3 / lat_steps)
+    import struct
+    dur = [0.0] * lat_steps
+    cad = [0.0] * (lat_steps - 1)
+    for li in range(len(aslist(send))):
+        _calls, entries = comm.read_trace(li, lat_steps)
+        assert len(entries) == lat_steps, (len(entries), lat_steps)
+        for c, (t0, t1) in enumerate(entries):
+            dur[c] = max(dur[c], (t1 - t0) * 1e-3)
+            if c:
+                cad[c - 1] = max(cad[c - 1], (t1 - entries[c - 1][1]) * 1e-3)
+    if comm.nlocal == 1 and comm.world > 1:  # call by call the max over ranks
+        parts = comm.allgather_object_bytes(struct.pack(f"{lat_steps}d", *dur) + struct.pack(f"{lat_steps - 1}d", *cad))
+        for p in parts:
+            vals = struct.unpack(f"{2 * lat_steps - 1}d", p)
+            dur = [max(x, y) for x, y in zip(dur, vals[:lat_steps])]
+            cad = [max(x, y) for x, y in zip(cad, vals[lat_steps:])]
+    p50, p99 = percentile(cad, 50), percentile(cad, 99)
+    d50, d99 = percentile(dur, 50), percentile(dur, 99)
     del graph
+    small_variant = comm.last_call()
 
     # ---- end to end through the public API: pinned H2D, all-reduce, D2H of the result ----
     n_local = len(aslist(send))
@@ -244,9 +305,19 @@ def run_own(args) -> dict:
     def e2e_step(_i):
         comm.all_reduce_host(h_in if n_local > 1 else h_in[0], h_out if n_local > 1 else h_out[0])
 
+    def copies_step(_i):
+        comm.all_reduce_host(h_in if n_local > 1 else h_in[0], h_out if n_local > 1 else h_out[0], copies_only=True)
+
     e2e_steps = max(3, min(args.steps, 20))
     e2e_ms, _ = time_steps(comm, torch, e2e_step, e2e_steps, 3)
     e2e_busbw = MESSAGE_BYTES * bus_factor(ranks) / (e2e_ms / e2e_steps * 1e-3) / 1e9
+    e2e_launches = time_steps.launches
+    # The same host <-> device copies on the same streams without the collective: what the host link
+    # allows for this step on this machine (all ranks copy at once).  Measured after the real step.
+    copies_ms, _ = time_steps(comm, torch, copies_step, e2e_steps, 2)
+    e2e_step(0)  # leave the reduced result in h_out for the check below
+    torch.cuda.synchronize()
+    comm.barrier()
     ok = ok and bool(torch.allclose(h_out[0], aslist(recv)[0].cpu(), rtol=1e-5, atol=1e-5))
     # Keep the GPU under the headline load until the sampler has a few readings.
     # (Same count on every rank: it is derived from the max-over-ranks step time.)
@@ -255,6 +326,7 @@ def run_own(args) -> dict:
     torch.cuda.synchronize()
     comm.barrier()
     clocks = sampler.stop() if rank == 0 else {}
+    nccl = run_nccl_arm(comm, n_gpus)
     comm.close()
 
     return {
@@ -284,15 +356,29 @@ def run_own(args) -> dict:
             "kernel": variant,
             "baseline": "reference README: 79.2 GB/s at 128 MB fp32 on 2x A100 NV4",
         },
-        "latency_1MiB_us": {"p50": round(p50 * 1e3, 2), "p99": round(p99 * 1e3, 2),
-                            "p99_over_p50": round(p99 / p50, 3) if p50 else None, "samples": lat_steps,
-                            "avg_back_to_back": round(batch_ms * 1e3 / lat_steps, 2),
+        "latency_1MiB_us": {"p50": round(p50, 2), "p99": round(p99, 2),
+                            "p99_over_p50": round(p99 / p50, 3) if p50 else None, "samples": lat_steps - 1,
+                            "kernel_p50": round(d50, 2), "kernel_p99": round(d99, 2),
+                            "kernel_p99_over_p50": round(d99 / d50, 3) if d50 else None,
+                            "avg_back_to_back": round(batch_ms * 1e3 / ev_steps, 2),
                             "avg_cuda_graph": round(graph_us, 2),
-                            "note": "p50/p99: one event pair per call; the averages: one pair around all calls"},
+                            "host_event_p50": round(ev_p50 * 1e3, 2), "host_event_p99": round(ev_p99 * 1e3, 2),
+                            "kernel": small_variant,
+                            "note": "p50/p99: 1000 calls replayed from one CUDA graph; every kernel stamps "
+                                    "%globaltimer at first-CTA entry and last-CTA exit; sample = end of previous call "
+                                    "to end of this call, call by call the max over ranks (kernel_*: entry to exit); "
+                                    "host_event_*: one CUDA event pair per call from Python (contains host jitter); "
+                                    "the averages: one event pair around all calls"},
         "e2e": {"value": round(e2e_busbw, 2), "unit": "GB/s", "h2d_bytes_per_step": MESSAGE_BYTES * n_local,
                 "d2h_bytes_per_step": MESSAGE_BYTES * n_local, "steps": e2e_steps,
+                "ms_per_step": round(e2e_ms / e2e_steps, 3),
+                "copies_only_ms_per_step": round(copies_ms / e2e_steps, 3),
+                "fraction_of_copies_only": round(copies_ms / e2e_ms, 3) if e2e_ms else None,
+                "gpu_launches": int(e2e_launches * (1 if emulated else ranks)),
                 "api": "Comm.all_reduce_host(pinned_in, pinned_out): H2D, all-reduce and D2H of 8 MiB chunks "
-                       "overlap on three streams"},
+                       "overlap on three streams; copies_only = the same copies without the collective, all "
+                       "ranks at once (the ceiling of the host link)"},
+        "nccl": nccl,
         "gpu_launches": int(launches),
         "clocks": clocks,
     }

@@ -31,7 +31,7 @@ HostPipeline::~HostPipeline() {
     }
 }
 
-Result HostPipeline::Prepare(uint64_t chunk_elems, Dtype dt) {
+Result HostPipeline::Prepare(uint64_t chunk_bytes) {
     const int nl = comm_.nlocal();
     if (loc_.empty()) {
         loc_.resize(nl);
@@ -49,22 +49,26 @@ Result HostPipeline::Prepare(uint64_t chunk_elems, Dtype dt) {
             }
         }
     }
-    if (chunk_elems_ != chunk_elems || dt_ != dt) {
-        const uint64_t bytes = chunk_elems * DtypeSize(dt);
+    // Symmetric memory is never freed piecemeal, so the staging buffers are sized by bytes (any
+    // dtype fits), grow in powers of two and are reused by every later call that fits: a program
+    // that alternates chunk sizes or dtypes holds at most twice its largest request.
+    if (chunk_bytes > slot_bytes_) {
+        uint64_t cap = 1ull << 20;
+        while (cap < chunk_bytes) cap <<= 1;
         for (int k = 0; k < kSlots; ++k) {
-            Result r = comm_.SymmAlloc(bytes, &send_[k]);
+            Result r = comm_.SymmAlloc(cap, &send_[k]);
             if (r != Result::Success) return r;
-            r = comm_.SymmAlloc(bytes, &recv_[k]);
+            r = comm_.SymmAlloc(cap, &recv_[k]);
             if (r != Result::Success) return r;
         }
-        chunk_elems_ = chunk_elems;
-        dt_ = dt;
+        slot_bytes_ = cap;
     }
     return Result::Success;
 }
 
 Result HostPipeline::AllReduce(const void* const* src, void* const* dst, uint64_t count, Dtype dt,
-                               const OpOptions& opt, uint64_t chunk_bytes, const cudaStream_t* user_streams) {
+                               const OpOptions& opt, uint64_t chunk_bytes, const cudaStream_t* user_streams,
+                               bool copies_only) {
     YALI_NVTX_RANGE("yali::AllReduceHost");
     if (count == 0) return Result::Success;
     const int nl = comm_.nlocal();
@@ -82,7 +86,7 @@ Result HostPipeline::AllReduce(const void* const* src, void* const* dst, uint64_
     // vector paths.
     uint64_t chunk = std::max<uint64_t>(256, (std::max<uint64_t>(chunk_bytes, esz) / esz) / 256 * 256);
     chunk = std::min<uint64_t>(chunk, (count + 255) / 256 * 256);
-    Result pr = Prepare(chunk, dt);
+    Result pr = Prepare(chunk * esz);
     if (pr != Result::Success) return pr;
 
     int prev_dev = 0;
@@ -121,10 +125,17 @@ Result HostPipeline::AllReduce(const void* const* src, void* const* dst, uint64_
             s_in[i] = send_[k][i];
             s_out[i] = recv_[k][i];
         }
-        Result r = comm_.AllReduce(s_in.data(), s_out.data(), m, dt, dt, opt, comp.data());
-        if (r != Result::Success) {
-            cudaSetDevice(prev_dev);
-            return r;
+        if (copies_only) {
+            for (int i = 0; i < nl; ++i) {
+                YALI_HP_CUDA(cudaSetDevice(comm_.device_of(i)));
+                YALI_HP_CUDA(cudaMemcpyAsync(s_out[i], s_in[i], m * esz, cudaMemcpyDeviceToDevice, loc_[i].comp));
+            }
+        } else {
+            Result r = comm_.AllReduce(s_in.data(), s_out.data(), m, dt, dt, opt, comp.data());
+            if (r != Result::Success) {
+                cudaSetDevice(prev_dev);
+                return r;
+            }
         }
         for (int i = 0; i < nl; ++i) {
             YALI_HP_CUDA(cudaSetDevice(comm_.device_of(i)));

@@ -31,17 +31,22 @@ uint64_t RoundUp(uint64_t a, uint64_t b) { return CeilDiv(a, b) * b; }
 
 // One-shot sends (N-1)*S per rank, two-shot 2(N-1)/N*S: at N=2 they tie and the
 // one-shot wins on latency up to its staging capacity; at larger N the one-shot
-// only pays off while the message is latency-bound. Measured on 2 x B200: the
-// one-shot leads by about 5 % at 32 MiB and trails the two-shot by 8-10 % at 64 MiB.
+// only pays off while the message is latency-bound. Measured on 2 x B200 (CUDA graph): the staged
+// one-shot leads at 16 MiB (36.5 us against 37.3 us for the pipelined two-shot) and trails it at
+// 64 MiB.
 uint64_t FlashCrossoverBytes(Dtype /*dt*/, int world) {
-    if (world <= 2) return 48ull << 20;
+    if (world <= 2) return 32ull << 20;
     if (world <= 4) return 1ull << 20;
     return 256ull << 10;
 }
 
-uint64_t LowLatencyMaxBytes(int /*world*/) {
+uint64_t LowLatencyMaxBytes(int world) {
     const long long e = env::GetInt("YALI_LL_MAX_BYTES", -1);
-    return e >= 0 ? static_cast<uint64_t>(e) : (256ull << 10);
+    if (e >= 0) return static_cast<uint64_t>(e);
+    // Measured on 2 x B200 in a CUDA graph: at 1 MiB the flag-in-data form on 128 CTAs takes 10.9 us,
+    // the flagged one-shot 11.9 us; at 4 MiB the flagged form leads (16.0 us).  From four ranks on
+    // the doubled traffic only pays up to 256 KiB.
+    return world <= 2 ? (1ull << 20) : (256ull << 10);
 }
 
 int FlashLanePreset(uint64_t bytes, Dtype /*dt*/, int /*world*/) {
@@ -81,26 +86,34 @@ int AutoCtasPerLane(bool use_flash, int lanes, uint64_t max_lane_elems, uint64_t
     return static_cast<int>(std::min<uint64_t>(std::max<uint64_t>(CeilDiv(max_lane_elems, tile_elems), 1), 32));
 }
 
-uint64_t PullCrossoverBytes(int world) {
-    // One-shot pull receives (W-1)*S per rank, the two-shot form 2(W-1)/W*S in each direction plus
-    // one more link trip for its pushes: the pull only pays while the message is latency-bound.
+uint64_t PullCrossoverBytes(int /*world*/) {
+    // The one-shot pull needs two link trips around its loads (peers ready, peers done) where the
+    // staged push needs one, and loads in both directions at once reach 660-670 GB/s per direction on
+    // 2 x B200 where stores reach 705: measured 16.4 us against 10.9-11.9 us at 1 MiB and 27.8 us
+    // against 16.0 us at 4 MiB.  It is therefore never picked by size; YALI_PULL_MAX_BYTES or the forced
+    // mode select it (it needs no staging, so it also serves messages beyond the one-shot staging).
     const long long e = env::GetInt("YALI_PULL_MAX_BYTES", -1);
-    if (e >= 0) return static_cast<uint64_t>(e);
-    if (world <= 2) return 8ull << 20;
-    return 0;  // from three ranks on the staged one-shot / the in-switch forms cover the small sizes
+    return e >= 0 ? static_cast<uint64_t>(e) : 0;
 }
 
 void DirectPreset(uint64_t bytes, int world, bool one_shot, uint32_t sm_count, uint32_t* ctas, uint32_t* chunk_bytes,
                   uint32_t* stages) {
-    // A stage holds one chunk of every rank's input.  About 96 KiB of stages per CTA lets two CTAs
-    // share an SM; chunks of 8 KiB (4 KiB from five ranks on) keep each bulk copy large.
+    // A stage holds one chunk of every rank's input.  Measured on 2 and 4 x B200: one CTA per SM is
+    // best from 16 MiB on (651 GB/s at 128 MiB on 2 GPUs against 630 with two per SM); at 2 ranks large
+    // messages like 32 KiB chunks in 3 stages, otherwise about 96 KiB of stages per CTA in chunks of
+    // 8 KiB (4 KiB from three ranks on) so that two CTAs can share an SM for small messages.
     const uint64_t budget = 96ull << 10;
-    const uint32_t chunk = world <= 4 ? (8u << 10) : (4u << 10);
+    uint32_t chunk = world <= 2 ? (8u << 10) : (4u << 10);
     uint32_t st = static_cast<uint32_t>(budget / (static_cast<uint64_t>(chunk) * std::max(world, 1)));
+    if (world <= 2 && bytes >= (128ull << 20) && !one_shot) {
+        chunk = 32u << 10;
+        st = 3;
+    }
     st = std::max<uint32_t>(2, std::min<uint32_t>(st, kMaxPipelineStages));
     const uint64_t range = one_shot ? bytes : CeilDiv(bytes, static_cast<uint64_t>(std::max(world, 1)));
     const uint64_t n_chunks = std::max<uint64_t>(CeilDiv(range, chunk), 1);
-    *ctas = static_cast<uint32_t>(std::min<uint64_t>(n_chunks, 2ull * std::max<uint32_t>(sm_count, 1)));
+    const uint64_t cap = bytes >= (16ull << 20) ? std::max<uint32_t>(sm_count, 1) : 2ull * std::max<uint32_t>(sm_count, 1);
+    *ctas = static_cast<uint32_t>(std::min<uint64_t>(n_chunks, cap));
     *chunk_bytes = chunk;
     *stages = st;
 }
@@ -290,7 +303,7 @@ Result MakePlan(int world, uint64_t count, Dtype in, Dtype out, int epilogue, Ke
         v = bytes <= (128ull << 10) ? Variant::NvlsOneShot : Variant::NvlsTwoShot;
     else if (bytes <= LowLatencyMaxBytes(world) && bytes <= caps.ll_cap) v = Variant::Flash;
     else if (pull_ok && bytes <= PullCrossoverBytes(world)) v = Variant::FlashPull;
-    else if (bytes <= FlashCrossoverBytes(in, world) && !(direct_ok && world == 2)) v = Variant::Flash;
+    else if (bytes <= FlashCrossoverBytes(in, world)) v = Variant::Flash;
     else if (nvls_ok && world > 2) v = Variant::NvlsTwoShot;
     else if (direct_ok) v = Variant::StreamDirect;
     else v = Variant::Stream;
@@ -341,9 +354,12 @@ Result MakePlan(int world, uint64_t count, Dtype in, Dtype out, int epilogue, Ke
                 bytes <= LowLatencyMaxBytes(world)) {
                 p.flags |= kFlagLowLatency;
                 if (!(row && row->ctas) && dev_ctas <= 0)
-                    // about 16 KiB of pushes per CTA (each CTA pushes its slice to world-1 peers)
-                    c = static_cast<uint32_t>(
-                        std::min<uint64_t>(std::max<uint64_t>(CeilDiv(bytes * (world - 1), 16ull << 10), 1), 64));
+                    // about 16 KiB of pushes per CTA (each CTA pushes its slice to world-1 peers); from
+                    // 512 KiB one 16-byte vector per thread (128 CTAs at 1 MiB measured fastest)
+                    c = bytes > (512ull << 10)
+                            ? 128u
+                            : static_cast<uint32_t>(std::min<uint64_t>(
+                                  std::max<uint64_t>(CeilDiv(bytes * (world - 1), 16ull << 10), 1), 64));
             }
             p.ctas = std::max<uint32_t>(1, std::min<uint32_t>(std::min<uint32_t>(c, max_ctas), kMaxFlashCtas));
             break;
@@ -390,7 +406,10 @@ Result MakePlan(int world, uint64_t count, Dtype in, Dtype out, int epilogue, Ke
             p.smem_bytes = st * per_stage;
             const uint32_t per_sm = std::max<uint32_t>(1, std::min<uint32_t>(2, (220u << 10) / (p.smem_bytes + 1024)));
             const uint32_t resident = per_sm * std::max<uint32_t>(caps.sm_count, 1);
-            p.ctas = std::max<uint32_t>(1, std::min<uint32_t>(std::min<uint32_t>(c, max_ctas), std::min<uint32_t>(resident, kBarSlots)));
+            // `max_ctas` counts two CTAs per SM (emulated ranks share one GPU and one cooperative launch):
+            // with stages so large that only one CTA fits an SM, half of that.
+            const uint32_t share = std::max<uint32_t>(1, per_sm >= 2 ? max_ctas : max_ctas / 2);
+            p.ctas = std::max<uint32_t>(1, std::min<uint32_t>(std::min<uint32_t>(c, share), std::min<uint32_t>(resident, kBarSlots)));
             p.slot_bytes = chunk;
             p.stages = st;
             if (one_shot) p.flags |= kFlagPullOneShot;
@@ -401,9 +420,12 @@ Result MakePlan(int world, uint64_t count, Dtype in, Dtype out, int epilogue, Ke
             p.shard_elems = ShardElems(count, world);
             // Measured on 8 x B200: the switch-side reduction saturates with few CTAs; 32 CTAs give
             // 843 GB/s bus bandwidth at 1 GiB where 148 give 725 and 296 give 636.
+            // On 4 x B200 16 CTAs lead up to 128 MiB (658 against 650 GB/s at 128 MiB, 23.5 against 24.8 us
+            // at 4 MiB); from 512 MiB 32 and 64 CTAs are level.
+            const uint64_t nvls_cap_ctas = (world <= 4 && bytes < (256ull << 20)) ? 16 : 32;
             uint32_t c = row && row->ctas ? row->ctas
                                           : static_cast<uint32_t>(std::min<uint64_t>(
-                                                std::max<uint64_t>(CeilDiv(bytes, 64ull << 10), 1), 32));
+                                                std::max<uint64_t>(CeilDiv(bytes, 64ull << 10), 1), nvls_cap_ctas));
             if (v == Variant::NvlsTwoShot)
                 c = static_cast<uint32_t>(std::min<uint64_t>(c, std::max<uint64_t>(CeilDiv(bytes / world, 8192), 1)));
             if (dev_ctas > 0) c = dev_ctas;

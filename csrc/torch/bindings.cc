@@ -370,7 +370,7 @@ class PyComm {
     // dst = scale * sum over ranks of src, both in pinned host memory; copies and all-reduce
     // overlap chunk by chunk (ops/host_pipeline.h).
     void AllReduceHost(std::vector<at::Tensor> src, std::vector<at::Tensor> dst, int64_t chunk_bytes,
-                       c10::optional<double> scale, const std::string& mode) {
+                       c10::optional<double> scale, const std::string& mode, bool copies_only) {
         const int nl = c().nlocal();
         TORCH_CHECK(static_cast<int>(src.size()) == nl && static_cast<int>(dst.size()) == nl,
                     "yali: one src and one dst tensor per local rank");
@@ -397,7 +397,7 @@ class PyComm {
         auto st = Streams();
         c10::cuda::OptionalCUDAGuard guard(c().device_of(0));
         Throw(host_pipe_->AllReduce(s.data(), r.data(), static_cast<uint64_t>(n), ToDtype(d), o,
-                                    static_cast<uint64_t>(std::max<int64_t>(chunk_bytes, 4096)), st.data()),
+                                    static_cast<uint64_t>(std::max<int64_t>(chunk_bytes, 4096)), st.data(), copies_only),
               c().last_error());
     }
 
@@ -552,7 +552,7 @@ PYBIND11_MODULE(_C, m) {
         .def("symm_empty", &PyComm::SymmEmpty, py::arg("shape"), py::arg("dtype"))
         .def("symm_reset", &PyComm::SymmReset)
         .def("all_reduce_host", &PyComm::AllReduceHost, py::arg("src"), py::arg("dst"), py::arg("chunk_bytes") = 8 << 20,
-             py::arg("scale") = py::none(), py::arg("mode") = "auto")
+             py::arg("scale") = py::none(), py::arg("mode") = "auto", py::arg("copies_only") = false)
         .def("sync", &PyComm::Sync)
         .def("check", &PyComm::Check)
         .def("reset", &PyComm::Reset)

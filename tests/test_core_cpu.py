@@ -98,13 +98,18 @@ def test_heap_layout(native_lib):
 def test_plan_pipelined_variants_need_addressable_buffers(native_lib):
     lib = native_lib
     addressable = dict(peer_recv=1, peer_send=1)
-    rc, p, _ = make_plan(lib, 2, 1 << 20, cp=caps(2, **addressable))  # 4 MiB at two ranks
+    rc, p, _ = make_plan(lib, 2, 1 << 20, mode=4, cp=caps(2, **addressable))  # 4 MiB at two ranks, forced pull
     assert rc == 0 and p.variant == 4 and p.flags & 256 and p.stages >= 2 and p.smem_bytes == p.stages * 2 * p.slot_bytes
     assert p.smem_bytes <= 100 * 1024  # two CTAs share an SM
-    rc, p, _ = make_plan(lib, 2, 1 << 20, cp=caps(2, in_place=1, **addressable))
-    assert rc == 0 and p.variant == 5  # the one-shot pull cannot run in place
-    rc, p, _ = make_plan(lib, 2, 32 * MiB, cp=caps(2, **addressable))  # 128 MiB: two-shot, all SMs twice
-    assert rc == 0 and p.variant == 5 and p.ctas == 296 and p.shard_elems == 16 * MiB
+    rc, p, msg = make_plan(lib, 2, 1 << 20, mode=4, cp=caps(2, in_place=1, **addressable))
+    assert rc != 0 and "cannot run" in msg  # the one-shot pull cannot run in place
+    rc, p, _ = make_plan(lib, 2, 1 << 20, cp=caps(2, **addressable))
+    assert rc == 0 and p.variant == 0  # by size the staged one-shot keeps 4 MiB (measured faster than the pull)
+    rc, p, _ = make_plan(lib, 2, 32 * MiB, cp=caps(2, **addressable))  # 128 MiB: pipelined two-shot, one CTA per SM
+    assert rc == 0 and p.variant == 5 and p.ctas == 148 and p.shard_elems == 16 * MiB
+    assert p.slot_bytes == 32768 and p.stages == 3 and p.smem_bytes == 3 * 2 * 32768
+    rc, p, _ = make_plan(lib, 2, 32 * MiB, cp=caps(2, in_place=1, **addressable))
+    assert rc == 0 and p.variant == 5  # safe in place
     rc, p, _ = make_plan(lib, 2, 32 * MiB)  # plain buffers: the ring kernel
     assert rc == 0 and p.variant == 1
     rc, p, _ = make_plan(lib, 2, 1024, cp=caps(2, **addressable))

@@ -217,15 +217,18 @@ class Comm:
         return self._like_input(x, outs)
 
     def all_reduce_host(self, src: TensorOrList, dst: Optional[TensorOrList] = None, *,
-                        chunk_bytes: int = 8 << 20, scale: Optional[float] = None, mode: str = "auto"):
+                        chunk_bytes: int = 8 << 20, scale: Optional[float] = None, mode: str = "auto",
+                        copies_only: bool = False):
         """All-reduce of tensors that live in pinned host memory: dst = scale * sum over ranks of src.
 
         The message is cut into chunks that move through three streams per GPU: host-to-device copy,
         all-reduce, device-to-host copy.  Chunk i+1 is copied in while chunk i is reduced and chunk i-1
         is copied out, so both PCIe directions and NVLink are busy at the same time and a call costs
         about one direction's copy time instead of the sum of the three phases.  Staging is a ring of
-        three symmetric chunk buffers per direction, allocated on first use (every rank must make the
-        same calls).  The call returns with the work queued; the caller's current stream waits for it."""
+        four symmetric chunk buffers per direction, allocated on first use and reused by every later
+        call that fits (every rank must make the same calls).  The call returns with the work queued;
+        the caller's current stream waits for it.  `copies_only=True` leaves the collective out
+        (dst = src through the device): the ceiling the host link sets for the same call."""
         srcs = self._as_list(src, "src")
         if dst is None:
             dsts = [torch.empty_like(t).pin_memory() for t in srcs]
@@ -235,7 +238,7 @@ class Comm:
             if t.is_cuda or not t.is_pinned() or not t.is_contiguous():
                 raise ValueError("all_reduce_host takes contiguous tensors in pinned host memory")
         try:
-            self._impl.all_reduce_host(srcs, dsts, int(chunk_bytes), scale, mode)
+            self._impl.all_reduce_host(srcs, dsts, int(chunk_bytes), scale, mode, bool(copies_only))
         except RuntimeError as e:
             raise _translate(e) from None
         return self._like_input(src, dsts)
