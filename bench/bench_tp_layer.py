@@ -6,7 +6,9 @@ bf16, W ~ N(0, 0.02), x ~ N(0, 1), eps 1e-5), T in {1, 16, 128, 2048}.
     python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 bench/bench_tp_layer.py
     python bench/bench_tp_layer.py --emulate 8         # one GPU, ranks emulated (no NVLink)
 
-Arms: `fused` = one kernel per rank (tcgen05 GEMM, peer pushes, reduce + norm);
+Arms: `fused_*` = one kernel per rank (tcgen05 GEMM, peer pushes, reduce + norm): the 128 x 128
+tile form one-shot / two-shot (peer stores, in-switch reduce, multicast delivery), `fused_decode` =
+the few-token form (T <= 64), `fused_auto` = the form RowParallelLinearNorm picks by size;
 `gemm+ar_norm` = library GEMM, then this library's all-reduce fused with residual +
 RMSNorm; `nccl` = library GEMM, NCCL all-reduce, PyTorch residual + RMSNorm (the baseline;
 not available with --emulate).  Times are device times (CUDA events, max over ranks).
@@ -125,7 +127,12 @@ def main():
             if nvls and not has_nvls:
                 continue
             arms[label] = lambda oneshot=oneshot, nvls=nvls: comm.fused_linear_rmsnorm(
-                one(xs), one(ws), one(nw), one(res), out=one(outs), oneshot=oneshot, nvls=nvls)
+                one(xs), one(ws), one(nw), one(res), out=one(outs), oneshot=oneshot, nvls=nvls, decode=False)
+        if T <= 64 and W > 1:  # the few-token form: hidden/32 CTAs, partial rows as flag-in-data lines
+            arms["fused_decode"] = lambda: comm.fused_linear_rmsnorm(one(xs), one(ws), one(nw), one(res), out=one(outs),
+                                                                     decode=True)
+        # What RowParallelLinearNorm runs: the form picked by size.
+        arms["fused_auto"] = lambda: comm.fused_linear_rmsnorm(one(xs), one(ws), one(nw), one(res), out=one(outs))
         arms["gemm+ar_norm"] = lambda: tp.unfused_row_parallel(comm, xs, ws, nw, res) if nl > 1 else \
             comm.all_reduce_rmsnorm(xs[0] @ ws[0].T, nw[0], res[0])
         if use_nccl:
@@ -144,18 +151,20 @@ def main():
             if args.arms and label not in args.arms.split(","):
                 continue
             us = timed(comm, fn, iters, args.warmup, graph=args.graph)
-            link_bytes = 0.0 if emu else (bytes_one if label == "fused_oneshot" else bytes_two)
+            one_shot_traffic = label in ("fused_oneshot", "fused_decode") or (label == "fused_auto" and T <= 64)
+            link_bytes = 0.0 if emu else (bytes_one if one_shot_traffic else bytes_two)
             roof = max(t_gemm, link_bytes / (LINK_GBS * 1e9) * 1e6)
             row = {"T": T, "world": W, "arm": label, "us": round(us, 2), "roofline_us": round(roof, 3),
                    "fraction_of_roofline": round(roof / us, 4), "peaks": src, "emulated": emu,
                    "timing": "graph" if args.graph else "events"}
             if args.trace and label.startswith("fused_"):
-                mode = {"fused_oneshot": (True, 0), "fused_twoshot": (False, 0), "fused_twoshot_nvls": (False, 1),
-                        "fused_twoshot_mcast": (False, 2)}[label]
+                mode = {"fused_oneshot": (True, 0, False), "fused_twoshot": (False, 0, False),
+                        "fused_twoshot_nvls": (False, 1, False), "fused_twoshot_mcast": (False, 2, False),
+                        "fused_decode": (None, None, True), "fused_auto": (None, None, None)}[label]
                 tr = [torch.zeros(8, dtype=torch.int64, device=dev[i]) for i in range(nl)]
                 for _ in range(3):
                     comm.fused_linear_rmsnorm(one(xs), one(ws), one(nw), one(res), out=one(outs), oneshot=mode[0],
-                                              nvls=mode[1], trace=one(tr))
+                                              nvls=mode[1], decode=mode[2], trace=one(tr))
                 comm.sync()
                 comm.barrier()
                 t = tr[0].cpu().tolist()

@@ -115,9 +115,9 @@ int yali_c_make_plan(int world, uint64_t count, int in_dt, int out_dt, int epilo
 int yali_c_heap_layout(int world, uint64_t requested_total, uint64_t* f) {
     HeapLayout l;
     if (!MakeHeapLayout(world, requested_total, 0, &l)) return 1;
-    const uint64_t v[14] = {l.total_bytes, l.flags_off, l.flash_off, l.flash_cap, l.ring_off,  l.ring_bytes,
-                            l.nvls_off,    l.nvls_cap,  l.gemm_off,  l.gemm_cap,  l.user_off,  l.user_bytes,
-                            l.ll_off,      l.ll_cap};
+    const uint64_t v[16] = {l.total_bytes, l.flags_off, l.flash_off, l.flash_cap, l.ring_off,    l.ring_bytes,
+                            l.nvls_off,    l.nvls_cap,  l.gemm_off,  l.gemm_cap,  l.user_off,    l.user_bytes,
+                            l.ll_off,      l.ll_cap,    l.gemm_ll_off, l.gemm_ll_cap};
     std::memcpy(f, v, sizeof(v));
     return 0;
 }

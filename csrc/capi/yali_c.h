@@ -60,7 +60,7 @@ typedef struct YaliPlan {
 /* mode: 0 auto, 1 flash, 2 stream, 3 nvls, 4 flash_pull, 5 stream_direct.  tuning_json may be NULL.  Returns a Result code. */
 int yali_c_make_plan(int world, uint64_t count, int in_dtype, int out_dtype, int epilogue, int mode,
                      const YaliPlanCaps* caps, const char* tuning_json, YaliPlan* plan, char* err, size_t err_len);
-int yali_c_heap_layout(int world, uint64_t requested_total, uint64_t* fields /* 14 values: the 12 region fields, then ll_off, ll_cap */);
+int yali_c_heap_layout(int world, uint64_t requested_total, uint64_t* fields /* 16 values: the 12 region fields, then ll_off, ll_cap, gemm_ll_off, gemm_ll_cap */);
 
 /* ---- partition arithmetic (mirrors the device code) ---- */
 void yali_c_flash_slice(uint64_t count, int vec, uint32_t ctas, uint32_t cta, int vec_ok, uint64_t* out4);

@@ -29,6 +29,8 @@ constexpr uint32_t kCallStreamSeq = 1;    // ring sequence numbers consumed so f
 constexpr uint32_t kCallBarEpoch = 2;     // per-CTA barrier epochs consumed so far
 constexpr uint32_t kCallGemmEpoch = 3;    // fused GEMM calls so far
 constexpr uint32_t kCallFlashEpochHi = 5;  // upper half of the one-shot call number (flag-in-data protocol)
+constexpr uint32_t kCallGemmLLEpoch = 6;   // calls of the fused GEMM's few-token form so far (lower half)
+constexpr uint32_t kCallGemmLLEpochHi = 7;  // upper half of that call number
 constexpr uint32_t kCallGemmCnt = 4;      // arrivals (per source) this rank has been promised so far
 constexpr uint32_t kCallGemmDone = 8;     // [kMaxRanks] rows each owner has been asked to deliver so far
 constexpr uint32_t kCallDoneCtas = 16;    // [4] CTAs of the running launch that have finished, per kernel kind
@@ -66,6 +68,8 @@ struct HeapLayout {
     uint64_t gemm_cap;
     uint64_t ll_off;       // staging of the flag-in-data one-shot protocol: [2 parities][world-1 sources][2 * ll_cap]
     uint64_t ll_cap;       // largest message (bytes of payload) that protocol takes
+    uint64_t gemm_ll_off;  // landing zone of the fused GEMM's few-token form, flag-in-data lines: [2][world][gemm_ll_cap]
+    uint64_t gemm_ll_cap;  // bytes per (parity, source): rows * N * 2 bytes of payload, doubled by the flags
     uint64_t user_off;     // symmetric allocations handed to the user
     uint64_t user_bytes;
 };

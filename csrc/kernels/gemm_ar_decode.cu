@@ -1,0 +1,326 @@
+// Few-token form of the fused tensor-parallel layer (decode: T <= 64 rows):
+//
+//     out = RMSNorm(residual + sum_r x_r @ W_r^T) * norm_weight
+//
+// The full-size kernel (gemm_ar_rmsnorm.cu) cuts the output into 128x128 tiles, which for a
+// handful of tokens leaves N/128 = 32 CTAs streaming the weight slice and pays a release
+// fence plus a counter round trip before the reduction.  This form is built for latency:
+//
+//   * tiles are 128 (padded rows) x 32 columns, so N/32 = 128 CTAs each stream 1/128 of
+//     the weight slice: warp 0 feeds an 8-stage shared-memory ring with TMA
+//     (cp.async.bulk.tensor, 128-byte swizzle, no multicast; rows of x beyond T are
+//     out-of-bounds and arrive as zeros), warp 1 issues tcgen05.mma (M = 128, N = 32,
+//     bf16 x bf16 -> fp32) into a 32-column TMEM accumulator, and of warps 2..5 the ones
+//     whose TMEM lane quarter holds real rows read the accumulator back (tcgen05.ld);
+//   * every row of the partial tile (32 bf16 = 64 bytes) goes to EVERY rank, this one
+//     included, as eight 16-byte lines that carry 8 bytes of payload and the 64-bit call
+//     number {data, call_lo, data, call_hi}: the flag travels in the data, so there is no
+//     release fence, no counter and no barrier between the GEMM and the reduction;
+//   * CTA t (t < T) then owns row t on this rank: its 512 threads poll the lines of all
+//     ranks for one 16-byte output vector each (all loads of a vector in flight together),
+//     add them in fp32 in rank order, add the residual, normalise and store the row.
+// Every rank normalises all T rows for itself (one-shot), so nothing is sent back.
+//
+// Parity: none in the reference (no GEMM, no fused op, no tensor-core code there).
+#include <cuda.h>
+
+#include "coll_common.cuh"
+#include "gemm_ar_rmsnorm.h"
+
+namespace yali {
+
+namespace {
+
+constexpr int DBM = 128, DBN = kGemmDecodeTileN, DBK = 64;
+constexpr int kDStages = 8;
+constexpr uint32_t kDStageA = DBM * DBK * 2, kDStageB = DBN * DBK * 2, kDStageBytes = kDStageA + kDStageB;
+constexpr uint32_t kDSmemBytes = kDStages * kDStageBytes + 1024;  // + slack to align the base
+constexpr uint32_t kDTmemCols = 64;                               // two accumulators of 32 fp32 columns
+
+// D = fp32, A = B = bf16, both K-major, N at bit 17 (>>3), M at bit 24 (>>4).
+constexpr uint32_t kDIdesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(DBN >> 3) << 17) |
+                             (static_cast<uint32_t>(DBM >> 4) << 24);
+
+__device__ __forceinline__ uint64_t desc_sw128(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((smem_addr & 0x3ffffu) >> 4);
+    d |= static_cast<uint64_t>(1) << 16;
+    d |= static_cast<uint64_t>(1024 >> 4) << 32;
+    d |= static_cast<uint64_t>(1) << 46;
+    d |= static_cast<uint64_t>(2) << 61;
+    return d;
+}
+
+__device__ __forceinline__ uint4 ld_volatile16(const void* p) {
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p)
+                 : "memory");
+    return v;
+}
+
+// Flag-in-data landing zone on `on_rank` for the partial rows of `src`: line i (16 bytes) holds
+// columns 4i..4i+3 of the row-major [T, N] partial.
+__device__ __forceinline__ char* ll_landing(const GemmDecodeArgs& a, int on_rank, int src, uint32_t parity) {
+    return a.cv.heap[on_rank] + a.cv.lay.gemm_ll_off +
+           (static_cast<uint64_t>(parity) * a.cv.world + src) * a.cv.lay.gemm_ll_cap;
+}
+
+__device__ __forceinline__ void decode_body(const GemmDecodeArgs& a, const CUtensorMap* tmap_a,
+                                            const CUtensorMap* tmap_b, uint32_t cta, uint32_t nctas) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t full_bar[kDStages], empty_bar[kDStages], tmem_full_bar[2], tmem_empty_bar[2];
+    __shared__ uint32_t s_tmem;
+    __shared__ int s_abort;
+    __shared__ float s_red[32];
+    __shared__ uint32_t s_call[2];
+
+    const CommView& cv = a.cv;
+    const int W = cv.world, r = cv.rank;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    volatile int* abort_flag = &s_abort;
+    const uint64_t deadline = ptx::globaltimer() + cv.timeout_ns;
+#define YALI_DSTAMP(slot, who)                                                       \
+    do {                                                                             \
+        if (a.trace && cta == 0 && tid == (who)) a.trace[slot] = ptx::globaltimer(); \
+    } while (0)
+    YALI_DSTAMP(0, 0);
+    if (tid < 2)
+        s_call[tid] = *reinterpret_cast<volatile uint32_t*>(flag_word(cv, r, tid == 0 ? kCallGemmLLEpoch : kCallGemmLLEpochHi));
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    if (tid == 0) {
+        s_abort = 0;
+        for (int s = 0; s < kDStages; ++s) {
+            ptx::mbar_init(&full_bar[s], 1);
+            ptx::mbar_init(&empty_bar[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            ptx::mbar_init(&tmem_full_bar[b], 1);
+            ptx::mbar_init(&tmem_empty_bar[b], 4);  // the four epilogue warps
+        }
+        ptx::mbar_fence_init();
+        ptx::tma_prefetch_desc(tmap_a);
+        ptx::tma_prefetch_desc(tmap_b);
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc(&s_tmem, kDTmemCols);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem = s_tmem;
+    const uint32_t lo = s_call[0] + 1u;                                    // this call's number
+    const uint32_t hi = (s_call[1] + (lo == 0u ? 1u : 0u)) | 0x80000000u;  // never zero: fresh memory never matches
+    const uint32_t parity = lo & 1u;
+    YALI_DSTAMP(1, 0);
+
+    const uint32_t ntn = a.N / DBN, kblocks = a.K / DBK;
+
+    // ------------------------------------------------------------------ phase 1: GEMM tiles [128 x 32]
+    if (warp == 0) {
+        if (lane == 0) {
+            uint32_t g = 0;
+            for (uint32_t tile = cta; tile < ntn && !*abort_flag; tile += nctas) {
+                for (uint32_t kb = 0; kb < kblocks; ++kb, ++g) {
+                    const uint32_t s = g % kDStages;
+                    if (!mbar_wait_deadline(&empty_bar[s], ((g / kDStages) & 1u) ^ 1u, deadline, abort_flag)) {
+                        if (!*abort_flag) report_timeout(cv, kSiteMbar, r, cta, 11, g);
+                        *abort_flag = 1;
+                        break;
+                    }
+                    ptx::mbar_expect_tx(&full_bar[s], kDStageBytes);
+                    ptx::tma_load_2d(smem + s * kDStageBytes, tmap_a, kb * DBK, 0, &full_bar[s]);
+                    ptx::tma_load_2d(smem + s * kDStageBytes + kDStageA, tmap_b, kb * DBK, tile * DBN, &full_bar[s]);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            uint32_t g = 0, it = 0;
+            for (uint32_t tile = cta; tile < ntn && !*abort_flag; tile += nctas, ++it) {
+                const uint32_t b = it & 1u;
+                if (!mbar_wait_deadline(&tmem_empty_bar[b], ((it >> 1) & 1u) ^ 1u, deadline, abort_flag)) {
+                    if (!*abort_flag) report_timeout(cv, kSiteMbar, r, cta, 14, it);
+                    *abort_flag = 1;
+                    break;
+                }
+                ptx::tc_fence_after_sync();
+                const uint32_t d_tmem = tmem + b * DBN;
+                for (uint32_t kb = 0; kb < kblocks; ++kb, ++g) {
+                    const uint32_t s = g % kDStages;
+                    if (!mbar_wait_deadline(&full_bar[s], (g / kDStages) & 1u, deadline, abort_flag)) {
+                        if (!*abort_flag) report_timeout(cv, kSiteMbar, r, cta, 12, g);
+                        *abort_flag = 1;
+                        break;
+                    }
+                    ptx::tc_fence_after_sync();
+                    const uint32_t a_addr = ptx::smem_u32(smem + s * kDStageBytes);
+                    const uint64_t da = desc_sw128(a_addr), db = desc_sw128(a_addr + kDStageA);
+#pragma unroll
+                    for (int k = 0; k < DBK / 16; ++k)
+                        ptx::tc_mma_f16(d_tmem, da + 2 * k, db + 2 * k, kDIdesc, (kb | k) != 0 ? 1u : 0u);
+                    ptx::tc_commit(&empty_bar[s]);
+                }
+                if (*abort_flag) break;
+                ptx::tc_commit(&tmem_full_bar[b]);
+            }
+        }
+    } else if (warp < 6) {
+        const int q = warp & 3;  // TMEM lane quarter this warp may read
+        uint32_t it = 0;
+        for (uint32_t tile = cta; tile < ntn; tile += nctas, ++it) {
+            const uint32_t b = it & 1u;
+            if (!mbar_wait_deadline(&tmem_full_bar[b], (it >> 1) & 1u, deadline, abort_flag)) {
+                if (lane == 0 && !*abort_flag) report_timeout(cv, kSiteMbar, r, cta, 13, it);
+                *abort_flag = 1;
+                break;
+            }
+            ptx::tc_fence_after_sync();
+            if (it == 0) YALI_DSTAMP(2, 64);  // first accumulator complete
+            const uint32_t row = q * 32 + lane;
+            if (static_cast<uint32_t>(q) * 32 < a.T) {  // this quarter holds real rows
+                uint32_t v[32];
+                ptx::tmem_ld_32x32(tmem + b * DBN + (static_cast<uint32_t>(q * 32) << 16), v);
+                ptx::tmem_ld_wait();
+                ptx::tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(&tmem_empty_bar[b]);
+                if (row < a.T) {
+                    // 32 fp32 -> 32 bf16 -> eight lines {2 bf16, call_lo, 2 bf16, call_hi}
+                    uint32_t packed[16];
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+                        packed[i] = *reinterpret_cast<const uint32_t*>(&h);
+                    }
+                    const uint64_t line0 = (static_cast<uint64_t>(row) * a.N + static_cast<uint64_t>(tile) * DBN) / 4;
+                    for (int k = 0; k < W; ++k) {
+                        const int d = (r + k) % W;  // own copy first, then the right-hand neighbour
+                        char* dst = ll_landing(a, d, r, parity) + line0 * 16;
+#pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            ptx::st_v4(dst + j * 16, make_uint4(packed[2 * j], lo, packed[2 * j + 1], hi));
+                    }
+                }
+            } else {
+                ptx::tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(&tmem_empty_bar[b]);
+            }
+        }
+    }
+
+    // TMEM is not needed any more (also on the abort path).
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) ptx::tmem_dealloc(tmem, kDTmemCols);
+    if (s_abort) return;
+    YALI_DSTAMP(3, 0);  // all tiles of this CTA pushed
+
+    // ------------------------------------------------------------------ phase 2: rows, all threads
+    constexpr int VEC = 8;  // bf16 per 16 bytes
+    const uint32_t vec_per_row = a.N / VEC;
+    const char* res = static_cast<const char*>(a.residual);
+    char* res_out = static_cast<char*>(a.residual_out);
+    const char* wgt = static_cast<const char*>(a.norm_weight);
+    const float inv_n = 1.f / static_cast<float>(a.N);
+    const int nt = blockDim.x;
+    for (uint32_t row = cta; row < a.T; row += nctas) {
+        float f[kGemmDecodeVecPerThread][VEC];
+        float ss = 0.f;
+        bool timed_out = false;
+#pragma unroll
+        for (int j = 0; j < kGemmDecodeVecPerThread; ++j) {
+            const uint32_t c = tid + j * nt;
+            if (c < vec_per_row && !timed_out) {
+                // Output vector c = columns 8c..8c+7 = lines 2c and 2c+1 of the row, from every rank.
+                const uint64_t off = ((static_cast<uint64_t>(row) * a.N + static_cast<uint64_t>(c) * VEC) / 4) * 16;
+                uint4 l0[kMaxRanks], l1[kMaxRanks];
+                uint32_t pending = (1u << W) - 1u, polls = 0;
+                const uint4 rv = res ? ptx::ld_cg_v4(res + (static_cast<uint64_t>(row) * a.N + static_cast<uint64_t>(c) * VEC) * 2)
+                                     : make_uint4(0, 0, 0, 0);
+                while (pending) {
+#pragma unroll
+                    for (int q = 0; q < kMaxRanks; ++q) {
+                        if (q < W && (pending >> q & 1u)) {
+                            const char* p = ll_landing(a, r, q, parity) + off;
+                            l0[q] = ld_volatile16(p);
+                            l1[q] = ld_volatile16(p + 16);
+                        }
+                    }
+#pragma unroll
+                    for (int q = 0; q < kMaxRanks; ++q) {
+                        if (q < W && (pending >> q & 1u) && l0[q].y == lo && l0[q].w == hi && l1[q].y == lo && l1[q].w == hi)
+                            pending &= ~(1u << q);
+                    }
+                    if (pending && (++polls & 63u) == 0u && (*abort_flag || ptx::globaltimer() > deadline)) {
+                        if (!*abort_flag) report_timeout(cv, kSiteGemmPartials, __ffs(pending) - 1, cta, lo, 0u);
+                        timed_out = true;
+                        break;
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) f[j][i] = 0.f;
+                if (!timed_out) {
+#pragma unroll
+                    for (int q = 0; q < kMaxRanks; ++q)
+                        if (q < W) accumulate<__nv_bfloat16>(f[j], make_uint4(l0[q].x, l0[q].z, l1[q].x, l1[q].z));
+                    if (res) accumulate<__nv_bfloat16>(f[j], rv);
+                    if (res_out)
+                        ptx::st_v4(res_out + (static_cast<uint64_t>(row) * a.N + static_cast<uint64_t>(c) * VEC) * 2,
+                                   pack16<__nv_bfloat16>(f[j]));
+#pragma unroll
+                    for (int i = 0; i < VEC; ++i) ss += f[j][i] * f[j][i];
+                }
+            }
+        }
+        if (__syncthreads_or(timed_out ? 1 : 0)) {
+            if (tid == 0) s_abort = 1;
+            break;
+        }
+        const float inv_rms = rsqrtf(block_sum(ss, s_red) * inv_n + a.eps);
+#pragma unroll
+        for (int j = 0; j < kGemmDecodeVecPerThread; ++j) {
+            const uint32_t c = tid + j * nt;
+            if (c < vec_per_row) {
+                float w[VEC];
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) w[i] = 0.f;
+                accumulate<__nv_bfloat16>(w, *reinterpret_cast<const uint4*>(wgt + static_cast<uint64_t>(c) * 16));
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) f[j][i] = f[j][i] * inv_rms * w[i];
+                ptx::st_v4(static_cast<char*>(a.out) + (static_cast<uint64_t>(row) * a.N + static_cast<uint64_t>(c) * VEC) * 2,
+                           pack16<__nv_bfloat16>(f[j]));
+            }
+        }
+    }
+    __syncthreads();
+    if (s_abort) return;
+    YALI_DSTAMP(4, 0);  // rows written
+#undef YALI_DSTAMP
+    if (tid == 0 && check_out_last(cv, 3, nctas)) {
+        advance_call_word(cv, kCallGemmLLEpoch, 1);
+        if (lo == 0u) advance_call_word(cv, kCallGemmLLEpochHi, 1);
+    }
+}
+
+}  // namespace
+
+__global__ void __launch_bounds__(kGemmDecodeThreads, 1) gemm_ar_decode_kernel(const __grid_constant__ GemmDecodeArgs a) {
+    decode_body(a, &a.tmap_a, &a.tmap_b, blockIdx.x, gridDim.x);
+}
+
+// All ranks of an emulated communicator in one cooperative launch (ranks = blockIdx.y).
+__global__ void __launch_bounds__(kGemmDecodeThreads, 1)
+    gemm_ar_decode_kernel_emu(const __grid_constant__ GemmDecodeEmuArgs e) {
+    const GemmDecodeArgs& a = e.r[blockIdx.y];
+    decode_body(a, &a.tmap_a, &a.tmap_b, blockIdx.x, gridDim.x);
+}
+
+const void* GemmDecodeKernel(bool emu) {
+    return emu ? reinterpret_cast<const void*>(gemm_ar_decode_kernel_emu)
+               : reinterpret_cast<const void*>(gemm_ar_decode_kernel);
+}
+uint32_t GemmDecodeSmemBytes() { return kDSmemBytes; }
+
+}  // namespace yali

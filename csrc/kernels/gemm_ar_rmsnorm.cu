@@ -7,15 +7,17 @@
 // [N, K] (this rank's slice of the row-parallel weight, K contiguous, the layout of
 // torch.nn.Linear.weight), both bf16; the sum runs over the ranks.
 //
-// Phase 1 (GEMM): a persistent grid (one 7-warp CTA per SM) walks 128x128 output
+// Phase 1 (GEMM): a persistent grid (one 11-warp CTA per SM) walks 128x128 output
 // tiles, warp-specialised.  Warp 0 feeds a 5-stage shared-memory pipeline with TMA
 // (cp.async.bulk.tensor, 128-byte swizzle, no multicast); warp 1 issues tcgen05.mma
 // (bf16 x bf16 -> fp32) into one of two 128-column TMEM accumulators and signals
 // stage release and accumulator completion through tcgen05.commit on mbarriers;
-// warps 2..5 read a finished accumulator back with tcgen05.ld while the next tile's
-// MMAs run into the other one, round to bf16, transpose through swizzled shared
-// memory and PUSH every row straight into the landing zone of the rank that owns
-// that row (peer stores over NVLink).  Warp 6 announces each pushed tile to the
+// warps 2..9 (two per TMEM lane quarter, each taking half of the columns) read a
+// finished accumulator back with tcgen05.ld while the next tile's MMAs run into the
+// other one, round to bf16, transpose through swizzled shared memory and PUSH every
+// row straight into the landing zone of the rank that owns that row (peer stores
+// over NVLink): while one warp of a pair reads TMEM and converts, the other one's
+// stores are in flight.  Warp 10 announces each pushed tile to the
 // owners with red.release.sys on their arrival counters: the fence in front of that
 // reduction waits for the peer stores to land, so it sits in a warp of its own and
 // the epilogue warps go straight on to the next tile.
@@ -48,10 +50,10 @@ namespace {
 
 constexpr int BM = kGemmTileM, BN = kGemmTileN, BK = 64;  // BK bf16 = one 128-byte swizzle row
 constexpr int kStages = 5;
-constexpr int kEpilogueWarps = 4;
+constexpr int kEpilogueWarps = 8;  // two per TMEM lane quarter, each takes half of the tile's columns
 constexpr uint32_t kStageABytes = BM * BK * 2, kStageBBytes = BN * BK * 2;
 constexpr uint32_t kStageBytes = kStageABytes + kStageBBytes;
-constexpr uint32_t kEpiStageBytes = kEpilogueWarps * 32 * BN * 2;  // transposition buffer of the epilogue warps
+constexpr uint32_t kEpiStageBytes = kEpilogueWarps * 32 * (BN / 2) * 2;  // transposition buffers of the epilogue warps
 constexpr uint32_t kSmemBytes = kStages * kStageBytes + kEpiStageBytes + 1024;  // + slack to align the base
 constexpr uint32_t kTmemCols = 256;  // two accumulators of BN fp32 columns
 
@@ -155,8 +157,8 @@ __device__ __forceinline__ void gemm_ar_body(const GemmArArgs& a, const CUtensor
     const uint32_t mt_shift = a.oneshot ? 0u : (((static_cast<uint32_t>(r) + 1u) % W) * Rs / BM) % ntm;
 
     // ------------------------------------------------------------------ phase 1: GEMM tiles, warp-specialised
-    // warp 0: TMA producer; warp 1: MMA issuer; warps 2..5: epilogue (TMEM -> bf16 -> peers);
-    // warp 6: announcer (arrival counters of the owners).
+    // warp 0: TMA producer; warp 1: MMA issuer; warps 2..9: epilogue (TMEM -> bf16 -> peers);
+    // warp 10: announcer (arrival counters of the owners).
     // Two TMEM accumulators of 128 columns alternate, so the MMAs of tile i+1 run while tile i
     // is read back and pushed.
     if (warp == 0) {
@@ -210,8 +212,8 @@ __device__ __forceinline__ void gemm_ar_body(const GemmArArgs& a, const CUtensor
                 ptx::tc_commit(&tmem_full_bar[b]);  // accumulator complete
             }
         }
-    } else if (warp == 6) {
-        // Announcer: when the four epilogue warps have issued the pushes of a tile, tell every owner
+    } else if (warp == 2 + kEpilogueWarps) {
+        // Announcer: when the eight epilogue warps have issued the pushes of a tile, tell every owner
         // that received rows of it.  red.release.sys orders the pushes (made visible to this warp by
         // the mbarrier) before the counter; waiting for them costs an NVLink round trip, which this
         // warp absorbs instead of the epilogue warps.
@@ -232,11 +234,13 @@ __device__ __forceinline__ void gemm_ar_body(const GemmArArgs& a, const CUtensor
             }
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(&announced_bar[b]);
-            if (it == 0) YALI_STAMP(3, 192);  // first tile pushed and announced
+            if (it == 0) YALI_STAMP(3, (2 + kEpilogueWarps) * 32);  // first tile pushed and announced
         }
     } else {
-        const int q = warp & 3;                       // TMEM lane quarter this warp may read
-        uint8_t* stage = smem + kStages * kStageBytes + q * (32 * BN * 2);  // 32 rows x 256 bytes per warp
+        const int q = warp & 3;         // TMEM lane quarter this warp may read
+        const int h = (warp - 2) >> 2;  // column half of the tile this warp handles: [64h, 64h + 64)
+        constexpr int HN = BN / 2;      // 64 columns = 128 bytes of bf16 per row
+        uint8_t* stage = smem + kStages * kStageBytes + (warp - 2) * (32 * HN * 2);  // 32 rows x 128 bytes per warp
         uint32_t it = 0;
         for (uint32_t tile = cta; tile < ntiles; tile += nctas, ++it) {
             const uint32_t mt = (tile / ntn + mt_shift) % ntm, nt = tile % ntn, b = it & 1u;
@@ -250,10 +254,10 @@ __device__ __forceinline__ void gemm_ar_body(const GemmArArgs& a, const CUtensor
             // Warps whose 32 rows lie entirely beyond T (small batches) have nothing to read back.
             const bool warp_has_rows = mt * BM + q * 32 < a.T;
 #pragma unroll
-            for (int c = 0; c < BN / 32; ++c) {
+            for (int c = 0; c < HN / 32; ++c) {
                 if (!warp_has_rows) break;
                 uint32_t v[32];
-                ptx::tmem_ld_32x32(tmem + b * BN + (static_cast<uint32_t>(q * 32) << 16) + c * 32, v);
+                ptx::tmem_ld_32x32(tmem + b * BN + (static_cast<uint32_t>(q * 32) << 16) + h * HN + c * 32, v);
                 ptx::tmem_ld_wait();
                 if (mt * BM + q * 32 + lane >= a.T) continue;  // this lane's row is padding
 #pragma unroll
@@ -261,24 +265,24 @@ __device__ __forceinline__ void gemm_ar_body(const GemmArArgs& a, const CUtensor
                     float f[8];
 #pragma unroll
                     for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(v[j * 8 + i]);
-                    const int chunk = c * 4 + j;  // logical 16-byte chunk of the 256-byte row
-                    *reinterpret_cast<uint4*>(stage + lane * (BN * 2) + ((chunk ^ (lane & 15)) << 4)) =
+                    const int chunk = c * 4 + j;  // logical 16-byte chunk of the 128-byte row
+                    *reinterpret_cast<uint4*>(stage + lane * (HN * 2) + ((chunk ^ (lane & 7)) << 4)) =
                         pack16<__nv_bfloat16>(f);
                 }
             }
-            // The accumulator is in shared memory now: hand it back to the MMA warp.
+            // The accumulator half is in shared memory now: hand it back to the MMA warp.
             ptx::tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(&tmem_empty_bar[b]);
-            const int half = lane >> 4, c16 = lane & 15;
+            const int rsub = lane >> 3, c16 = lane & 7;  // four rows per step, eight 16-byte chunks per row
 #pragma unroll 4
-            for (int rr = 0; rr < 32; rr += 2) {
-                const int row_in_warp = rr + half;
+            for (int rr = 0; rr < 32; rr += 4) {
+                const int row_in_warp = rr + rsub;
                 const uint32_t grow = mt * BM + q * 32 + row_in_warp;  // global row
                 if (grow < a.T) {
-                    const uint4 x = *reinterpret_cast<const uint4*>(stage + row_in_warp * (BN * 2) +
-                                                                    ((c16 ^ (row_in_warp & 15)) << 4));
-                    const uint64_t col_off = (static_cast<uint64_t>(nt) * BN) * 2 + c16 * 16;
+                    const uint4 x = *reinterpret_cast<const uint4*>(stage + row_in_warp * (HN * 2) +
+                                                                    ((c16 ^ (row_in_warp & 7)) << 4));
+                    const uint64_t col_off = (static_cast<uint64_t>(nt) * BN + h * HN) * 2 + c16 * 16;
                     if (a.nvls) {
                         ptx::st_v4(cv.heap[r] + landing_nvls_off(a, parity) + static_cast<uint64_t>(grow) * a.N * 2 + col_off, x);
                     } else if (a.oneshot) {

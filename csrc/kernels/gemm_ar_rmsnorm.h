@@ -12,8 +12,8 @@ namespace yali {
 
 constexpr int kGemmTileM = 128;
 constexpr int kGemmTileN = 128;
-constexpr int kGemmThreads = 224;  // TMA warp, MMA warp, four epilogue warps, announcer warp
-constexpr int kGemmMaxVecPerThread = 3;  // N <= 3 * 224 threads * 8 bf16 = 5376 (the host caps N at 4096)
+constexpr int kGemmThreads = 352;  // TMA warp, MMA warp, eight epilogue warps, announcer warp
+constexpr int kGemmMaxVecPerThread = 2;  // N <= 2 * 352 threads * 8 bf16 = 5632 (the host caps N at 4096)
 
 struct alignas(64) GemmArArgs {
     CUtensorMap tmap_a;  // x  [T, K] bf16, box 64 x 128, 128-byte swizzle
@@ -46,5 +46,29 @@ struct GemmArEmuArgs {
 
 const void* GemmArKernel(bool emu);
 uint32_t GemmArSmemBytes();
+
+// ---- few-token form (gemm_ar_decode.cu): 128 x 32 tiles, partial rows travel as flag-in-data lines
+constexpr int kGemmDecodeTileN = 32;
+constexpr int kGemmDecodeThreads = 512;       // TMA warp, MMA warp, four epilogue warps; all 16 warps reduce rows
+constexpr int kGemmDecodeVecPerThread = 1;    // N <= 512 threads * 8 bf16 = 4096
+constexpr uint32_t kGemmDecodeMaxRows = 64;   // two TMEM lane quarters
+
+struct alignas(64) GemmDecodeArgs {
+    CUtensorMap tmap_a;  // x  [T, K] bf16, box 64 x 128 (rows beyond T read as zeros), 128-byte swizzle
+    CUtensorMap tmap_b;  // W  [N, K] bf16, box 64 x 32, 128-byte swizzle
+    CommView cv;
+    const void* residual;     // [T, N] bf16 or nullptr
+    void* residual_out;       // [T, N] bf16 or nullptr
+    const void* norm_weight;  // [N] bf16
+    void* out;                // [T, N] bf16, this rank's
+    uint32_t T, N, K;
+    float eps;
+    unsigned long long* trace;  // optional: %globaltimer of CTA 0 at the phase boundaries
+};
+struct GemmDecodeEmuArgs {
+    GemmDecodeArgs r[kMaxRanks];
+};
+const void* GemmDecodeKernel(bool emu);
+uint32_t GemmDecodeSmemBytes();
 
 }  // namespace yali

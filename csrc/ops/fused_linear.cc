@@ -16,6 +16,89 @@ namespace yali {
 namespace {
 
 bool EncodeTileMap(const DriverApi* d, CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols_k,
+                   uint32_t box_rows, std::string* err);
+
+// Few-token form: one launch of gemm_ar_decode.cu per rank.
+Result LaunchDecode(Communicator& comm, const DriverApi* drv, const FusedLinearDesc* descs, uint32_t T, uint32_t N,
+                    uint32_t K, const FusedLinearOptions& opt, const cudaStream_t* streams) {
+    const int W = comm.world(), nlocal = comm.nlocal();
+    auto fail = [&](Result r, const std::string& what) {
+        comm.set_error(what);
+        return r;
+    };
+    const void* fn = GemmDecodeKernel(comm.emulated());
+    const uint32_t smem = GemmDecodeSmemBytes();
+    static std::mutex attr_mu;
+    static std::set<std::pair<int, int>> attr_done;
+    {
+        std::lock_guard<std::mutex> lock(attr_mu);
+        for (int i = 0; i < nlocal; ++i) {
+            const std::pair<int, int> key(comm.emulated() ? 1 : 0, comm.device_of(i));
+            if (attr_done.count(key)) continue;
+            if (nlocal > 1) cudaSetDevice(comm.device_of(i));
+            cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+            if (e != cudaSuccess) return fail(Result::CudaError, std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(e));
+            attr_done.insert(key);
+        }
+    }
+    int sms = 0;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, comm.device_of(0));
+    // One CTA per SM (160 KiB of stages each); emulated ranks share the GPU.
+    uint32_t resident = static_cast<uint32_t>(std::max(1, sms));
+    if (comm.emulated()) resident = std::max<uint32_t>(1, resident / W);
+    uint32_t ctas = std::min<uint32_t>(resident, N / kGemmDecodeTileN);
+    if (opt.ctas > 0) ctas = std::min<uint32_t>(ctas, opt.ctas);
+    std::string derr;
+    std::vector<GemmDecodeArgs> args(nlocal);
+    for (int i = 0; i < nlocal; ++i) {
+        GemmDecodeArgs& a = args[i];
+        std::memset(&a, 0, sizeof(a));
+        const FusedLinearDesc& d = descs[i];
+        if (nlocal > 1) cudaSetDevice(comm.device_of(i));
+        if (!EncodeTileMap(drv, &a.tmap_a, d.x, T, K, kGemmTileM, &derr) ||
+            !EncodeTileMap(drv, &a.tmap_b, d.w, N, K, kGemmDecodeTileN, &derr))
+            return fail(Result::CudaError, derr);
+        a.cv = comm.View(i);
+        a.residual = d.residual;
+        a.residual_out = d.residual_out;
+        a.norm_weight = d.norm_weight;
+        a.out = d.out;
+        a.T = T;
+        a.N = N;
+        a.K = K;
+        a.eps = opt.eps;
+        a.trace = opt.trace ? opt.trace[i] : nullptr;
+    }
+    if (comm.emulated()) {
+        GemmDecodeEmuArgs* e = new GemmDecodeEmuArgs();
+        std::memset(e, 0, sizeof(*e));
+        for (int i = 0; i < nlocal; ++i) e->r[comm.rank_of(i)] = args[i];
+        cudaStream_t s = streams && streams[0] ? streams[0] : comm.default_stream(0);
+        void* params[] = {e};
+        cudaError_t ce = cudaLaunchCooperativeKernel(fn, dim3(ctas, W), dim3(kGemmDecodeThreads), params, smem, s);
+        delete e;
+        if (ce != cudaSuccess) {
+            (void)cudaGetLastError();
+            return fail(Result::CudaError, std::string("cooperative launch failed: ") + cudaGetErrorString(ce));
+        }
+        comm.CountLaunch(1);
+        return Result::Success;
+    }
+    for (int i = 0; i < nlocal; ++i) {
+        if (nlocal > 1) cudaSetDevice(comm.device_of(i));
+        cudaStream_t s = streams && streams[i] ? streams[i] : comm.default_stream(i);
+        void* params[] = {&args[i]};
+        cudaError_t ce = cudaLaunchKernel(fn, dim3(ctas), dim3(kGemmDecodeThreads), params, smem, s);
+        if (ce != cudaSuccess) {
+            (void)cudaGetLastError();
+            return fail(Result::CudaError, std::string("kernel launch failed: ") + cudaGetErrorString(ce));
+        }
+        comm.CountLaunch(1);
+    }
+    return Result::Success;
+}
+
+bool EncodeTileMap(const DriverApi* d, CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols_k,
                    uint32_t box_rows, std::string* err) {
     const cuuint64_t dims[2] = {cols_k, rows};             // innermost first
     const cuuint64_t strides[1] = {cols_k * 2};            // bytes between rows
@@ -35,6 +118,15 @@ bool EncodeTileMap(const DriverApi* d, CUtensorMap* map, const void* base, uint6
 }  // namespace
 
 uint32_t FusedLinearOneShotMaxRows(int world) { return world <= 2 ? 256u : 32u; }
+
+uint32_t FusedLinearDecodeMaxRows(const HeapLayout& lay, uint32_t N, int world) {
+    if (world < 2 || N == 0 || N % kGemmDecodeTileN != 0 ||
+        N > static_cast<uint32_t>(kGemmDecodeThreads) * kGemmDecodeVecPerThread * 8 || lay.gemm_ll_cap == 0)
+        return 0;
+    // Payload bytes double as flag-in-data lines.
+    const uint64_t rows = lay.gemm_ll_cap / (static_cast<uint64_t>(N) * 4);
+    return static_cast<uint32_t>(std::min<uint64_t>(rows, kGemmDecodeMaxRows));
+}
 
 // Counter targets of one call: every source announces each 128x128 tile once to every owner
 // that has rows in the tile's row block (one-shot: to everybody), and every owner reports the
@@ -93,6 +185,17 @@ Result FusedLinearAllReduceRmsNorm(Communicator& comm, const FusedLinearDesc* de
 
     const HeapLayout& lay = comm.layout();
     const uint64_t row_bytes = static_cast<uint64_t>(N) * 2;
+    {
+        // Few tokens: the latency form (every rank normalises all rows; nothing else to decide).
+        const uint32_t decode_max = FusedLinearDecodeMaxRows(lay, N, W);
+        static const long long decode_env = env::GetInt("YALI_GEMM_DECODE", -1);
+        const int want = opt.decode >= 0 ? opt.decode : static_cast<int>(decode_env);
+        if (want == 1 && T > decode_max)
+            return fail(Result::Unsupported, "the few-token form of the fused linear takes at most " +
+                                                 std::to_string(decode_max) + " rows of this width");
+        if (want != 0 && T <= decode_max && (want == 1 || (opt.force_oneshot != 0 && opt.nvls <= 0)))
+            return LaunchDecode(comm, drv, descs, T, N, K, opt, streams);
+    }
     bool oneshot = opt.force_oneshot >= 0 ? opt.force_oneshot != 0 : T <= FusedLinearOneShotMaxRows(W);
     if (W == 1) oneshot = true;
     // Two-shot writes into every rank's output: those must be addressable from here.

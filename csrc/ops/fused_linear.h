@@ -23,6 +23,9 @@ struct FusedLinearDesc {
 
 struct FusedLinearOptions {
     int force_oneshot = -1;  // -1: by size; 0: two-shot; 1: one-shot
+    // Few-token form (128 x 32 tiles on N/32 CTAs, partial rows as flag-in-data lines, every rank
+    // normalises all rows): -1 by size (T <= FusedLinearDecodeMaxRows), 0 never, 1 required.
+    int decode = -1;
     int ctas = 0;            // 0: as many as are resident
     float eps = 1e-5f;
     // Use of the NVSwitch multicast object by the two-shot form: -1 by measurement, 0 none (peer
@@ -36,6 +39,9 @@ struct FusedLinearOptions {
 Result FusedLinearAllReduceRmsNorm(Communicator& comm, const FusedLinearDesc* descs, uint32_t T, uint32_t N,
                                    uint32_t K, const FusedLinearOptions& opt, const cudaStream_t* streams);
 
+// Largest T the few-token form takes for rows of N elements (limited by its landing zone and by
+// the two TMEM lane quarters its epilogue reads); 0 when it cannot run.
+uint32_t FusedLinearDecodeMaxRows(const HeapLayout& lay, uint32_t N, int world);
 // Rows from which the two-shot form is used when `force_oneshot` is -1.
 uint32_t FusedLinearOneShotMaxRows(int world);
 int FusedLinearAutoMulticastMode(int world, uint32_t T);

@@ -293,7 +293,7 @@ class PyComm {
     void FusedLinear(std::vector<at::Tensor> x, std::vector<at::Tensor> w, std::vector<at::Tensor> norm_weight,
                      std::vector<at::Tensor> out, c10::optional<std::vector<at::Tensor>> residual,
                      c10::optional<std::vector<at::Tensor>> residual_out, double eps, int force_oneshot, int ctas,
-                     c10::optional<std::vector<at::Tensor>> trace, int nvls) {
+                     c10::optional<std::vector<at::Tensor>> trace, int nvls, int decode) {
         at::ScalarType d;
         int64_t n;
         CheckTensors(x, "x", &d, &n);
@@ -330,6 +330,7 @@ class PyComm {
         o.force_oneshot = force_oneshot;
         o.ctas = ctas;
         o.nvls = nvls;
+        o.decode = decode;
         o.eps = static_cast<float>(eps);
         std::vector<unsigned long long*> tr(nl, nullptr);
         if (trace.has_value()) {
@@ -548,7 +549,7 @@ PYBIND11_MODULE(_C, m) {
         .def("fused_linear", &PyComm::FusedLinear, py::arg("x"), py::arg("w"), py::arg("norm_weight"), py::arg("out"),
              py::arg("residual") = py::none(), py::arg("residual_out") = py::none(), py::arg("eps") = 1e-5,
              py::arg("force_oneshot") = -1, py::arg("ctas") = 0, py::arg("trace") = py::none(),
-             py::arg("nvls") = -1)
+             py::arg("nvls") = -1, py::arg("decode") = -1)
         .def("symm_empty", &PyComm::SymmEmpty, py::arg("shape"), py::arg("dtype"))
         .def("symm_reset", &PyComm::SymmReset)
         .def("all_reduce_host", &PyComm::AllReduceHost, py::arg("src"), py::arg("dst"), py::arg("chunk_bytes") = 8 << 20,

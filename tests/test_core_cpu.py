@@ -72,11 +72,11 @@ def test_shard_elems(native_lib):
 
 
 def test_heap_layout(native_lib):
-    f = (ctypes.c_uint64 * 14)()
+    f = (ctypes.c_uint64 * 16)()
     for world in (1, 2, 4, 8):
         assert native_lib.yali_c_heap_layout(world, 0, f) == 0
         total, flags_off, flash_off, flash_cap, ring_off, ring_bytes, nvls_off, nvls_cap, gemm_off, gemm_cap, \
-            user_off, user_bytes, ll_off, ll_cap = list(f)
+            user_off, user_bytes, ll_off, ll_cap, gll_off, gll_cap = list(f)
         assert flags_off == 0 and user_off + user_bytes == total and user_bytes >= 256 * MiB
         if world > 1:
             assert flash_off >= 1 * MiB
@@ -84,14 +84,15 @@ def test_heap_layout(native_lib):
             assert nvls_off == ring_off + ring_bytes
             assert gemm_off == nvls_off + 2 * nvls_cap
             assert ll_off == gemm_off + 2 * world * gemm_cap
-            assert user_off == ll_off + 2 * (world - 1) * 2 * ll_cap
+            assert gll_off == ll_off + 2 * (world - 1) * 2 * ll_cap
+            assert user_off == gll_off + 2 * world * gll_cap and gll_cap >= 64 * 4096 * 4
     assert native_lib.yali_c_heap_layout(8, 1 * MiB, f) != 0  # too small for the fixed regions
     # Every region starts on a 4 KiB boundary for every world size (vector accesses, bulk copies).
     for world in range(1, 9):
         assert native_lib.yali_c_heap_layout(world, 0, f) == 0
         total, flags_off, flash_off, flash_cap, ring_off, ring_bytes, nvls_off, nvls_cap, gemm_off, gemm_cap, \
-            user_off, user_bytes, ll_off, ll_cap = list(f)
-        for off in (flash_off, ring_off, nvls_off, gemm_off, ll_off, user_off, flash_cap, gemm_cap, ll_cap):
+            user_off, user_bytes, ll_off, ll_cap, gll_off, gll_cap = list(f)
+        for off in (flash_off, ring_off, nvls_off, gemm_off, ll_off, gll_off, user_off, flash_cap, gemm_cap, ll_cap):
             assert off % 4096 == 0, (world, off)
 
 

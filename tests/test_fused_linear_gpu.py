@@ -57,6 +57,44 @@ def test_fused_linear_matches_reference(comm, T, oneshot):
         assert torch.equal(o, outs[0])
 
 
+@pytest.mark.parametrize("T", [1, 2, 16, 31, 33, 64])
+def test_few_token_form_matches_reference(comm, T):
+    """T <= 64: 128 x 32 tiles, partial rows to every rank as flag-in-data lines, every rank normalises all rows."""
+    K, N = 512, 4096
+    W = comm.world
+    xs, ws, nw, res = make_layer(W, T, K, N, seed=100 + T)
+    ref, pre = reference(xs, ws, nw, res)
+    res_out = [torch.empty(T, N, dtype=torch.bfloat16, device="cuda") for _ in range(W)]
+    results = []
+    for it in range(5):  # back to back without synchronisation: the two landing parities alternate
+        results.append(comm.fused_linear_rmsnorm(xs, ws, [nw] * W, [res] * W, eps=1e-5, residual_out=res_out, decode=True))
+    comm.sync()
+    for outs in results:
+        for o in outs:
+            torch.testing.assert_close(o.double().cpu(), ref, rtol=3e-2, atol=3e-2)
+        for o in outs[1:]:
+            assert torch.equal(o, outs[0])
+    for q in range(W):
+        torch.testing.assert_close(res_out[q].double().cpu(), pre, rtol=2e-2, atol=2e-2 * W)
+    with pytest.raises(RuntimeError, match="at most"):
+        big = make_layer(W, 65, K, N, seed=1)
+        comm.fused_linear_rmsnorm(big[0], big[1], [big[2]] * W, None, decode=True)
+
+
+def test_few_token_form_other_shapes_and_alternation(comm):
+    W = comm.world
+    for (T, K, N) in [(8, 64, 128), (40, 1024, 2048), (5, 192, 512)]:
+        xs, ws, nw, _ = make_layer(W, T, K, N, seed=K + 1)
+        ref, _ = reference(xs, ws, nw, None)
+        results = []
+        for it in range(6):  # alternate with the tile form (its counters and landing zone are separate)
+            results.append(comm.fused_linear_rmsnorm(xs, ws, [nw] * W, None, decode=bool(it % 2 == 0)))
+        comm.sync()
+        for outs in results:
+            for o in outs:
+                torch.testing.assert_close(o.double().cpu(), ref, rtol=3e-2, atol=3e-2)
+
+
 def test_fused_linear_back_to_back_and_other_shapes(comm):
     W = comm.world
     for (T, K, N) in [(64, 64, 128), (200, 1024, 2048), (33, 192, 512)]:

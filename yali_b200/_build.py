@@ -50,6 +50,7 @@ LIB_SOURCES = [
     "kernels/direct_pipeline.cu",
     "kernels/util_kernels.cu",
     "kernels/gemm_ar_rmsnorm.cu",
+    "kernels/gemm_ar_decode.cu",
     "kernels/no_alloc_entry.cu",
 ]
 

@@ -182,7 +182,7 @@ class Comm:
                              residual: Optional[TensorOrList] = None, *, eps: float = 1e-5,
                              out: Optional[TensorOrList] = None, residual_out: Optional[TensorOrList] = None,
                              oneshot: Optional[bool] = None, ctas: int = 0, trace: Optional[TensorOrList] = None,
-                             nvls: Union[None, bool, int] = None):
+                             nvls: Union[None, bool, int] = None, decode: Optional[bool] = None):
         """out = RMSNorm(residual + sum over ranks of x @ w.T) * norm_weight in ONE kernel per rank
         (tcgen05 GEMM whose epilogue pushes partial rows to their owner over NVLink, then reduce + norm).
         x: [T, K], w: [N, K] (this rank's slice, nn.Linear layout), bf16.  With one GPU per process the
@@ -191,7 +191,9 @@ class Comm:
         tensor(s) of 8 elements that receive CTA 0's %globaltimer at the phase boundaries.  `nvls`: how the
         two-shot form uses the NVSwitch multicast object: None = by measurement, 0/False = not at all
         (peer pushes and peer stores), 1/True = in-switch reduce + multicast store, 2 = peer pushes +
-        multicast store; 1 and 2 need the multicast object and `out` from symm_empty()."""
+        multicast store; 1 and 2 need the multicast object and `out` from symm_empty().  `decode`: the
+        few-token form (up to 64 rows: 128 x 32 tiles on hidden/32 CTAs, partial rows sent to every rank as
+        flag-in-data lines, every rank normalises all rows): None = by size, False = never, True = required."""
         xs, ws, nws = self._as_list(x, "x"), self._as_list(w, "w"), self._as_list(norm_weight, "norm_weight")
         if out is None:
             T, N = xs[0].shape[0], ws[0].shape[0]
@@ -211,7 +213,7 @@ class Comm:
         try:
             tr = None if trace is None else self._as_list(trace, "trace")
             self._impl.fused_linear(xs, ws, nws, outs, res, ro, eps, -1 if oneshot is None else int(oneshot), ctas, tr,
-                                    -1 if nvls is None else int(nvls))
+                                    -1 if nvls is None else int(nvls), -1 if decode is None else int(decode))
         except RuntimeError as e:
             raise _translate(e) from None
         return self._like_input(x, outs)

@@ -11,21 +11,12 @@ Reference parity: the reference has no tensor-parallel layer; its all-reduce is 
 primitive such a layer would call (README.md:9)."""
 from __future__ import annotations
 
-import os
 from typing import List, Optional, Sequence
 
 import torch
 from torch import nn
 
 from ..ops import reference
-
-
-def fused_min_tokens() -> int:
-    """Rows from which the single fused kernel is used.  Measured on 8 x B200 (CUDA-graph replay, Llama-3-8B
-    o_proj shapes): below ~128 rows the library GEMM followed by the one-shot all-reduce + RMSNorm kernel is
-    faster (13.7 vs 22.0 us at T=1, 16.3 vs 24.8 us at T=16), at 128 rows they tie (30.9 vs 31.0 us), at 2048
-    rows the fused kernel wins (90 vs 104 us).  YALI_FUSED_MIN_TOKENS overrides."""
-    return int(os.environ.get("YALI_FUSED_MIN_TOKENS", "128"))
 
 
 class RowParallelLinearNorm(nn.Module):
@@ -48,12 +39,10 @@ class RowParallelLinearNorm(nn.Module):
         x2 = x_local.reshape(-1, shape[-1])
         if x2.is_cuda:
             r2 = None if residual is None else residual.reshape(x2.shape[0], -1)
-            if x2.shape[0] >= fused_min_tokens():
-                y = comm.fused_linear_rmsnorm(x2, self.weight, self.norm_weight, r2, eps=self.eps, out=out,
-                                              residual_out=residual_out)
-            else:  # few rows: library GEMM, then ONE kernel for all-reduce + residual + RMSNorm
-                y = comm.all_reduce_rmsnorm(x2 @ self.weight.T, self.norm_weight, r2, eps=self.eps, out=out,
-                                            residual_out=residual_out)
+            # One kernel per rank for every token count: up to 64 rows the few-token form (hidden/32 CTAs,
+            # flag-in-data pushes), above that the 128 x 128 tile form.  No library GEMM on this path.
+            y = comm.fused_linear_rmsnorm(x2, self.weight, self.norm_weight, r2, eps=self.eps, out=out,
+                                          residual_out=residual_out)
         else:
             part = x2.float() @ self.weight.float().T
             y = comm.all_reduce_rmsnorm(part, self.norm_weight.float(), None if residual is None else
