@@ -27,7 +27,7 @@ $(BIN):
 	mkdir -p $(BIN)
 
 BENCH := $(BIN)/benchmark_yali $(BIN)/benchmark_yali_mpi $(BIN)/p2p_bandwidth
-BENCH_NCCL := $(BIN)/benchmark_nccl $(BIN)/benchmark_nccl_mpi
+BENCH_NCCL := $(BIN)/benchmark_nccl $(BIN)/benchmark_nccl_mpi $(BIN)/nccl_sweep
 bench: $(BENCH) $(BENCH_NCCL)
 $(BIN)/benchmark_yali: bench/benchmark_yali.cu bench/bench_common.h $(HDRS) $(LIB) | $(BIN)
 	$(NVCC) $(NVFLAGS) $< -o $@ $(LINK)
@@ -38,6 +38,8 @@ $(BIN)/p2p_bandwidth: bench/p2p_bandwidth.cu | $(BIN)
 $(BIN)/benchmark_nccl: bench/benchmark_nccl.cu bench/bench_common.h $(HDRS) $(LIB) | $(BIN)
 	$(NVCC) $(NVFLAGS) $< -o $@ $(LINK) -lnccl
 $(BIN)/benchmark_nccl_mpi: bench/benchmark_nccl_mpi.cu bench/bench_common.h $(HDRS) $(LIB) | $(BIN)
+	$(NVCC) $(NVFLAGS) $< -o $@ $(LINK) -lnccl
+$(BIN)/nccl_sweep: bench/nccl_sweep.cu $(HDRS) $(LIB) | $(BIN)
 	$(NVCC) $(NVFLAGS) $< -o $@ $(LINK) -lnccl
 
 EXAMPLES := $(BIN)/example_simple $(BIN)/example_multilane $(BIN)/example_simple_mpi $(BIN)/example_multilane_mpi \

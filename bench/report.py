@@ -4,8 +4,8 @@ run-level statistics and a markdown summary with the speed-up over NCCL per size
 
     python bench/report.py --out report_dir run1.jsonl [run2.jsonl ...]
 
-Reference counterpart: the CSV / summary.md / index.md phases of scripts/sweep.py (654-680, 1501-1891).
-The reference's PNG graphs need matplotlib, which is not a dependency here; the CSVs carry the same columns."""
+Reference counterpart: the CSV / summary.md / graph phases of scripts/sweep.py (654-680, 702-1193,
+1501-1798).  The charts are SVG files written by bench/plots.py (no plotting dependency)."""
 from __future__ import annotations
 
 import argparse
@@ -15,6 +15,7 @@ import sys
 from collections import defaultdict
 from pathlib import Path
 
+sys.path.insert(0, str(Path(__file__).resolve().parent))
 sys.path.insert(0, str(Path(__file__).resolve().parent.parent))
 from yali_b200.utils.stats import summarise  # noqa: E402
 
@@ -38,6 +39,7 @@ def main() -> None:
     out.mkdir(parents=True, exist_ok=True)
     samples = defaultdict(list)  # (impl, world, dtype, variant, bytes) -> [busbw per run]
     times = defaultdict(list)
+    tails = defaultdict(list)  # device-timed p99 / p50 per call
     for run in args.runs:
         for line in Path(run).read_text().splitlines():
             if not line.startswith("{"):
@@ -46,6 +48,8 @@ def main() -> None:
             key = (r["impl"], r["world"], r["dtype"], r["variant"], r["bytes"])
             samples[key].append(r["busbw_gbps"])
             times[key].append(r["us"])
+            if r.get("dev_p50_us"):
+                tails[key].append(r["dev_p99_us"] / r["dev_p50_us"])
     by_file = defaultdict(list)
     for (impl, world, dtype, variant, nbytes), vals in sorted(samples.items()):
         st = summarise(vals)
@@ -69,21 +73,28 @@ def main() -> None:
     for world in worlds:
         for dtype in sorted({k[2] for k in samples if k[1] == world}):
             lines += [f"## {world} ranks, {dtype}", "",
-                      "| size | auto | flash | stream | nvls | NCCL | auto / NCCL | auto % of measured link |",
-                      "|---|---|---|---|---|---|---|---|"]
+                      "| size | auto | flash | stream | nvls | stream_direct | NCCL | auto / NCCL | auto % of measured link | "
+                      "auto p99/p50 (device) |",
+                      "|---|---|---|---|---|---|---|---|---|---|"]
             sizes = sorted({k[4] for k in samples if k[1] == world and k[2] == dtype})
             for b in sizes:
                 def g(impl, variant):
                     v = samples.get((impl, world, dtype, variant, b))
                     return sum(v) / len(v) if v else None
-                cells = [g("yali_b200", v) for v in ("auto", "flash", "stream", "nvls")] + [g("nccl", "nccl")]
-                ratio = f"{cells[0] / cells[4]:.2f}x" if cells[0] and cells[4] else "-"
+                cells = [g("yali_b200", v) for v in ("auto", "flash", "stream", "nvls", "stream_direct")] + [g("nccl", "nccl")]
+                ratio = f"{cells[0] / cells[5]:.2f}x" if cells[0] and cells[5] else "-"
                 sol = f"{100 * cells[0] / LINK_MEASURED_GBS:.0f} %" if cells[0] else "-"
+                tl = tails.get(("yali_b200", world, dtype, "auto", b))
+                tail = f"{sum(tl) / len(tl):.2f}" if tl else "-"
                 lines.append("| " + human(b) + " | " + " | ".join("-" if c is None else f"{c:.1f}" for c in cells) +
-                             f" | {ratio} | {sol} |")
+                             f" | {ratio} | {sol} | {tail} |")
             lines.append("")
+    from plots import make_all  # bench/plots.py
+    charts = make_all(args.runs, out, LINK_MEASURED_GBS)
+    if charts:
+        lines += ["## Charts", ""] + [f"![{c}]({c})" for c in charts] + [""]
     (out / "summary.md").write_text("\n".join(lines))
-    print(f"wrote {out}/summary.md and {len(by_file)} CSV file(s)")
+    print(f"wrote {out}/summary.md, {len(by_file)} CSV file(s) and {len(charts)} chart(s)")
 
 
 if __name__ == "__main__":

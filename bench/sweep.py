@@ -2,14 +2,20 @@
 """Size sweep of the all-reduce variants against NCCL on the same GPUs.
 
     python -m torch.distributed.run --nproc-per-node N --master-addr 127.0.0.1 bench/sweep.py \
-        [--min-bytes 4096] [--max-bytes 2147483648] [--dtypes fp32,bf16] [--variants auto,flash,stream,nvls] \
-        [--nccl] [--out sweep.jsonl] [--tuning-out tuning.json]
+        [--min-bytes 4096] [--max-bytes 2147483648] [--dtypes fp32,bf16] \
+        [--variants auto,flash,stream,nvls,stream_direct] [--torch-nccl] [--out sweep.jsonl] [--tuning-out tuning.json]
 
 Every (size, dtype, variant) is timed on the device (CUDA events around the timed
 calls on the launching stream, 20 warm-up calls, barrier + synchronize on both
 sides, max over ranks) and reported as NCCL-convention bus bandwidth; small
-messages rotate over buffers that together exceed L2.  `--nccl` times
-torch.distributed.all_reduce (backend nccl) with the same loop as the baseline.
+messages rotate over buffers that together exceed L2.  Every row also carries the
+device-side timeline of the timed calls (the kernels stamp their own start and end):
+p50 / p99 / max of the time per call without host jitter, call by call the max over
+ranks.  The NCCL baseline of a campaign comes from build/bin/nccl_sweep (same timing
+code in C++, started by bench/run_sweep.py); `--torch-nccl` additionally times
+torch.distributed.all_reduce with this file's loop (rows of impl "nccl_torch": the
+Python binding of NCCL costs several microseconds per call inside a CUDA graph, so
+these rows are context, not the baseline).
 `--tuning-out` writes the fastest variant per size as a table the library loads
 through YALI_TUNING_FILE.
 
@@ -73,13 +79,33 @@ def timed(comm, fn, iters: int, warmup: int, graph: bool = False) -> float:
     return gather_max(comm, e0.elapsed_time(e1) * 1e3 / iters)
 
 
+def device_times(comm, iters: int) -> dict:
+    """p50 / p99 / max microseconds of the last `iters` traced calls (first CTA in -> last CTA out), call by
+    call the max over ranks."""
+    n = min(iters, 4096)
+    dur = [0.0] * n
+    for li in range(comm.nlocal):
+        _calls, entries = comm.read_trace(li, n)
+        if len(entries) != n:
+            return {}
+        for c, (t0, t1) in enumerate(entries):
+            dur[c] = max(dur[c], (t1 - t0) * 1e-3)
+    if comm.nlocal == 1 and comm.world > 1:
+        for p in comm.allgather_object_bytes(struct.pack(f"{n}d", *dur)):
+            dur = [max(x, y) for x, y in zip(dur, struct.unpack(f"{n}d", p))]
+    s = sorted(dur)
+    pick = (lambda q: s[min(n - 1, int(round(q * (n - 1))))])
+    return {"dev_p50_us": round(pick(0.5), 2), "dev_p99_us": round(pick(0.99), 2), "dev_max_us": round(s[-1], 2),
+            "dev_samples": n}
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--min-bytes", type=int, default=4096)
     ap.add_argument("--max-bytes", type=int, default=1 << 30)
     ap.add_argument("--dtypes", default="fp32")
-    ap.add_argument("--variants", default="auto,flash,stream,nvls")
-    ap.add_argument("--nccl", action="store_true")
+    ap.add_argument("--variants", default="auto,flash,stream,nvls,stream_direct")
+    ap.add_argument("--torch-nccl", dest="nccl", action="store_true")
     ap.add_argument("--emulate", type=int, default=0, help="emulate this many ranks on one GPU (no launcher)")
     ap.add_argument("--out", default="")
     ap.add_argument("--tuning-out", default="")
@@ -125,9 +151,12 @@ def main() -> None:
                 def call(i, var=var):
                     comm.all_reduce(pick(views_s[i % nbuf]), pick(views_r[i % nbuf]), mode=var)
                 try:
+                    comm.set_trace(True)
                     us = timed(comm, call, iters, 20 if size <= (16 << 20) else 5, graph=size <= args.graph_max_bytes)
+                    comm.set_trace(False)
                     comm.check()
                 except RuntimeError as e:
+                    comm.set_trace(False)
                     if "cannot run" in str(e) or "Unsupported" in str(e):
                         continue
                     raise
@@ -136,6 +165,7 @@ def main() -> None:
                        "kernel": lc["variant"], "ctas": lc["ctas"], "slot_bytes": lc["slot_bytes"], "us": round(us, 2),
                        "busbw_gbps": round(size * factor / us / 1e3, 2), "emulated": emu,
                        "timing": "graph" if size <= args.graph_max_bytes else "events"}
+                row.update(device_times(comm, iters))
                 rows.append(row)
                 if var != "auto":
                     key = (dname, size)
@@ -152,7 +182,7 @@ def main() -> None:
                 def ncall(i):
                     dist.all_reduce(bufs[i % len(bufs)])
                 us = timed(comm, ncall, iters, 20 if size <= (16 << 20) else 5, graph=size <= args.graph_max_bytes)
-                row = {"impl": "nccl", "world": world, "dtype": dname, "bytes": size, "variant": "nccl",
+                row = {"impl": "nccl_torch", "world": world, "dtype": dname, "bytes": size, "variant": "nccl_torch",
                        "us": round(us, 2), "busbw_gbps": round(size * factor / us / 1e3, 2),
                        "timing": "graph" if size <= args.graph_max_bytes else "events"}
                 if rank == 0:
@@ -164,7 +194,7 @@ def main() -> None:
     if args.tuning_out and rank == 0:
         trows = []
         for (dname, size), row in sorted(best.items(), key=lambda kv: (kv[0][0], kv[0][1])):
-            name = {"flash": "flash", "stream": "stream", "nvls1": "nvls1", "nvls2": "nvls2"}[row["kernel"]]
+            name = row["kernel"]  # flash, stream, nvls1, nvls2, flash_pull, stream_direct: the planner's names
             trows.append({"world": world, "elem_bytes": 4 if dname == "fp32" else 2, "max_bytes": size,
                           "variant": name, "ctas": 0, "slot_bytes": 0, "busbw": row["busbw_gbps"]})
         Path(args.tuning_out).write_text(json.dumps({"rows": trows}, indent=1))

@@ -498,11 +498,15 @@ Result Communicator::Collective(const void* const* send, void* const* recv, uint
     // and are advanced by the kernels; the host keeps no per-call state.
     plan.flags |= extra_flags;
     if (trace_) plan.flags |= kFlagTrace;
-    // Only the staged one-shot kernel may treat alignment as a per-rank property: its CTA slices do
-    // not depend on it, and a rank touches nothing but its own buffers and the (aligned) staging.
-    // Every other kernel uses the flag all local ranks share: the ring kernel's direct all-gather
-    // and the pipelined kernels store 16-byte vectors into the peers' outputs.
-    const bool per_rank_alignment = plan.variant == Variant::Flash && !(plan.flags & kFlagLowLatency);
+    // The staged kernels (one-shot incl. flag-in-data, ring without direct all-gather, staged NVLS)
+    // treat alignment as a per-rank property: their partition of the message does not depend on it
+    // and a rank touches nothing but its own buffers and the (aligned) staging.  The ring kernel's
+    // direct all-gather and the pipelined kernels store 16-byte vectors into the peers' outputs and
+    // use the flag all local ranks share.
+    const bool per_rank_alignment =
+        plan.variant == Variant::Flash ||
+        ((plan.variant == Variant::NvlsOneShot || plan.variant == Variant::NvlsTwoShot) && !(plan.flags & kFlagSymmetric)) ||
+        (plan.variant == Variant::Stream && !(plan.flags & kFlagDirectAg));
     for (int i = 0; i < nlocal(); ++i) {
         CollArgs& a = args[i];
         a.cv = View(i);

@@ -291,7 +291,11 @@ __device__ __forceinline__ void flash_ll_body(const CollArgs& a, uint32_t cta) {
     const uint32_t parity = lo & 1u;
     const uint64_t deadline = ptx::globaltimer() + cv.timeout_ns;
 
-    const uint64_t nvec = a.count / VEC;  // the planner only picks this form for whole, aligned vectors
+    const uint64_t nvec = a.count / VEC;  // the planner only picks this form for whole vectors
+    // This rank's own buffers may be aligned to their element type only (kFlagVecOk is a per-rank
+    // property here): then they are read and written element by element; the lines on the wire and
+    // the CTA slices are the same either way.
+    const bool aligned = (a.flags & kFlagVecOk) != 0;
     const uint64_t per = (nvec + a.ctas - 1) / a.ctas;
     const uint64_t vb = min(nvec, static_cast<uint64_t>(cta) * per), ve = min(nvec, vb + per);
     const char* src = static_cast<const char*>(a.send);
@@ -305,7 +309,7 @@ __device__ __forceinline__ void flash_ll_body(const CollArgs& a, uint32_t cta) {
 
     // ---- push: payload vector v becomes lines 2v and 2v+1
     for (uint64_t v = vb + tid; v < ve; v += nt) {
-        const uint4 x = *reinterpret_cast<const uint4*>(src + v * 16);
+        const uint4 x = aligned ? *reinterpret_cast<const uint4*>(src + v * 16) : load16_elems<T>(src, v);
         const uint4 l0 = make_uint4(x.x, lo, x.y, hi), l1 = make_uint4(x.z, lo, x.w, hi);
 #pragma unroll
         for (int k = 0; k < kMaxPeers; ++k) {
@@ -327,7 +331,7 @@ __device__ __forceinline__ void flash_ll_body(const CollArgs& a, uint32_t cta) {
         for (int q = 0; q < kMaxW; ++q) {
             if (q >= W) continue;
             if (q == r) {
-                accumulate<T>(f, *reinterpret_cast<const uint4*>(src + v * 16));
+                accumulate<T>(f, aligned ? *reinterpret_cast<const uint4*>(src + v * 16) : load16_elems<T>(src, v));
                 continue;
             }
             uint4 l0, l1;
@@ -348,7 +352,8 @@ __device__ __forceinline__ void flash_ll_body(const CollArgs& a, uint32_t cta) {
         if (timed_out) break;
 #pragma unroll
         for (int i = 0; i < VEC; ++i) f[i] = epi(f[i]);
-        store_lanes<T, VEC>(out + v * VEC, f);
+        if (aligned) store_lanes<T, VEC>(out + v * VEC, f);
+        else store16_elems<T>(out, v, pack16<T>(f));
     }
     if (__syncthreads_or(timed_out ? 1 : 0)) return;
     if (tid == 0 && check_out_last(cv, 0, a.ctas)) {

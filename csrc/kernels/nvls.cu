@@ -51,9 +51,21 @@ __device__ __forceinline__ uint4 scale16(const uint4& v, float s) {
     return pack16<T>(f);
 }
 
-__device__ __forceinline__ void copy16(char* dst, const char* src, uint64_t vb, uint64_t ve) {
+// `aligned` false: the user buffer (whichever side it is) is aligned to its element type only.
+template <typename T>
+__device__ __forceinline__ void copy16(char* dst, const char* src, uint64_t vb, uint64_t ve, bool aligned) {
     const int tid = threadIdx.x, nt = blockDim.x;
     uint64_t v = vb + tid;
+    if (!aligned) {
+        constexpr int VEC = 16 / sizeof(T);
+        for (; v < ve; v += nt) {
+            const T* s = reinterpret_cast<const T*>(src) + v * VEC;
+            T* d = reinterpret_cast<T*>(dst) + v * VEC;
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) d[i] = s[i];
+        }
+        return;
+    }
     for (; v + 3ull * nt < ve; v += 4ull * nt) {
         uint4 x[4];
 #pragma unroll
@@ -70,7 +82,7 @@ __device__ __forceinline__ void copy16(char* dst, const char* src, uint64_t vb, 
 // U loads are in flight per thread before the first store.
 template <typename T, int U, bool BROADCAST>
 __device__ __forceinline__ void reduce_range(const char* mc_in, char* out, uint64_t vb, uint64_t ve, float scale,
-                                             bool scaled) {
+                                             bool scaled, bool out_aligned = true) {
     const int tid = threadIdx.x, nt = blockDim.x;
     uint64_t v = vb + tid;
     for (; v + static_cast<uint64_t>(U - 1) * nt < ve; v += static_cast<uint64_t>(U) * nt) {
@@ -81,19 +93,22 @@ __device__ __forceinline__ void reduce_range(const char* mc_in, char* out, uint6
         for (int u = 0; u < U; ++u) {
             const uint4 y = scaled ? scale16<T>(x[u], scale) : x[u];
             if (BROADCAST) ptx::multimem_st_v4(out + (v + u * nt) * 16, y);
-            else ptx::st_v4(out + (v + u * nt) * 16, y);
+            else if (out_aligned) ptx::st_v4(out + (v + u * nt) * 16, y);
+            else store16_elems<T>(out, v + u * nt, y);
         }
     }
     for (; v < ve; v += nt) {
         const uint4 x = mc_ld_reduce<T>(mc_in + v * 16);
         const uint4 y = scaled ? scale16<T>(x, scale) : x;
         if (BROADCAST) ptx::multimem_st_v4(out + v * 16, y);
-        else ptx::st_v4(out + v * 16, y);
+        else if (out_aligned) ptx::st_v4(out + v * 16, y);
+        else store16_elems<T>(out, v, y);
     }
 }
 
-// count*sizeof(T) is a multiple of 16 and all buffers are 16-byte aligned (the
-// dispatcher falls back to the peer-to-peer kernels otherwise).
+// count*sizeof(T) is a multiple of 16 (the dispatcher falls back to the peer-to-peer kernels
+// otherwise).  Symmetric buffers are 16-byte aligned on every rank; staged user buffers may be
+// aligned to their element type only on some ranks (kFlagVecOk clear there).
 template <typename T, bool TWO_SHOT>
 __global__ void __launch_bounds__(kNvlsThreads, 2) nvls_kernel(const __grid_constant__ CollArgs a) {
     constexpr int VEC = TypeTraits<T>::kVec;
@@ -110,6 +125,7 @@ __global__ void __launch_bounds__(kNvlsThreads, 2) nvls_kernel(const __grid_cons
     const uint64_t deadline = ptx::globaltimer() + cv.timeout_ns;
 
     const bool symmetric = (a.flags & kFlagSymmetric) != 0;
+    const bool aligned = (a.flags & kFlagVecOk) != 0;  // per rank: only the staging copies look at it
     const uint32_t parity = (epoch >> 1) & 1u;
     const uint64_t total_vec = a.count / VEC;
     const float scale = a.ep.scale;
@@ -126,11 +142,11 @@ __global__ void __launch_bounds__(kNvlsThreads, 2) nvls_kernel(const __grid_cons
     if constexpr (!TWO_SHOT) {
         const uint64_t per = (total_vec + nctas - 1) / nctas;
         const uint64_t vb = min(total_vec, cta * per), ve = min(total_vec, vb + per);
-        if (!symmetric) copy16(heap + stage_off, send, vb, ve);
+        if (!symmetric) copy16<T>(heap + stage_off, send, vb, ve, aligned);
         if (!cta_barrier_all_ranks(cv, cta, epoch + 1, deadline, &s_abort)) return;
         const char* mc_in = cv.mc_heap + in_off;
-        if (a.stages == 8) reduce_range<T, 8, false>(mc_in, recv, vb, ve, scale, scaled);
-        else reduce_range<T, 4, false>(mc_in, recv, vb, ve, scale, scaled);
+        if (a.stages == 8) reduce_range<T, 8, false>(mc_in, recv, vb, ve, scale, scaled, aligned);
+        else reduce_range<T, 4, false>(mc_in, recv, vb, ve, scale, scaled, aligned);
         // In-place user buffers may be overwritten by their owner right after this
         // kernel, so nobody leaves before everybody has read.  Staged input sits in
         // the half of the staging region that is not touched again before every
@@ -150,7 +166,7 @@ __global__ void __launch_bounds__(kNvlsThreads, 2) nvls_kernel(const __grid_cons
             for (int k = 0; k < W; ++k) {
                 uint64_t vb, ve;
                 slice((r + k) % W, &vb, &ve);
-                copy16(heap + stage_off, send, vb, ve);
+                copy16<T>(heap + stage_off, send, vb, ve, aligned);
             }
         }
         if (!cta_barrier_all_ranks(cv, cta, epoch + 1, deadline, &s_abort)) return;
@@ -178,7 +194,7 @@ __global__ void __launch_bounds__(kNvlsThreads, 2) nvls_kernel(const __grid_cons
             for (int k = 0; k < W; ++k) {
                 uint64_t vb, ve;
                 slice((r + k) % W, &vb, &ve);
-                copy16(recv, heap + stage_off, vb, ve);
+                copy16<T>(recv, heap + stage_off, vb, ve, aligned);
             }
         }
     }

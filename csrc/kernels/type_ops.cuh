@@ -138,6 +138,28 @@ __device__ __forceinline__ void store_lanes(Tout* p, const float* f) {
     }
 }
 
+// 16 bytes at p + 16*v of a buffer that is only aligned to its element type T: assembled from
+// element loads / written with element stores.  The slow path of ranks whose buffers are not
+// 16-byte aligned; their peers never notice, because the data on the wire is laid out the same.
+template <typename T>
+__device__ __forceinline__ uint4 load16_elems(const void* base, uint64_t v) {
+    constexpr int VEC = 16 / sizeof(T);
+    const T* p = static_cast<const T*>(base) + v * VEC;
+    uint4 r;
+    T* o = reinterpret_cast<T*>(&r);
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) o[i] = p[i];
+    return r;
+}
+template <typename T>
+__device__ __forceinline__ void store16_elems(void* base, uint64_t v, const uint4& x) {
+    constexpr int VEC = 16 / sizeof(T);
+    T* p = static_cast<T*>(base) + v * VEC;
+    const T* i_ = reinterpret_cast<const T*>(&x);
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) p[i] = i_[i];
+}
+
 // ---- epilogue functors: applied to the fp32 sum before it is stored ----
 struct EpiIdentity {
     static constexpr int kKind = kEpiIdentity;

@@ -279,8 +279,13 @@ Result MakePlan(int world, uint64_t count, Dtype in, Dtype out, int epilogue, Ke
     const bool rows = epilogue == kEpiResidualRmsNorm;
     const bool flash_ok = bytes <= caps.flash_cap || world == 1;
     const bool stream_ok = !rows && world > 1 && caps.ring_bytes > 0;
-    const bool nvls_ok = !rows && world > 1 && caps.has_multicast && in == out && caps.vec_ok &&
-                         (bytes % 16 == 0) && (caps.symmetric || bytes <= caps.nvls_cap);
+    // A rank's own alignment must not influence which kernel runs: with one GPU per process it is a
+    // local fact, and ranks that chose differently would wait for each other until the deadline.  The
+    // staged forms (one-shot, flag-in-data, ring, staged NVLS) therefore cope with buffers that are
+    // aligned to their element type only; alignment matters for the plan only where all ranks share
+    // it (symmetric buffers sit at one heap offset everywhere, ranks of one process are all known).
+    const bool nvls_ok = !rows && world > 1 && caps.has_multicast && in == out && (bytes % 16 == 0) &&
+                         (caps.symmetric ? caps.vec_ok : bytes <= caps.nvls_cap);
     // The pipelined kernels read every rank's input and (two-shot) write every rank's output in
     // place: all of them must be addressable and 16-byte aligned.  The one-shot pull overwrites
     // its output while peers may still read their inputs, so it cannot run in place.
@@ -350,7 +355,7 @@ Result MakePlan(int world, uint64_t count, Dtype in, Dtype out, int epilogue, Ke
             if (dev_ctas > 0) c = dev_ctas;
             // Small messages of equal in/out type take the flag-in-data form (twice the bytes on
             // the wire, but no flag round trip).
-            if (!rows && world > 1 && in == out && caps.vec_ok && bytes % 16 == 0 && bytes <= caps.ll_cap &&
+            if (!rows && world > 1 && in == out && bytes % 16 == 0 && bytes <= caps.ll_cap &&
                 bytes <= LowLatencyMaxBytes(world)) {
                 p.flags |= kFlagLowLatency;
                 if (!(row && row->ctas) && dev_ctas <= 0)

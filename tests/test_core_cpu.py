@@ -129,6 +129,20 @@ def test_plan_pipelined_variants_need_addressable_buffers(native_lib):
     assert rc == 0 and p.variant == 3
 
 
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_plan_of_staged_variants_ignores_local_alignment(native_lib, world):
+    """With one GPU per process a rank's alignment is a local fact: two ranks must reach the same plan
+    whether or not their own buffers are 16-byte aligned (symmetric buffers share their alignment)."""
+    for count in (4, 1024, 65536, 1 << 20, 1 << 24, (1 << 26) + 4):
+        for mc in (0, 1):
+            plans = []
+            for vec_ok in (0, 1):
+                rc, p, _ = make_plan(native_lib, world, count, cp=caps(world, has_multicast=mc, vec_ok=vec_ok))
+                assert rc == 0
+                plans.append((p.variant, p.ctas, p.slot_bytes, p.shard_elems, p.stages, p.flags & ~1))
+            assert plans[0] == plans[1], (count, mc, plans)
+
+
 def test_plan_auto_selection(native_lib):
     lib = native_lib
     rc, p, _ = make_plan(lib, 2, 262144)  # 1 MiB fp32 at two ranks: one-shot
@@ -147,7 +161,9 @@ def test_plan_auto_selection(native_lib):
     rc, p, _ = make_plan(lib, 8, 32768, cp=caps(8, has_multicast=1, symmetric=0))
     assert rc == 0 and p.variant == 0  # plain buffers stay with the peer-to-peer one-shot
     rc, p, _ = make_plan(lib, 8, 1024, cp=caps(8, vec_ok=0))
-    assert rc == 0 and not p.flags & 64  # needs aligned buffers
+    assert rc == 0 and p.flags & 64  # a rank's own alignment never changes the plan (its peers cannot know it)
+    rc, p2, _ = make_plan(lib, 8, 1024, cp=caps(8, vec_ok=1))
+    assert (p.variant, p.ctas, p.flags & ~1) == (p2.variant, p2.ctas, p2.flags & ~1)
 
 
 def test_plan_forced_modes_and_errors(native_lib):

@@ -143,7 +143,7 @@ def test_only_one_rank_misaligned(comm, mode, dtype):
     """Rank 1 passes buffers one element off a 16-byte boundary, the others aligned ones: all
     ranks must still cut the message into the same pieces."""
     ext = _native.ext()
-    for n in (40001, 10007):
+    for n in (40001, 10007, 4096):  # 4096: whole vectors, so small enough for the flag-in-data form
         xs, outs = [], []
         for r in range(comm.world):
             off = 1 if r == 1 else 0

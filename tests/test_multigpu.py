@@ -47,7 +47,7 @@ def _check(outs, in_dtype, world, dist=0, seed=1234, scale=1.0):
 def test_single_process_all_variants(world):
     with yali.Comm.single_process(list(range(world)), heap_bytes=2 << 30) as comm:
         assert comm.world == world and comm.nlocal == world
-        modes = ["flash", "stream"] + (["nvls"] if comm.has_multicast else [])
+        modes = ["flash", "stream", "flash_pull", "stream_direct", "auto"] + (["nvls"] if comm.has_multicast else [])
         for dtype in (torch.float32, torch.bfloat16, torch.float16):
             for n in (1, 33, 4099, 262144, (1 << 21) + 16):
                 xs = [torch.empty(n, dtype=dtype, device=f"cuda:{d}") for d in range(world)]
@@ -69,10 +69,30 @@ def test_single_process_all_variants(world):
                 comm.all_reduce(send, recv, mode=mode)
             comm.sync()
             _check(recv, torch.bfloat16, world, dist=1)
-        # in place on symmetric memory
-        comm.all_reduce(send, send, mode=modes[-1])
+        # in place on symmetric memory: the pipelined two-shot, then (fresh data) a small message through
+        # the switch, where the planner must avoid the one-shot form (it would overwrite operands of
+        # the peers' multimem.ld_reduce)
+        comm.all_reduce(send, send, mode="stream_direct")
         comm.sync()
         _check(send, torch.bfloat16, world, dist=1)
+        if comm.has_multicast:
+            small = [t[:32768] for t in send]  # 64 KiB
+            _fill(small, dist=1, seed=4242)
+            comm.all_reduce(small, small, mode="nvls")
+            comm.sync()
+            assert comm.last_call()["variant"] == "nvls2"
+            _check([t.clone() for t in small], torch.bfloat16, world, dist=1, seed=4242)
+        # one rank's buffers one element off a 16-byte boundary (cudaMalloc memory, all variants by size)
+        for n in (4096, 100001, 1 << 20):
+            xs, outs = [], []
+            for d in range(world):
+                off = 1 if d == 1 else 0
+                xs.append(torch.empty(n + 8, dtype=torch.float32, device=f"cuda:{d}")[off:off + n])
+                outs.append(torch.empty(n + 8, dtype=torch.float32, device=f"cuda:{d}")[off:off + n])
+            _fill(xs, seed=777)
+            comm.all_reduce(xs, outs)
+            comm.sync()
+            _check([o.clone() for o in outs], torch.float32, world, seed=777)
         # fused row epilogue across real GPUs
         rows, hidden = 16, 4096
         xs = [torch.empty(rows, hidden, dtype=torch.bfloat16, device=f"cuda:{d}") for d in range(world)]
@@ -112,10 +132,21 @@ def _rank_main(rank, world, port, q, scenario):
                         y = comm.all_reduce(x, mode=mode)
                         comm.sync()
                         ok &= ext.validate_sum(y, dtype, 0, 1234, world)["mismatches"] == 0
+            # Rank 1 alone passes buffers one element off a 16-byte boundary: every rank must still pick
+            # the same kernel and the sums must be right (sizes for the flag-in-data form, the flagged
+            # one-shot, and the ring / staged in-switch kernels).
+            for n in (4096, 100001, 1 << 22):
+                off = 1 if rank == 1 else 0
+                x = torch.empty(n + 8, dtype=torch.float32, device=dev)[off:off + n]
+                y = torch.empty(n + 8, dtype=torch.float32, device=dev)[off:off + n]
+                ext.fill_random(x, 0, 555 + rank)
+                comm.all_reduce(x, y)
+                comm.sync()
+                ok &= ext.validate_sum(y.clone(), torch.float32, 0, 555, world)["mismatches"] == 0
             n = 1 << 20
             s, r = comm.symm_empty(n, torch.float32), comm.symm_empty(n, torch.float32)
             ext.fill_random(s, 1, 99 + rank)
-            for mode in modes:
+            for mode in modes + ["flash_pull", "stream_direct", "auto"]:
                 for _ in range(4):
                     comm.all_reduce(s, r, mode=mode)
                 comm.sync()
@@ -128,7 +159,7 @@ def _rank_main(rank, world, port, q, scenario):
             # Row-parallel GEMM + all-reduce + residual + RMSNorm in one kernel per rank: the push
             # forms and (with a multicast object) the in-switch form against an fp32 reference.
             N, K = 1024, 256
-            for T in (1, 100, 300, 1000):
+            for T in (1, 16, 100, 300, 1000):
                 gens = [torch.Generator().manual_seed(4321 + 17 * q + T) for q in range(world)]
                 xs = [torch.randn(T, K, generator=g).to(torch.bfloat16) for g in gens]
                 ws = [(torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16) for g in gens]
@@ -137,8 +168,10 @@ def _rank_main(rank, world, port, q, scenario):
                 h = sum(x.float() @ w.float().T for x, w in zip(xs, ws)) + res.float()
                 want = h * torch.rsqrt(h.pow(2).mean(-1, keepdim=True) + 1e-5) * nw.float()
                 x, w = xs[rank].to(dev), ws[rank].to(dev)
-                forms = [(True, 0), (False, 0)] + ([(False, 1), (False, 2)] if comm.has_multicast else [])
-                for oneshot, nvls in forms:
+                forms = [(True, 0, False), (False, 0, False)] + \
+                    ([(False, 1, False), (False, 2, False)] if comm.has_multicast else []) + \
+                    ([(None, None, True)] if T <= 64 else [])  # the few-token form
+                for oneshot, nvls, decode in forms:
                     out = comm.symm_empty([T, N], torch.bfloat16)
                     ro = comm.symm_empty([T, N], torch.bfloat16)
                     for _ in range(3):  # both call parities, and a repeat
@@ -146,13 +179,13 @@ def _rank_main(rank, world, port, q, scenario):
                         comm.sync()
                         comm.barrier()
                         comm.fused_linear_rmsnorm(x, w, nw.to(dev), res.to(dev), out=out, residual_out=ro,
-                                                  oneshot=oneshot, nvls=nvls)
+                                                  oneshot=oneshot, nvls=nvls, decode=decode)
                         comm.sync()
                         err = (out.float().cpu() - want).abs().max().item()
                         err_h = (ro.float().cpu() - h).abs().max().item()
                         good = err < 0.08 and err_h < 0.06 * max(1.0, h.abs().max().item())
                         if not good:
-                            info[f"T{T}_one{int(oneshot)}_nvls{int(nvls)}"] = (err, err_h)
+                            info[f"T{T}_one{oneshot}_nvls{nvls}_decode{decode}"] = (err, err_h)
                         ok &= good
                         comm.barrier()  # nobody clears `out` while a peer still writes rows into it
                 comm.symm_reset()

@@ -24,7 +24,8 @@ def test_report_from_sweep_lines(tmp_path):
     for size, y, n in [(4096, 0.5, 0.2), (1 << 20, 90.0, 56.0), (1 << 30, 670.0, 566.0)]:
         for var in ("auto", "flash"):
             rows.append({"impl": "yali_b200", "world": 2, "dtype": "fp32", "bytes": size, "variant": var,
-                         "kernel": "flash", "ctas": 8, "slot_bytes": 0, "us": size / y / 1e3, "busbw_gbps": y})
+                         "kernel": "flash", "ctas": 8, "slot_bytes": 0, "us": size / y / 1e3, "busbw_gbps": y,
+                         "dev_p50_us": 10.0, "dev_p99_us": 10.5, "dev_max_us": 12.0, "dev_samples": 200})
         rows.append({"impl": "nccl", "world": 2, "dtype": "fp32", "bytes": size, "variant": "nccl", "us": size / n / 1e3,
                      "busbw_gbps": n})
     run = tmp_path / "run.jsonl"
@@ -32,9 +33,26 @@ def test_report_from_sweep_lines(tmp_path):
     out = tmp_path / "rep"
     subprocess.run([sys.executable, str(ROOT / "bench" / "report.py"), "--out", str(out), str(run), str(run)], check=True)
     summary = (out / "summary.md").read_text()
-    assert "| 1M | 90.0 | 90.0 | - | - | 56.0 | 1.61x |" in summary and "## 2 ranks, fp32" in summary
+    assert "| 1M | 90.0 | 90.0 | - | - | - | 56.0 | 1.61x | 12 % | 1.05 |" in summary and "## 2 ranks, fp32" in summary
     csv_text = (out / "yali_b200_w2_fp32.csv").read_text()
     assert "mean_gbps" in csv_text and ",2\n" in csv_text  # two runs per point
+    # charts: bandwidth, latency, speed-up over NCCL, speed of light, run-to-run variation, device-timed tail
+    for name in ("bandwidth", "latency", "speedup", "sol", "variation", "tail"):
+        svg = (out / f"{name}_w2_fp32.svg").read_text()
+        assert svg.startswith("<svg") and "polyline" in svg and svg.rstrip().endswith("</svg>")
+    assert "![bandwidth_w2_fp32.svg]" in summary
+    # the per-kernel device-time summary and the index of a campaign directory
+    sys.path.insert(0, str(ROOT / "bench"))
+    import run_sweep
+    run_sweep.write_profiler_summary([str(run)], out)
+    prof = json.loads((out / "profiler_summary.json").read_text())
+    assert prof["kernels"]["flash"][f"fp32:{1 << 20}"] == {"calls": 400, "p50_us": 10.0, "p99_us": 10.5, "max_us": 12.0}
+
+    class A:
+        gpus, mode = 2, "quick"
+    run_sweep.write_index(out, A, run_sweep.MODES["quick"])
+    index = (out / "index.md").read_text()
+    assert "[summary.md](summary.md)" in index and "profiler_summary.json" in index and ".svg" in index
 
 
 def test_consolidate_eval(tmp_path):
@@ -143,7 +161,7 @@ def test_fused_layer_output_buffer_is_cached_per_shape():
             self.allocs += 1
             return [torch.empty(shape, dtype=dtype)]
 
-        def fused_linear(self, xs, ws, nws, outs, res, ro, eps, oneshot, ctas, tr, nvls):
+        def fused_linear(self, xs, ws, nws, outs, res, ro, eps, oneshot, ctas, tr, nvls, decode):
             self.calls.append((outs[0], oneshot, nvls))
 
         def symm_reset(self):
