@@ -84,6 +84,8 @@ def main():
     ap.add_argument("--emulate", type=int, default=0)
     ap.add_argument("--tokens", default="1,16,128,2048")
     ap.add_argument("--hidden", type=int, default=4096)
+    ap.add_argument("--k-per-rank", type=int, default=0,
+                    help="K of every rank's slice (default hidden / ranks); lets a 2-rank run use the TP = 8 shape K = 512")
     ap.add_argument("--iters", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--graph", action="store_true", help="time one CUDA-graph replay of all calls")
@@ -97,7 +99,7 @@ def main():
     emu = args.emulate > 0
     comm = yali.Comm.emulated(args.emulate) if emu else yali.Comm.from_env()
     W, rank = comm.world, comm.rank
-    N, K = args.hidden, args.hidden // W
+    N, K = args.hidden, (args.k_per_rank or args.hidden // W)
     tflops, src = peaks()
     use_nccl = not emu
     if use_nccl:
