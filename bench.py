@@ -12,8 +12,8 @@ per step on the launching stream after W warm-up steps, barrier + synchronize on
 both sides, max over ranks.  The line also carries p50/p99 latency of a 1 MiB
 all-reduce (1000 calls replayed from one CUDA graph, rotating over buffers that
 together exceed L2; every kernel stamps %globaltimer when its first CTA starts and
-when its last CTA leaves, so the samples contain no host jitter; call by call the
-max over ranks), the end-to-end number (pinned host -> device copy of the step's
+when its last CTA leaves, so the samples contain no host jitter; percentiles per
+rank, then the max over ranks), the end-to-end number (pinned host -> device copy of the step's
 input, all-reduce through the public API, device -> host copy of the result) next
 to the same copies without the collective, an NCCL arm measured with the same
 timing code on the same GPUs, and the clocks sampled during the timed region.
@@ -271,24 +271,18 @@ def run_own(args) -> dict:
     comm.barrier()
     comm.check()
     graph_us = gather_max(comm, g0.elapsed_time(g1) * 1e3 / lat_steps)
-    import struct
-    dur = [0.0] * lat_steps
-    cad = [0.0] * (lat_steps - 1)
+    # Per rank: cadence = end of the previous call -> end of this call (the time per call a stream of
+    # calls sees), duration = first CTA in -> last CTA out.  Percentiles per rank, then the max over ranks
+    # of each percentile (taking the max call by call would add the ranks' phase jitter to every sample).
+    p50 = p99 = d50 = d99 = 0.0
     for li in range(len(aslist(send))):
         _calls, entries = comm.read_trace(li, lat_steps)
         assert len(entries) == lat_steps, (len(entries), lat_steps)
-        for c, (t0, t1) in enumerate(entries):
-            dur[c] = max(dur[c], (t1 - t0) * 1e-3)
-            if c:
-                cad[c - 1] = max(cad[c - 1], (t1 - entries[c - 1][1]) * 1e-3)
-    if comm.nlocal == 1 and comm.world > 1:  # call by call the max over ranks
-        parts = comm.allgather_object_bytes(struct.pack(f"{lat_steps}d", *dur) + struct.pack(f"{lat_steps - 1}d", *cad))
-        for p in parts:
-            vals = struct.unpack(f"{2 * lat_steps - 1}d", p)
-            dur = [max(x, y) for x, y in zip(dur, vals[:lat_steps])]
-            cad = [max(x, y) for x, y in zip(cad, vals[lat_steps:])]
-    p50, p99 = percentile(cad, 50), percentile(cad, 99)
-    d50, d99 = percentile(dur, 50), percentile(dur, 99)
+        dur = [(t1 - t0) * 1e-3 for (t0, t1) in entries]
+        cad = [(entries[c][1] - entries[c - 1][1]) * 1e-3 for c in range(1, lat_steps)]
+        p50, p99 = max(p50, percentile(cad, 50)), max(p99, percentile(cad, 99))
+        d50, d99 = max(d50, percentile(dur, 50)), max(d99, percentile(dur, 99))
+    p50, p99, d50, d99 = (gather_max(comm, v) for v in (p50, p99, d50, d99))
     del graph
     small_variant = comm.last_call()
 
@@ -366,7 +360,8 @@ def run_own(args) -> dict:
                             "kernel": small_variant,
                             "note": "p50/p99: 1000 calls replayed from one CUDA graph; every kernel stamps "
                                     "%globaltimer at first-CTA entry and last-CTA exit; sample = end of previous call "
-                                    "to end of this call, call by call the max over ranks (kernel_*: entry to exit); "
+                                    "to end of this call on one rank (kernel_*: entry to exit); percentiles per rank, "
+                                    "then the max over ranks; "
                                     "host_event_*: one CUDA event pair per call from Python (contains host jitter); "
                                     "the averages: one event pair around all calls"},
         "e2e": {"value": round(e2e_busbw, 2), "unit": "GB/s", "h2d_bytes_per_step": MESSAGE_BYTES * n_local,
@@ -421,6 +416,23 @@ def run_reference(args) -> dict:
     small = subprocess.run([str(binary), str((1 << 20) // 4), "1000", "0", "auto", "0", "cuda-events", "fp32"],
                            capture_output=True, text=True, timeout=600)
     ms = re.search(r"([\d.]+) us/call(?: avg)?, ([\d.]+) GB/s", small.stdout)
+    # The reference's own NCCL benchmark (bench/benchmark_nccl.cu, argv: elements calls timing dtype), the
+    # comparator its README quotes: one process, two communicators, event pair on GPU 0.
+    ref_nccl = {}
+    nccl_bin = ref_dir / "benchmark_nccl"
+    if nccl_bin.exists():
+        for key, n, calls in (("busbw_128MiB_fp32", elems, args.steps), ("latency_1MiB", (1 << 20) // 4, 1000)):
+            try:
+                rn = subprocess.run([str(nccl_bin), str(n), str(calls), "cuda-events", "fp32"], capture_output=True,
+                                    text=True, timeout=600)
+                mn = re.search(r"NCCL \([^)]*\): (\d+) calls, ([\d.]+) us/call avg, ([\d.]+) GB/s", rn.stdout)
+                ref_nccl[key] = ({"avg_us": float(mn.group(2)), "busbw_gbps": float(mn.group(3))} if mn else
+                                 {"unavailable": (rn.stderr.strip() or rn.stdout.strip())[-160:].replace("\n", " ")})
+            except subprocess.TimeoutExpired:
+                ref_nccl[key] = {"unavailable": "timed out"}
+        ref_nccl["how"] = "the reference's bench/benchmark_nccl.cu built unmodified against the system libnccl"
+    else:
+        ref_nccl = {"unavailable": "baseline/_ref/benchmark_nccl is not built"}
     e2e = subprocess.run([str(harness), str(elems), str(max(3, min(args.steps, 20))), "3"], capture_output=True,
                          text=True, timeout=600)
     me = re.search(r"REF_E2E fp32 (\d+) (\d+) (\d+) ([\d.]+) ([\d.]+)", e2e.stdout)
@@ -439,6 +451,7 @@ def run_reference(args) -> dict:
         "e2e": {"value": round(e2e_val, 2) if e2e_val else None, "unit": "GB/s",
                 "h2d_bytes_per_step": MESSAGE_BYTES * 2, "d2h_bytes_per_step": MESSAGE_BYTES * 2,
                 "timing": "wall clock around H2D + yali::allreduce + D2H on both GPUs"},
+        "nccl": ref_nccl,
         "gpu_launches": 0, "clocks": clocks,
     }
 
