@@ -514,6 +514,7 @@ Result Communicator::Collective(const void* const* send, void* const* recv, uint
         a.recv = recv[i];
         a.count = count;
         a.stages = plan.stages;
+        a.plan_word = PlanWord(static_cast<int>(plan.variant) * 2 + ((plan.flags & kFlagLowLatency) ? 1 : 0), plan.ctas, count);
         a.ctas = plan.ctas;
         a.slot_bytes = plan.slot_bytes;
         a.shard_elems = plan.shard_elems;
@@ -628,10 +629,23 @@ std::string Communicator::DescribeStatus() const {
     for (const Local& l : local_) {
         const DeviceStatus s = *l.status;
         if (s.code == 0) continue;
-        char buf[256];
-        std::snprintf(buf, sizeof(buf),
-                      "rank %u gave up waiting for rank %u at '%s' (cta/lane %u): wanted %u, saw %u", s.rank, s.peer,
-                      s.code < 10 ? sites[s.code] : "?", s.cta, s.wanted, s.observed);
+        char buf[512];
+        int len = std::snprintf(buf, sizeof(buf),
+                                "rank %u gave up waiting for rank %u at '%s' (cta/lane %u): wanted %u, saw %u", s.rank, s.peer,
+                                s.code < 10 ? sites[s.code] : "?", s.cta, s.wanted, s.observed);
+        if (s.my_plan != 0 && s.peer_plan != 0 && s.my_plan != s.peer_plan) {
+            static const char* const kernels[] = {"flash", "flash (flag in data)", "stream", "stream", "nvls1", "nvls1",
+                                                  "nvls2", "nvls2", "flash_pull", "flash_pull", "stream_direct", "stream_direct"};
+            auto name = [&](uint32_t w) {
+                const uint32_t k = (w >> 28) - 1;
+                return k < 12 ? kernels[k] : "?";
+            };
+            std::snprintf(buf + len, sizeof(buf) - len,
+                          "; the ranks ran different kernels (rank %u: %s on %u CTAs, rank %u: %s on %u CTAs): their "
+                          "arguments differ (element count, dtype, or symmetric buffers on one rank only)",
+                          s.rank, name(s.my_plan), (s.my_plan >> 16) & 0xfffu, s.peer, name(s.peer_plan),
+                          (s.peer_plan >> 16) & 0xfffu);
+        }
         return buf;
     }
     return "";

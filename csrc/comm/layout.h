@@ -35,6 +35,7 @@ constexpr uint32_t kCallGemmCnt = 4;      // arrivals (per source) this rank has
 constexpr uint32_t kCallGemmDone = 8;     // [kMaxRanks] rows each owner has been asked to deliver so far
 constexpr uint32_t kCallDoneCtas = 16;    // [4] CTAs of the running launch that have finished, per kernel kind
 constexpr uint32_t kCallTraceIdx = 20;    // traced calls so far (index into the kTraceOff ring)
+constexpr uint32_t kCallPlanWord = 21;    // what this rank's running (or last) collective is: PlanWord() of its plan
 constexpr uint32_t kFlashFlagOff = 32;                                       // [kMaxFlashCtas][kMaxRanks]
 constexpr uint32_t kRsSeqOff = kFlashFlagOff + kMaxFlashCtas * kMaxRanks;    // [kMaxLanes][kMaxRanks]
 constexpr uint32_t kAgSeqOff = kRsSeqOff + kMaxLanes * kMaxRanks;            // [kMaxLanes][kMaxRanks]
@@ -102,8 +103,15 @@ struct DeviceStatus {
     uint32_t cta;
     uint32_t wanted;
     uint32_t observed;
-    uint32_t pad[2];
+    uint32_t my_plan;    // PlanWord of the call that gave up ...
+    uint32_t peer_plan;  // ... and of what the awaited rank was running (or last ran): they differ when the
+                         // ranks were given different arguments and therefore chose different kernels
 };
+
+// Identity of a plan in 32 bits: kernel (4 bits, variant + 1), CTAs (12 bits), low bits of the element count.
+__host__ __device__ inline uint32_t PlanWord(int variant, uint32_t ctas, uint64_t count) {
+    return (static_cast<uint32_t>(variant + 1) << 28) | ((ctas & 0xfffu) << 16) | static_cast<uint32_t>(count & 0xffffu);
+}
 
 // One rank's view of the communicator.
 struct CommView {
@@ -135,7 +143,7 @@ struct CollArgs {
     void* peer_recv[kMaxRanks];         // outputs of all ranks when they are peer-addressable, else nullptr
     uint64_t count;                     // elements
     uint32_t stages;                    // pipelined kernels: shared-memory stages per CTA
-    uint32_t reserved;
+    uint32_t plan_word;                 // PlanWord(): published at kernel start, compared with the peer's after a timeout
     uint32_t ctas;                      // CTAs (one-shot, NVLS, pipelined) or lanes (two-shot ring) per rank
     uint32_t slot_bytes;                // two-shot ring slot size; pipelined kernels: bytes per source and stage
     uint64_t shard_elems;               // two-shot / NVLS: elements owned by each rank

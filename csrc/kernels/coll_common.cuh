@@ -45,6 +45,9 @@ __device__ __forceinline__ void report_timeout(const CommView& cv, uint32_t site
         st->cta = cta;
         st->wanted = wanted;
         st->observed = observed;
+        // Which kernels the two ranks were running: a mismatch means mismatched arguments.
+        st->my_plan = *reinterpret_cast<volatile uint32_t*>(flag_word(cv, cv.rank, kCallPlanWord));
+        st->peer_plan = peer < static_cast<uint32_t>(cv.world) ? ptx::ld_relaxed_sys(flag_word(cv, peer, kCallPlanWord)) : 0u;
         __threadfence_system();
         st->code = site;
         __threadfence_system();
@@ -111,6 +114,12 @@ __device__ __forceinline__ void advance_call_word(const CommView& cv, uint32_t w
 // Device-side timeline (kFlagTrace): the first CTA stamps %globaltimer when it starts, the last CTA
 // to check out stamps it again and advances the ring index.  The host reads the ring after a
 // synchronisation and obtains per-call device times that contain no host jitter.
+// Publishes which plan this rank runs (one store by one thread per call): read by a peer that gave up
+// waiting for this rank, to tell "never arrived" from "arrived in a different kernel".
+__device__ __forceinline__ void announce_plan(const CommView& cv, uint32_t plan_word, uint32_t cta) {
+    if (cta == 0 && threadIdx.x == 0) *reinterpret_cast<volatile uint32_t*>(flag_word(cv, cv.rank, kCallPlanWord)) = plan_word;
+}
+
 __device__ __forceinline__ void trace_begin(const CommView& cv, uint32_t flags, uint32_t cta) {
     if ((flags & kFlagTrace) && cta == 0 && threadIdx.x == 0) {
         const uint32_t idx = *reinterpret_cast<volatile uint32_t*>(flag_word(cv, cv.rank, kCallTraceIdx));

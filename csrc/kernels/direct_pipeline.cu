@@ -57,6 +57,7 @@ __device__ __forceinline__ void direct_body(const CollArgs& a, uint32_t cta) {
     __shared__ uint32_t s_epoch;
 
     trace_begin(cv, a.flags, cta);
+    announce_plan(cv, a.plan_word, cta);
     if (tid == 0) {
         s_abort = 0;
         for (uint32_t s = 0; s < stages; ++s) {

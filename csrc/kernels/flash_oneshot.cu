@@ -86,6 +86,7 @@ __device__ __forceinline__ void flash_body(const CollArgs& a, uint32_t cta) {
     __shared__ uint32_t s_epoch;
     if (tid == 0) s_abort = 0;
     trace_begin(cv, a.flags, cta);
+    announce_plan(cv, a.plan_word, cta);
     const uint64_t deadline = ptx::globaltimer() + cv.timeout_ns;
     const uint32_t epoch = load_call_word(cv, kCallFlashEpoch, &s_epoch) + 1;  // this call's number
     const uint32_t parity = epoch & 1u;
@@ -189,6 +190,7 @@ __device__ __forceinline__ void flash_rmsnorm_body(const CollArgs& a, uint32_t c
     __shared__ uint32_t s_epoch;
     if (tid == 0) s_abort = 0;
     trace_begin(cv, a.flags, cta);
+    announce_plan(cv, a.plan_word, cta);
     const uint64_t deadline = ptx::globaltimer() + cv.timeout_ns;
     const uint32_t epoch = load_call_word(cv, kCallFlashEpoch, &s_epoch) + 1;  // this call's number
     const uint32_t parity = epoch & 1u;
@@ -283,6 +285,7 @@ __device__ __forceinline__ void flash_ll_body(const CollArgs& a, uint32_t cta) {
     const int tid = threadIdx.x, nt = blockDim.x;
     __shared__ uint32_t s_call[2];
     trace_begin(cv, a.flags, cta);
+    announce_plan(cv, a.plan_word, cta);
     if (tid < 2)
         s_call[tid] = *reinterpret_cast<volatile uint32_t*>(flag_word(cv, r, tid == 0 ? kCallFlashEpoch : kCallFlashEpochHi));
     __syncthreads();

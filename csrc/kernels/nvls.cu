@@ -121,6 +121,7 @@ __global__ void __launch_bounds__(kNvlsThreads, 2) nvls_kernel(const __grid_cons
     __shared__ uint32_t s_epoch;
     if (tid == 0) s_abort = 0;
     trace_begin(cv, a.flags, cta);
+    announce_plan(cv, a.plan_word, cta);
     const uint32_t epoch = load_call_word(cv, kCallBarEpoch, &s_epoch);  // barrier epochs used before this call
     const uint64_t deadline = ptx::globaltimer() + cv.timeout_ns;
 

@@ -71,6 +71,7 @@ __device__ __forceinline__ void stream_body(const CollArgs& a, uint32_t lane) {
     __shared__ uint32_t s_seq;
     if (tid == 0) s_abort = 0;
     trace_begin(cv, a.flags, lane);
+    announce_plan(cv, a.plan_word, lane);
     const uint32_t seq_base = load_call_word(cv, kCallStreamSeq, &s_seq);  // sequence numbers used before this call
     const uint64_t deadline = ptx::globaltimer() + cv.timeout_ns;
 

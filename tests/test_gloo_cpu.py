@@ -56,6 +56,15 @@ def _worker(rank, world, port, q):
     import yali_b200.ops.registry  # noqa: F401
     out2 = torch.ops.yali.all_reduce(inputs[rank])
     ok &= torch.equal(out2, out)
+    # shape / dtype rules of the operators under a tracer (no data, nothing runs)
+    from torch._subclasses.fake_tensor import FakeTensorMode
+    with FakeTensorMode():
+        fx = torch.empty(n)
+        ok &= torch.ops.yali.all_reduce(fx).shape == (n,)
+        ok &= torch.ops.yali.all_reduce_scaled(fx, 0.5, torch.bfloat16).dtype == torch.bfloat16
+        ok &= torch.ops.yali.fused_linear_rmsnorm(torch.empty(T, K), torch.empty(N, K), torch.empty(N)).shape == (T, N)
+        ok &= torch.ops.yali.reduce_scatter(fx).shape == (s,)
+        ok &= torch.ops.yali.all_gather(torch.empty(s), n).shape == (n,)
     yali.destroy_process_group()
     q.put((rank, bool(ok)))
 

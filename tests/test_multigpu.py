@@ -113,8 +113,8 @@ def _rank_main(rank, world, port, q, scenario):
         from yali_b200 import _native as nat
         ext = nat.ext()
         # A rank that leaves must not hold memory bound to an NVSwitch multicast object.
-        comm = yl.Comm.from_env(heap_bytes=2 << 30, timeout_ms=3000,
-                                want_multicast=scenario != "leave_between_steps")
+        comm = yl.Comm.from_env(heap_bytes=2 << 30, timeout_ms=1000 if scenario == "plan_mismatch" else 3000,
+                                want_multicast=scenario not in ("leave_between_steps", "plan_mismatch"))
         dev = f"cuda:{comm.device}"
         info = {"kind": comm.heap_kind, "mc": comm.has_multicast}
         ok = True
@@ -189,6 +189,29 @@ def _rank_main(rank, world, port, q, scenario):
                         ok &= good
                         comm.barrier()  # nobody clears `out` while a peer still writes rows into it
                 comm.symm_reset()
+        elif scenario == "plan_mismatch":
+            # Rank 0 passes symmetric buffers, rank 1 plain ones (a usage error): at 64 MiB the first
+            # picks the pipelined two-shot, the second the ring kernel.  Their waits run out (1 s limit,
+            # set above), the status names both kernels, and after reset() the communicator works again.
+            n = 16 << 20
+            sym_s, sym_r = comm.symm_empty(n, torch.float32), comm.symm_empty(n, torch.float32)
+            x = torch.empty(n, dtype=torch.float32, device=dev)
+            ext.fill_random(x, 0, 1234 + rank)
+            sym_s.copy_(x)
+            if rank == 0:
+                comm.all_reduce(sym_s, sym_r)
+            else:
+                comm.all_reduce(x, torch.empty_like(x))
+            try:
+                comm.sync()
+                ok = False
+            except Exception as e:  # noqa: BLE001
+                info["msg"] = str(e)[-260:]
+                ok &= "different kernels" in str(e) and "stream_direct" in str(e) and "symmetric buffers" in str(e)
+            comm.reset()
+            comm.all_reduce(sym_s, sym_r)
+            comm.sync()
+            ok &= ext.validate_sum(sym_r, torch.float32, 0, 1234, world)["mismatches"] == 0
         elif scenario == "leave_between_steps":
             x = torch.empty(65536, dtype=torch.float32, device=dev)
             ext.fill_random(x, 0, 1234 + rank)
@@ -254,6 +277,12 @@ def test_fused_linear_one_process_per_gpu(world, free_port):
     res = _spawn(world, "fused_linear", free_port + 2)
     assert len(res) == world, res
     assert all(ok for ok, _ in res.values()), res
+
+
+def test_ranks_with_different_arguments_get_a_precise_error(free_port, monkeypatch):
+    monkeypatch.setenv("YALI_NVLS_DISABLE", "1")  # plain peer loads/stores only: the waits of both ranks run out
+    res = _spawn(2, "plan_mismatch", free_port + 3, timeout=120)
+    assert len(res) == 2 and all(ok for ok, _ in res.values()), res
 
 
 def test_rank_that_stops_between_steps_times_out_the_others(free_port, monkeypatch):

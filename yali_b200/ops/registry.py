@@ -57,3 +57,42 @@ for _key in ("CPU", "CUDA"):
     _lib.impl("fused_linear_rmsnorm", _fused_linear_rmsnorm, _key)
     _lib.impl("reduce_scatter", _reduce_scatter, _key)
     _lib.impl("all_gather", _all_gather, _key)
+
+
+# ---- shape / dtype rules ("fake" kernels): what a tracer (FakeTensor, torch.export, the meta device) needs to
+# know about the operators without running them.  Shapes follow the eager implementations above.
+def _shard_elems(count: int) -> int:
+    from ..parallel import comm as _comm
+    world = _comm.get_default_comm().world
+    per = -(-count // world)
+    return -(-per // 16) * 16  # ceil(count / world) rounded up to 16 elements, as ShardElems in csrc/ops/tuning.cc
+
+
+@torch.library.register_fake("yali::all_reduce")
+def _fake_all_reduce(x):
+    return torch.empty_like(x)
+
+
+@torch.library.register_fake("yali::all_reduce_scaled")
+def _fake_all_reduce_scaled(x, scale, out_dtype=None):
+    return torch.empty_like(x, dtype=out_dtype or x.dtype)
+
+
+@torch.library.register_fake("yali::all_reduce_rmsnorm")
+def _fake_all_reduce_rmsnorm(x, weight, residual=None, eps=1e-5):
+    return torch.empty_like(x)
+
+
+@torch.library.register_fake("yali::fused_linear_rmsnorm")
+def _fake_fused_linear_rmsnorm(x, w, norm_weight, residual=None, eps=1e-5):
+    return x.new_empty((x.shape[0], w.shape[0]))
+
+
+@torch.library.register_fake("yali::reduce_scatter")
+def _fake_reduce_scatter(x):
+    return x.new_empty((_shard_elems(x.numel()),))
+
+
+@torch.library.register_fake("yali::all_gather")
+def _fake_all_gather(shard, count):
+    return shard.new_empty((count,))
