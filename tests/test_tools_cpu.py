@@ -104,6 +104,23 @@ def test_nccl_header_matches_library():
     assert vb.header_version() == vb.library_version()
 
 
+def test_baseline_validators_judge_their_inputs():
+    """The checks behind `validate_baselines.py --run` (peer-copy floors, NCCL sweep sanity) on canned output."""
+    sys.path.insert(0, str(ROOT / "bench"))
+    import validate_baselines as vb
+    good = {"copy_engine_unidirectional_gbs": 779.0, "copy_engine_bidirectional_per_direction_gbs": 774.0,
+            "sm_remote_store_gbs": 714.0, "sm_remote_load_gbs": 772.0, "bulk_pull_gbs": 781.0, "bulk_push_gbs": 714.0}
+    assert vb.check_p2p(good, 500.0) == []
+    assert any("sm_remote_load_gbs" in m for m in vb.check_p2p({**good, "sm_remote_load_gbs": 90.0}, 500.0))
+    assert vb.check_p2p({"unavailable": "needs two distinct GPUs"}, 500.0) == ["needs two distinct GPUs"]
+    rows = [{"dtype": "fp32", "bytes": 4096 << i, "us": 8.0 + (4096 << i) / 450e3, "busbw_gbps": (4096 << i) / (8.0 + (4096 << i) / 450e3) / 1e3}
+            for i in range(17)]  # 4 KiB .. 256 MiB
+    assert vb.check_nccl_sweep(rows, 300.0) == []
+    assert vb.check_nccl_sweep(rows[:5] + rows[6:], 300.0)  # a size is missing
+    assert vb.check_nccl_sweep([{**r, "busbw_gbps": 100.0} if r is rows[-1] else r for r in rows], 300.0)  # too slow
+    assert vb.check_nccl_sweep([], 300.0) == ["no rows"]
+
+
 def test_make_tuning_table_from_sweep_lines(tmp_path):
     """bench/make_tuning_table.py: fastest forced variant per size, hysteresis against noise, merged rows; the
     planner loads the result (the committed table of the B200 runs included)."""
