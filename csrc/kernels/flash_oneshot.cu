@@ -288,12 +288,8 @@ __device__ __forceinline__ void flash_ll_body(const CollArgs& a, uint32_t cta) {
     announce_plan(cv, a.plan_word, cta);
     if (tid < 2)
         s_call[tid] = *reinterpret_cast<volatile uint32_t*>(flag_word(cv, r, tid == 0 ? kCallFlashEpoch : kCallFlashEpochHi));
-    __syncthreads();
-    const uint32_t lo = s_call[0] + 1u;                       // this call's number (shared with the flagged form)
-    const uint32_t hi = (s_call[1] + (lo == 0u ? 1u : 0u)) | 0x80000000u;  // never zero: fresh memory never matches
-    const uint32_t parity = lo & 1u;
-    const uint64_t deadline = ptx::globaltimer() + cv.timeout_ns;
-
+    // The first payload vector of this thread is fetched while the call number is on its way, and kept
+    // for the reduction (with one vector per thread, the common case, the input is read exactly once).
     const uint64_t nvec = a.count / VEC;  // the planner only picks this form for whole vectors
     // This rank's own buffers may be aligned to their element type only (kFlagVecOk is a per-rank
     // property here): then they are read and written element by element; the lines on the wire and
@@ -302,6 +298,14 @@ __device__ __forceinline__ void flash_ll_body(const CollArgs& a, uint32_t cta) {
     const uint64_t per = (nvec + a.ctas - 1) / a.ctas;
     const uint64_t vb = min(nvec, static_cast<uint64_t>(cta) * per), ve = min(nvec, vb + per);
     const char* src = static_cast<const char*>(a.send);
+    const uint64_t v0 = vb + tid;
+    uint4 x0 = make_uint4(0, 0, 0, 0);
+    if (v0 < ve) x0 = aligned ? *reinterpret_cast<const uint4*>(src + v0 * 16) : load16_elems<T>(src, v0);
+    __syncthreads();
+    const uint32_t lo = s_call[0] + 1u;                       // this call's number (shared with the flagged form)
+    const uint32_t hi = (s_call[1] + (lo == 0u ? 1u : 0u)) | 0x80000000u;  // never zero: fresh memory never matches
+    const uint32_t parity = lo & 1u;
+    const uint64_t deadline = ptx::globaltimer() + cv.timeout_ns;
 
     char* dst[kMaxPeers];
     const char* in[kMaxW];
@@ -312,7 +316,7 @@ __device__ __forceinline__ void flash_ll_body(const CollArgs& a, uint32_t cta) {
 
     // ---- push: payload vector v becomes lines 2v and 2v+1
     for (uint64_t v = vb + tid; v < ve; v += nt) {
-        const uint4 x = aligned ? *reinterpret_cast<const uint4*>(src + v * 16) : load16_elems<T>(src, v);
+        const uint4 x = v == v0 ? x0 : (aligned ? *reinterpret_cast<const uint4*>(src + v * 16) : load16_elems<T>(src, v));
         const uint4 l0 = make_uint4(x.x, lo, x.y, hi), l1 = make_uint4(x.z, lo, x.w, hi);
 #pragma unroll
         for (int k = 0; k < kMaxPeers; ++k) {
@@ -334,7 +338,7 @@ __device__ __forceinline__ void flash_ll_body(const CollArgs& a, uint32_t cta) {
         for (int q = 0; q < kMaxW; ++q) {
             if (q >= W) continue;
             if (q == r) {
-                accumulate<T>(f, aligned ? *reinterpret_cast<const uint4*>(src + v * 16) : load16_elems<T>(src, v));
+                accumulate<T>(f, v == v0 ? x0 : (aligned ? *reinterpret_cast<const uint4*>(src + v * 16) : load16_elems<T>(src, v)));
                 continue;
             }
             uint4 l0, l1;
@@ -366,8 +370,10 @@ __device__ __forceinline__ void flash_ll_body(const CollArgs& a, uint32_t cta) {
     }
 }
 
+// At most 128 CTAs, one per SM: no register cap (the emulated twin shares the GPU among all ranks' CTAs
+// and keeps two per SM).
 template <typename T, int WORLD>
-__global__ void __launch_bounds__(kFlashThreads, 2) flash_ll_kernel(const __grid_constant__ CollArgs a) {
+__global__ void __launch_bounds__(kFlashThreads, 1) flash_ll_kernel(const __grid_constant__ CollArgs a) {
     flash_ll_body<T, WORLD>(a, blockIdx.x);
 }
 template <typename T, int WORLD>

@@ -8,8 +8,9 @@
 //
 //   * tiles are 128 (padded rows) x 32 columns, so N/32 = 128 CTAs each stream 1/128 of
 //     the weight slice: warp 0 feeds an 8-stage shared-memory ring with TMA
-//     (cp.async.bulk.tensor, 128-byte swizzle, no multicast; rows of x beyond T are
-//     out-of-bounds and arrive as zeros), warp 1 issues tcgen05.mma (M = 128, N = 32,
+//     (cp.async.bulk.tensor, 128-byte swizzle, no multicast; the box of x has 32 or 64
+//     rows, rows beyond T are out of bounds and arrive as zeros, the rest of the 128-row
+//     operand is zeroed once), warp 1 issues tcgen05.mma (M = 128, N = 32,
 //     bf16 x bf16 -> fp32) into a 32-column TMEM accumulator, and of warps 2..5 the ones
 //     whose TMEM lane quarter holds real rows read the accumulator back (tcgen05.ld);
 //   * every row of the partial tile (32 bf16 = 64 bytes) goes to EVERY rank, this one
@@ -115,6 +116,20 @@ __device__ __forceinline__ void decode_body(const GemmDecodeArgs& a, const CUten
     YALI_DSTAMP(1, 0);
 
     const uint32_t ntn = a.N / DBN, kblocks = a.K / DBK;
+    // The TMA box of x holds a.a_box_rows (32 or 64) rows, not 128: the copy engine spends its time per
+    // 128-byte row, real or out of bounds, so a 128-row box would cost four times the B tile.  The MMA
+    // still reads 128 rows; the rows the copies never touch are zeroed once here (with the 128-byte
+    // swizzle a box of 32 or 64 rows fills whole 1024-byte groups, so they stay zero).
+    const uint32_t a_bytes = a.a_box_rows * DBK * 2;
+    {
+        const uint32_t first = a_bytes / 16, per_stage = kDStageA / 16;  // 16-byte words
+        for (uint32_t i = tid; i < kDStages * (per_stage - first); i += blockDim.x) {
+            const uint32_t s = i / (per_stage - first), w = first + i % (per_stage - first);
+            *reinterpret_cast<uint4*>(smem + s * kDStageBytes + w * 16) = make_uint4(0, 0, 0, 0);
+        }
+        ptx::fence_proxy_async();  // generic-proxy zeros before the tensor cores read them
+        __syncthreads();
+    }
 
     // ------------------------------------------------------------------ phase 1: GEMM tiles [128 x 32]
     if (warp == 0) {
@@ -128,7 +143,7 @@ __device__ __forceinline__ void decode_body(const GemmDecodeArgs& a, const CUten
                         *abort_flag = 1;
                         break;
                     }
-                    ptx::mbar_expect_tx(&full_bar[s], kDStageBytes);
+                    ptx::mbar_expect_tx(&full_bar[s], a_bytes + kDStageB);
                     ptx::tma_load_2d(smem + s * kDStageBytes, tmap_a, kb * DBK, 0, &full_bar[s]);
                     ptx::tma_load_2d(smem + s * kDStageBytes + kDStageA, tmap_b, kb * DBK, tile * DBN, &full_bar[s]);
                 }

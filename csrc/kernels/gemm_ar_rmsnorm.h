@@ -54,7 +54,7 @@ constexpr int kGemmDecodeVecPerThread = 1;    // N <= 512 threads * 8 bf16 = 409
 constexpr uint32_t kGemmDecodeMaxRows = 64;   // two TMEM lane quarters
 
 struct alignas(64) GemmDecodeArgs {
-    CUtensorMap tmap_a;  // x  [T, K] bf16, box 64 x 128 (rows beyond T read as zeros), 128-byte swizzle
+    CUtensorMap tmap_a;  // x  [T, K] bf16, box 64 x a_box_rows (rows beyond T read as zeros), 128-byte swizzle
     CUtensorMap tmap_b;  // W  [N, K] bf16, box 64 x 32, 128-byte swizzle
     CommView cv;
     const void* residual;     // [T, N] bf16 or nullptr
@@ -62,6 +62,7 @@ struct alignas(64) GemmDecodeArgs {
     const void* norm_weight;  // [N] bf16
     void* out;                // [T, N] bf16, this rank's
     uint32_t T, N, K;
+    uint32_t a_box_rows;  // rows of x one TMA copy brings in: 32 (T <= 32) or 64
     float eps;
     unsigned long long* trace;  // optional: %globaltimer of CTA 0 at the phase boundaries
 };

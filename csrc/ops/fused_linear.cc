@@ -55,9 +55,11 @@ Result LaunchDecode(Communicator& comm, const DriverApi* drv, const FusedLinearD
         std::memset(&a, 0, sizeof(a));
         const FusedLinearDesc& d = descs[i];
         if (nlocal > 1) cudaSetDevice(comm.device_of(i));
-        if (!EncodeTileMap(drv, &a.tmap_a, d.x, T, K, kGemmTileM, &derr) ||
+        const uint32_t a_box_rows = T <= 32 ? 32u : 64u;
+        if (!EncodeTileMap(drv, &a.tmap_a, d.x, T, K, a_box_rows, &derr) ||
             !EncodeTileMap(drv, &a.tmap_b, d.w, N, K, kGemmDecodeTileN, &derr))
             return fail(Result::CudaError, derr);
+        a.a_box_rows = a_box_rows;
         a.cv = comm.View(i);
         a.residual = d.residual;
         a.residual_out = d.residual_out;

@@ -308,7 +308,11 @@ Result MakePlan(int world, uint64_t count, Dtype in, Dtype out, int epilogue, Ke
         v = bytes <= (128ull << 10) ? Variant::NvlsOneShot : Variant::NvlsTwoShot;
     else if (bytes <= LowLatencyMaxBytes(world) && bytes <= caps.ll_cap) v = Variant::Flash;
     else if (pull_ok && bytes <= PullCrossoverBytes(world)) v = Variant::FlashPull;
-    else if (bytes <= FlashCrossoverBytes(in, world)) v = Variant::Flash;
+    // With addressable buffers the pipelined two-shot overtakes the staged one-shot earlier: measured
+    // on 2 x B200 (events) 8 MiB 26.5 against 36.4 us, 16 MiB 40.6 against 40.0, 32 MiB 71.2 against 64.2.
+    else if (bytes <= (direct_ok && world == 2 ? std::min<uint64_t>(12ull << 20, FlashCrossoverBytes(in, world))
+                                               : FlashCrossoverBytes(in, world)))
+        v = Variant::Flash;
     else if (nvls_ok && world > 2) v = Variant::NvlsTwoShot;
     else if (direct_ok) v = Variant::StreamDirect;
     else v = Variant::Stream;

@@ -36,7 +36,7 @@ def _call(fn, sends, recvs, dtype_code):
     return fn(s, r, world, sends[0].numel(), dtype_code, ctypes.c_void_p(stream))
 
 
-@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("world", [2, 3, 4])
 @pytest.mark.parametrize("dtype,code,n", [(torch.float32, 0, 65536), (torch.bfloat16, 2, 100003),
                                           (torch.float16, 1, 7)])
 def test_matches_the_communicator_entry_point_twice(world, dtype, code, n):
@@ -63,6 +63,32 @@ def test_matches_the_communicator_entry_point_twice(world, dtype, code, n):
             assert rep["mismatches"] == 0, rep
 
 
+@pytest.mark.parametrize("world", [2, 3])
+def test_one_rank_with_unaligned_buffers(world):
+    """Rank 1's buffers start one element off a 16-byte boundary, the others' do not: the ranks must still agree on
+    how the message is cut (a rank that cannot use vector accesses only changes how it touches its own slice)."""
+    torch.cuda.set_device(0)
+    lib, fn = _entry()
+    ext = _native.ext()
+    for dtype, code, n in ((torch.float32, 0, 40001), (torch.bfloat16, 2, 9999)):
+        for call in range(2):
+            sends, recvs = [], []
+            for r in range(world):
+                off = 1 if r == 1 else 0
+                base = torch.empty(n + 8, dtype=dtype, device="cuda:0")
+                tmp = torch.empty(n, dtype=dtype, device="cuda:0")
+                ext.fill_random(tmp, 1, 700 + 10 * call + r)
+                base[off:off + n].copy_(tmp)
+                sends.append(base[off:off + n])
+                recvs.append(torch.full((n + 8,), float("nan"), dtype=dtype, device="cuda:0")[off:off + n])
+            assert sends[1].data_ptr() % 16 != 0 and sends[0].data_ptr() % 16 == 0
+            assert _call(fn, sends, recvs, code) == 0, lib.yaliNoAllocLastError().decode()
+            torch.cuda.synchronize()
+            for got in recvs:
+                assert ext.validate_sum(got.clone(), dtype, 1, 700 + 10 * call, world)["mismatches"] == 0
+            assert all(torch.equal(recvs[0], g) for g in recvs[1:])
+
+
 def test_in_place_and_refusals():
     torch.cuda.set_device(0)
     lib, fn = _entry()
@@ -79,6 +105,10 @@ def test_in_place_and_refusals():
     assert torch.equal(xs[0], xs[1])
     big = [torch.empty(MAX_BYTES // 4 + 1, dtype=torch.float32, device="cuda:0") for _ in range(2)]
     assert _call(fn, big, big, 0) != 0 and b"larger than" in lib.yaliNoAllocLastError()
+    # A count whose byte size would wrap around 64 bits is refused like any other oversized message.
+    s = (ctypes.c_void_p * 2)(*[t.data_ptr() for t in xs])
+    assert fn(s, s, 2, ctypes.c_size_t(1 << 62), 0, ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)) != 0
+    assert b"larger than" in lib.yaliNoAllocLastError()
     five = [torch.empty(8, dtype=torch.float32, device="cuda:0") for _ in range(5)]
     assert _call(fn, five, five, 0) != 0 and b"world" in lib.yaliNoAllocLastError()
     assert _call(fn, xs, xs, 7) != 0 and b"dtype" in lib.yaliNoAllocLastError()
