@@ -370,7 +370,7 @@ def run_own(args) -> dict:
                 "copies_only_ms_per_step": round(copies_ms / e2e_steps, 3),
                 "fraction_of_copies_only": round(copies_ms / e2e_ms, 3) if e2e_ms else None,
                 "gpu_launches": int(e2e_launches * (1 if emulated else ranks)),
-                "api": "Comm.all_reduce_host(pinned_in, pinned_out): H2D, all-reduce and D2H of 8 MiB chunks "
+                "api": "Comm.all_reduce_host(pinned_in, pinned_out): H2D, all-reduce and D2H of 4 MiB chunks "
                        "overlap on three streams; copies_only = the same copies without the collective, all "
                        "ranks at once (the ceiling of the host link)"},
         "nccl": nccl,

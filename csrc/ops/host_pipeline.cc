@@ -84,6 +84,9 @@ Result HostPipeline::AllReduce(const void* const* src, void* const* dst, uint64_
     }
     // Chunks are multiples of 256 elements so that every chunk keeps the 16-byte alignment of the
     // vector paths.
+    // chunk_bytes == 0: about 32 chunks per message, between 1 and 8 MiB each: the first copy in and the
+    // last copy out are not overlapped with anything, so they should be a small part of the whole.
+    if (chunk_bytes == 0) chunk_bytes = std::min<uint64_t>(8ull << 20, std::max<uint64_t>(1ull << 20, count * esz / 32));
     uint64_t chunk = std::max<uint64_t>(256, (std::max<uint64_t>(chunk_bytes, esz) / esz) / 256 * 256);
     chunk = std::min<uint64_t>(chunk, (count + 255) / 256 * 256);
     Result pr = Prepare(chunk * esz);

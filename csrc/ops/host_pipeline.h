@@ -22,7 +22,8 @@ class HostPipeline {
     HostPipeline& operator=(const HostPipeline&) = delete;
 
     // dst[i] = epilogue(sum over ranks of src) for every local rank i; src / dst are page-locked
-    // host buffers of `count` elements.  The message moves in chunks of about `chunk_bytes`
+    // host buffers of `count` elements.  The message moves in chunks of about `chunk_bytes` (0: about 32
+    // chunks of 1-8 MiB)
     // through a ring of four symmetric staging buffers per direction (allocated from the
     // symmetric heap on first use: every process must make the same calls).  Work is queued
     // behind `user_streams[i]` (or the communicator's own stream), which also waits for the

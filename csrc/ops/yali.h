@@ -137,7 +137,7 @@ cudaError_t allreduce_host_raw(Comm& comm, const void* const* send, void* const*
                                const cudaStream_t* streams, bool sync, size_t chunk_bytes);
 template <typename T>
 cudaError_t allreduce_host(Comm& comm, const T* const* send, T* const* recv, size_t count,
-                           const cudaStream_t* streams = nullptr, bool sync = true, size_t chunk_bytes = 8u << 20) {
+                           const cudaStream_t* streams = nullptr, bool sync = true, size_t chunk_bytes = 0) {
     if (!comm.ok()) return cudaErrorInvalidValue;
     return allreduce_host_raw(comm, reinterpret_cast<const void* const*>(send), reinterpret_cast<void* const*>(recv),
                               count, DtypeOf<T>::value, streams, sync, chunk_bytes);
@@ -204,7 +204,7 @@ cudaError_t allreduce_host_raw(MPIComm& comm, const void* send, void* recv, size
 // Page-locked host buffers in and out; synchronises `stream` (0: the communicator's) unless sync is false.
 template <typename T>
 cudaError_t allreduce_host(MPIComm& comm, const T* send, T* recv, size_t count, cudaStream_t stream = nullptr,
-                           bool sync = true, size_t chunk_bytes = 8u << 20) {
+                           bool sync = true, size_t chunk_bytes = 0) {
     if (!comm.ok()) return cudaErrorInvalidValue;
     return allreduce_host_raw(comm, send, recv, count, DtypeOf<T>::value, stream, sync, chunk_bytes);
 }

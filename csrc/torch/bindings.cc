@@ -398,7 +398,7 @@ class PyComm {
         auto st = Streams();
         c10::cuda::OptionalCUDAGuard guard(c().device_of(0));
         Throw(host_pipe_->AllReduce(s.data(), r.data(), static_cast<uint64_t>(n), ToDtype(d), o,
-                                    static_cast<uint64_t>(std::max<int64_t>(chunk_bytes, 4096)), st.data(), copies_only),
+                                    static_cast<uint64_t>(chunk_bytes <= 0 ? 0 : std::max<int64_t>(chunk_bytes, 4096)), st.data(), copies_only),
               c().last_error());
     }
 
@@ -552,7 +552,7 @@ PYBIND11_MODULE(_C, m) {
              py::arg("nvls") = -1, py::arg("decode") = -1)
         .def("symm_empty", &PyComm::SymmEmpty, py::arg("shape"), py::arg("dtype"))
         .def("symm_reset", &PyComm::SymmReset)
-        .def("all_reduce_host", &PyComm::AllReduceHost, py::arg("src"), py::arg("dst"), py::arg("chunk_bytes") = 8 << 20,
+        .def("all_reduce_host", &PyComm::AllReduceHost, py::arg("src"), py::arg("dst"), py::arg("chunk_bytes") = 0,
              py::arg("scale") = py::none(), py::arg("mode") = "auto", py::arg("copies_only") = false)
         .def("sync", &PyComm::Sync)
         .def("check", &PyComm::Check)

@@ -40,7 +40,7 @@ def fused_linear_rmsnorm(x: torch.Tensor, w: torch.Tensor, norm_weight: torch.Te
 
 
 def all_reduce_host(src: torch.Tensor, dst: Optional[torch.Tensor] = None, *, comm=None,
-                    chunk_bytes: int = 8 << 20, scale: Optional[float] = None) -> torch.Tensor:
+                    chunk_bytes: int = 0, scale: Optional[float] = None) -> torch.Tensor:
     """Sum over all ranks of a tensor in pinned host memory, result in pinned host memory; the copies in
     both directions and the all-reduce overlap chunk by chunk (Comm.all_reduce_host)."""
     return _pick(comm).all_reduce_host(src, dst, chunk_bytes=chunk_bytes, scale=scale)

@@ -219,11 +219,11 @@ class Comm:
         return self._like_input(x, outs)
 
     def all_reduce_host(self, src: TensorOrList, dst: Optional[TensorOrList] = None, *,
-                        chunk_bytes: int = 8 << 20, scale: Optional[float] = None, mode: str = "auto",
+                        chunk_bytes: int = 0, scale: Optional[float] = None, mode: str = "auto",
                         copies_only: bool = False):
         """All-reduce of tensors that live in pinned host memory: dst = scale * sum over ranks of src.
 
-        The message is cut into chunks that move through three streams per GPU: host-to-device copy,
+        The message is cut into chunks (`chunk_bytes`; 0 = about 32 chunks of 1-8 MiB) that move through three streams per GPU: host-to-device copy,
         all-reduce, device-to-host copy.  Chunk i+1 is copied in while chunk i is reduced and chunk i-1
         is copied out, so both PCIe directions and NVLink are busy at the same time and a call costs
         about one direction's copy time instead of the sum of the three phases.  Staging is a ring of
@@ -413,7 +413,7 @@ class GlooComm:
         recv.copy_(full)
         return recv
 
-    def all_reduce_host(self, src: torch.Tensor, dst: Optional[torch.Tensor] = None, *, chunk_bytes: int = 8 << 20,
+    def all_reduce_host(self, src: torch.Tensor, dst: Optional[torch.Tensor] = None, *, chunk_bytes: int = 0,
                         scale: Optional[float] = None, mode: str = "auto") -> torch.Tensor:
         """Same call as Comm.all_reduce_host; on CPU the data is in host memory already."""
         return self.all_reduce(src, dst, scale=scale)
