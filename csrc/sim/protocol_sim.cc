@@ -412,6 +412,73 @@ void NvlsCta(Shared& s, int r, int cta) {
     }
 }
 
+// Pipelined direct forms (direct_pipeline.cu).  mode 4, two-shot IN PLACE: buf[r] is rank r's input and
+// output; CTA c of rank r sums chunk c, c+C, ... of shard r over all ranks' buffers and writes the sum into
+// every rank's buffer.  mode 5, one-shot pull: CTA c of rank r sums chunk c, c+C, ... of the whole message
+// over all ranks' inputs into its own output.  Two per-CTA barriers per call are the only synchronisation.
+// Between calls every rank overwrites its input with the next call's data (what a user or the next kernel
+// does), which is only safe if the second barrier really means "all peers are done with this rank's
+// buffer".  Stamps per element: 2*call+1 = input of the call, 2*call+2 = result of the call (mode 4).
+void DirectCta(Shared& s, int r, int cta) {
+    const YaliSimConfig& c = s.cfg;
+    const int W = s.W, C = s.L;
+    const bool one_shot = c.mode == 5;
+    const uint64_t S = ((c.count + W - 1) / W + 3) / 4 * 4;  // shard elements
+    const uint64_t chunk = std::max<uint64_t>(4, c.slot_elems ? c.slot_elems : 64);
+    const uint64_t range_b = one_shot ? 0 : std::min<uint64_t>(c.count, r * S);
+    const uint64_t range_e = one_shot ? c.count : std::min<uint64_t>(c.count, range_b + S);
+    auto stamp_at = [&](int rank, uint64_t e) -> std::atomic<uint64_t>& { return s.ll[rank][e]; };
+    for (int call = 0; call < c.calls; ++call) {
+        if (c.fault == 1 && r == c.fault_rank && call >= c.fault_call) return;
+        const uint32_t epoch = 2u * call;
+        const uint64_t in_stamp = 2ull * call + 1, out_stamp = 2ull * call + 2;
+        SignalPeers(s, r, kFlash, cta, epoch + 1, call);
+        bool ok = WaitPeers(s, r, kFlash, cta, epoch + 1, 1);
+        if (ok) {
+            for (uint64_t b = range_b + cta * chunk; b < range_e; b += static_cast<uint64_t>(C) * chunk) {
+                const uint64_t e = std::min(range_e, b + chunk);
+                for (uint64_t i = b; i < e; ++i) {
+                    float acc = 0.f;
+                    for (int q = 0; q < W; ++q) {  // the bulk copies of the stage: every rank's input
+                        if (stamp_at(q, i).load(std::memory_order_acquire) != in_stamp) s.violations.fetch_add(1);
+                        acc += s.send[q][i];
+                    }
+                    if (one_shot) {
+                        s.recv[r][i] = acc;
+                    } else {
+                        for (int q = 0; q < W; ++q) {
+                            s.send[q][i] = acc;  // in place: input and output are one buffer
+                            stamp_at(q, i).store(out_stamp, std::memory_order_release);
+                        }
+                    }
+                }
+            }
+            for (int p = 0; p < W; ++p)
+                if (p != r) Flag(s, p, kAg, cta, r).store(epoch + 2, std::memory_order_release);
+            ok = WaitPeers(s, r, kAg, cta, epoch + 2, 2);
+        }
+        if (!ok) s.abort = true;
+        if (s.abort.load()) s.rank_abort[r].store(1);
+        s.rank_barrier[r]->wait();  // the kernel of this rank is complete
+        if (s.rank_abort[r].load()) return;
+        if (cta == 0) {
+            // The stream's next operation on this rank: check the results and write the next call's input.
+            const bool last = call + 1 == c.calls;
+            for (uint64_t i = 0; i < c.count; ++i) {
+                if (!one_shot) {
+                    if (stamp_at(r, i).load(std::memory_order_acquire) != out_stamp) s.violations.fetch_add(1);
+                    if (last) s.recv[r][i] = s.send[r][i];
+                }
+                if (!last) {
+                    s.send[r][i] = yali::RandomValue(yali::kDistNormal, c.seed + r + 1000ull * (call + 1), i);
+                    stamp_at(r, i).store(in_stamp + 2, std::memory_order_release);
+                }
+            }
+        }
+        s.rank_barrier[r]->wait();
+    }
+}
+
 }  // namespace
 
 extern "C" int yali_c_simulate(const YaliSimConfig* cfg, YaliSimReport* rep) {
@@ -439,7 +506,10 @@ extern "C" int yali_c_simulate(const YaliSimConfig* cfg, YaliSimReport* rep) {
             s.ring_stamp.emplace_back(new std::atomic<uint64_t>[nslots]);
             for (size_t i = 0; i < nslots; ++i) s.ring_stamp[r][i].store(0);
         } else {
-            if (cfg->mode == 2 || cfg->mode == 3) {
+            if (cfg->mode == 4 || cfg->mode == 5) {
+                s.ll.emplace_back(new std::atomic<uint64_t>[cfg->count]);
+                for (size_t i = 0; i < cfg->count; ++i) s.ll[r][i].store(1);  // input of call 0
+            } else if (cfg->mode == 2 || cfg->mode == 3) {
                 const size_t nw = 2ull * std::max(W - 1, 1) * cfg->count;
                 s.ll.emplace_back(new std::atomic<uint64_t>[nw]);
                 for (size_t i = 0; i < nw; ++i) s.ll[r][i].store(0);
@@ -455,7 +525,11 @@ extern "C" int yali_c_simulate(const YaliSimConfig* cfg, YaliSimReport* rep) {
     std::vector<std::thread> threads;
     for (int r = 0; r < W; ++r)
         for (int l = 0; l < s.L; ++l)
-            threads.emplace_back(cfg->mode == 1 ? StreamLane : (cfg->mode == 2 ? FlashLLCta : (cfg->mode == 3 ? NvlsCta : FlashCta)),
+            threads.emplace_back(cfg->mode == 1   ? StreamLane
+                                 : cfg->mode == 2 ? FlashLLCta
+                                 : cfg->mode == 3 ? NvlsCta
+                                 : (cfg->mode == 4 || cfg->mode == 5) ? DirectCta
+                                                                      : FlashCta,
                                  std::ref(s), r, l);
     // A rank that stops launching leaves its lanes' barrier short-handed only for itself.
     for (auto& t : threads) t.join();
@@ -476,10 +550,12 @@ extern "C" int yali_c_simulate(const YaliSimConfig* cfg, YaliSimReport* rep) {
     }
     // Oracle: fp64 sum; fp32 rank-order accumulation differs from it by rounding only.
     uint64_t bad = 0;
+    const bool direct = cfg->mode == 4 || cfg->mode == 5;
     for (int r = 0; r < W; ++r) {
         for (uint64_t i = 0; i < cfg->count; ++i) {
             double e = 0.0;
-            for (int q = 0; q < W; ++q) e += s.send[q][i];
+            for (int q = 0; q < W; ++q)  // the pipelined forms get fresh inputs every call: the last call's count
+                e += direct ? yali::RandomValue(yali::kDistNormal, cfg->seed + q + 1000ull * (cfg->calls - 1), i) : s.send[q][i];
             if (!(std::fabs(s.recv[r][i] - e) <= 1e-5 * W + 1e-5 * std::fabs(e))) ++bad;
         }
     }

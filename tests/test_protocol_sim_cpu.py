@@ -44,6 +44,22 @@ def test_one_shot_protocol_back_to_back(world):
     assert rc == 0 and rep.mismatches == 0
 
 
+@pytest.mark.parametrize("world", [2, 3, 4, 8])
+@pytest.mark.parametrize("mode", [4, 5])
+def test_pipelined_direct_protocols_back_to_back(world, mode):
+    """Two-shot in place (4) and one-shot pull (5): the two per-CTA barriers of a call must keep every rank from
+    rewriting its input (which all ranks read in place) or reading its output too early, over back-to-back calls
+    with fresh inputs per call and chunks that interleave over the CTAs."""
+    for count, lanes, chunk in [(1, 1, 4), (4099, 3, 64), (50001, 5, 128)]:
+        rc, rep = simulate(mode=mode, world=world, lanes=lanes, calls=5, count=count, slot_elems=chunk)
+        assert rc == 0 and rep.mismatches == 0 and rep.timeouts == 0, (count, lanes, chunk, rc, rep.mismatches)
+
+
+def test_rank_that_never_launches_times_out_pipelined():
+    rc, rep = simulate(mode=4, world=4, lanes=2, fault=1, fault_rank=3, fault_call=1, calls=3, count=5000, timeout_ms=300)
+    assert rc == 2 and rep.timeouts >= 1 and rep.timeout_peer == 3 and rep.timeout_rank != 3
+
+
 def test_rank_that_never_launches_times_out_ring():
     rc, rep = simulate(world=4, fault=1, fault_rank=2, fault_call=1, calls=3, timeout_ms=300)
     assert rc == 2 and rep.timeouts >= 1 and rep.timeout_peer == 2 and rep.timeout_rank != 2
