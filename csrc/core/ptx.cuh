@@ -51,14 +51,9 @@ __device__ __forceinline__ uint32_t ld_relaxed_sys(const uint32_t* p) {
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
-__device__ __forceinline__ void st_relaxed_sys(uint32_t* p, uint32_t v) {
-    asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
 __device__ __forceinline__ void red_release_sys_add(uint32_t* p, uint32_t v) {
     asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
-__device__ __forceinline__ void fence_acq_rel_sys() { asm volatile("fence.acq_rel.sys;" ::: "memory"); }
-__device__ __forceinline__ void fence_acq_rel_gpu() { asm volatile("fence.acq_rel.gpu;" ::: "memory"); }
 // Orders generic-proxy accesses against async-proxy (bulk copy / tensor core) accesses.
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async;" ::: "memory"); }
 
@@ -95,18 +90,8 @@ __device__ __forceinline__ uint4 ld_cg_v4(const void* p) {
     asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
     return v;
 }
-// Read-once stream of an input buffer that nobody writes during the kernel.
-__device__ __forceinline__ uint4 ld_stream_v4(const void* p) {
-    uint4 v;
-    asm volatile("ld.global.cs.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-    return v;
-}
 __device__ __forceinline__ void st_v4(void* p, const uint4& v) {
     asm volatile("st.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
-}
-__device__ __forceinline__ void st_cs_v4(void* p, const uint4& v) {
-    asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
-                 : "memory");
 }
 
 // ----------------------------------------------------------------------------- multimem (NVLS)
@@ -142,11 +127,6 @@ __device__ __forceinline__ void multimem_st_v4(void* mc, const uint4& v) {
                  "r"(v.z), "r"(v.w)
                  : "memory");
 }
-// Adds to the same flag word on every bound GPU with one instruction.
-__device__ __forceinline__ void multimem_red_release_add(uint32_t* mc_flag, uint32_t v) {
-    asm volatile("multimem.red.release.sys.global.add.u32 [%0], %1;" ::"l"(mc_flag), "r"(v) : "memory");
-}
-
 // ----------------------------------------------------------------------------- mbarrier
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
@@ -170,15 +150,6 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait on an mbarrier phase.  Returns false when `max_tries` polls passed
-// (each try_wait already blocks for a hardware-defined slice of time).
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, uint32_t max_tries) {
-    for (uint32_t i = 0; i < max_tries; ++i) {
-        if (mbar_try_wait(bar, parity)) return true;
-    }
-    return false;
-}
-
 // ----------------------------------------------------------------------------- bulk async copies (TMA), no multicast
 // 1-D bulk copy global -> shared, completion counted in bytes on an mbarrier.
 // Both addresses 16-byte aligned, size a multiple of 16.
@@ -187,21 +158,6 @@ __device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gsrc, uint3
         "cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(smem_dst)),
         "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
         : "memory");
-}
-// 1-D bulk copy shared -> global (local or peer memory).
-__device__ __forceinline__ void bulk_s2g(void* gdst, const void* smem_src, uint32_t bytes) {
-    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(smem_u32(smem_src)),
-                 "r"(bytes)
-                 : "memory");
-}
-__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void bulk_wait_read() {
-    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
-}
-template <int N>
-__device__ __forceinline__ void bulk_wait() {
-    asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
 }
 // 2-D tiled TMA load through a tensor map (x = innermost coordinate; x * elem size
 // must be a multiple of 16 bytes).

@@ -155,6 +155,15 @@ def _rank_main(rank, world, port, q, scenario):
             full = comm.all_gather(sh, n)
             comm.sync()
             ok &= ext.validate_sum(full, torch.float32, 1, 99, world)["mismatches"] == 0
+            # the same all-gather between symmetric buffers: the ring kernel writes straight into the peers' outputs
+            sh_sym, full_sym = comm.symm_empty(sh.numel(), torch.float32), comm.symm_empty(n, torch.float32)
+            sh_sym.copy_(sh)
+            comm.barrier()
+            for _ in range(3):
+                comm.all_gather(sh_sym, n, full_sym)
+            comm.sync()
+            ok &= bool(comm.last_call()["flags"] & 2)  # direct all-gather
+            ok &= ext.validate_sum(full_sym, torch.float32, 1, 99, world)["mismatches"] == 0
         elif scenario == "fused_linear":
             # Row-parallel GEMM + all-reduce + residual + RMSNorm in one kernel per rank: the push
             # forms and (with a multicast object) the in-switch form against an fp32 reference.

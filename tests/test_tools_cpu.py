@@ -163,7 +163,7 @@ def test_make_tuning_table_from_sweep_lines(tmp_path):
 
 def test_fused_layer_output_buffer_is_cached_per_shape():
     """With one GPU per process the fused layer's default output comes from the symmetric heap, which is
-    never freed piecemeal: one buffer per shape, handed out again, forgotten by symm_reset()."""
+    never freed piecemeal: one buffer per row width, grown by doubling, handed out again, forgotten by symm_reset()."""
     import torch
 
     from yali_b200.parallel.comm import Comm
@@ -192,14 +192,19 @@ def test_fused_layer_output_buffer_is_cached_per_shape():
     x, w, g = torch.zeros(6, 8, dtype=torch.bfloat16), torch.zeros(16, 8, dtype=torch.bfloat16), torch.ones(16)
     y1 = comm.fused_linear_rmsnorm(x, w, g)
     y2 = comm.fused_linear_rmsnorm(x, w, g, nvls=2)
-    assert y1 is y2 and impl.allocs == 1 and tuple(y1.shape) == (6, 16)
+    assert y1.data_ptr() == y2.data_ptr() and impl.allocs == 1 and tuple(y1.shape) == (6, 16)
     assert impl.calls[0][1:] == (-1, -1) and impl.calls[1][2] == 2
-    y3 = comm.fused_linear_rmsnorm(torch.zeros(3, 8, dtype=torch.bfloat16), w, g)  # another shape: another buffer
-    assert y3 is not y1 and impl.allocs == 2
+    y3 = comm.fused_linear_rmsnorm(torch.zeros(3, 8, dtype=torch.bfloat16), w, g)  # fewer rows: the same buffer
+    assert y3.data_ptr() == y1.data_ptr() and tuple(y3.shape) == (3, 16) and impl.allocs == 1
+    y5 = comm.fused_linear_rmsnorm(torch.zeros(7, 8, dtype=torch.bfloat16), w, g)  # more rows: grown by doubling
+    assert tuple(y5.shape) == (7, 16) and impl.allocs == 2
+    for rows in (8, 9, 12, 5, 11):  # up to 12 rows fit the doubled buffer: no further allocation
+        assert tuple(comm.fused_linear_rmsnorm(torch.zeros(rows, 8, dtype=torch.bfloat16), w, g).shape) == (rows, 16)
+    assert impl.allocs == 2
     mine = torch.empty(6, 16, dtype=torch.bfloat16)
     assert comm.fused_linear_rmsnorm(x, w, g, out=mine) is mine and impl.allocs == 2
     comm.symm_reset()
     assert impl.resets == 1
     y4 = comm.fused_linear_rmsnorm(x, w, g)
-    assert y4 is not y1 and impl.allocs == 3
+    assert impl.allocs == 3 and tuple(y4.shape) == (6, 16)
     comm.close()

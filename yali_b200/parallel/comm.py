@@ -187,7 +187,7 @@ class Comm:
         (tcgen05 GEMM whose epilogue pushes partial rows to their owner over NVLink, then reduce + norm).
         x: [T, K], w: [N, K] (this rank's slice, nn.Linear layout), bf16.  With one GPU per process the
         two-shot form (T above a few dozen rows) needs `out` from symm_empty(); without `out` the call
-        returns a per-shape symmetric buffer of its own that the next call of that shape overwrites.  `trace`: int64 CUDA
+        returns the first T rows of a per-width symmetric buffer of its own that the next call of that width overwrites.  `trace`: int64 CUDA
         tensor(s) of 8 elements that receive CTA 0's %globaltimer at the phase boundaries.  `nvls`: how the
         two-shot form uses the NVSwitch multicast object: None = by measurement, 0/False = not at all
         (peer pushes and peer stores), 1/True = in-switch reduce + multicast store, 2 = peer pushes +
@@ -198,12 +198,16 @@ class Comm:
         if out is None:
             T, N = xs[0].shape[0], ws[0].shape[0]
             if self.nlocal == 1 and self.world > 1:
-                # Symmetric memory is never freed piecemeal: keep ONE output per shape and hand it out again.
-                # The tensor returned by a call is therefore overwritten by the next call of that shape.
+                # Symmetric memory is never freed piecemeal: keep ONE output per row width, large enough for the
+                # most rows seen so far (grown by doubling, so a program that varies its token count holds at
+                # most twice its largest output per width), and hand out its first T rows.  The tensor returned
+                # by a call is therefore overwritten by the next call of that width.
                 cache = self.__dict__.setdefault("_fused_out", {})
-                if (T, N) not in cache:
-                    cache[(T, N)] = self.symm_empty([T, N], torch.bfloat16)
-                outs = [cache[(T, N)]]
+                buf = cache.get(N)
+                if buf is None or buf.shape[0] < T:
+                    rows = T if buf is None else max(T, 2 * buf.shape[0])
+                    buf = cache[N] = self.symm_empty([rows, N], torch.bfloat16)
+                outs = [buf[:T]]
             else:
                 outs = [torch.empty(T, N, dtype=torch.bfloat16, device=t.device) for t in xs]
         else:
