@@ -108,8 +108,10 @@ def gather_max(comm, value: float) -> float:
     return max(struct.unpack("d", p)[0] for p in parts)
 
 
-def time_steps(comm, torch, fn, steps: int, warmup: int):
-    """Runs fn(i) warmup+steps times; returns (total_ms max over ranks, per-step ms list of this rank)."""
+def time_steps(comm, torch, fn, steps: int, warmup: int, per_step_events: bool = True):
+    """Runs fn(i) warmup+steps times; returns (total_ms max over ranks, per-step ms list of this rank).
+    One CUDA event pair brackets the `steps` timed calls; with `per_step_events` an event is also recorded
+    between the steps (each record keeps consecutive kernels a few microseconds apart)."""
     for i in range(warmup):
         fn(i)
     comm.barrier()
@@ -119,11 +121,12 @@ def time_steps(comm, torch, fn, steps: int, warmup: int):
     evs[0].record()
     for i in range(steps):
         fn(warmup + i)
-        evs[i + 1].record()
+        if per_step_events or i == steps - 1:
+            evs[i + 1].record()
     torch.cuda.synchronize()
     comm.barrier()
     comm.check()
-    per = [evs[i].elapsed_time(evs[i + 1]) for i in range(steps)]
+    per = [evs[i].elapsed_time(evs[i + 1]) for i in range(steps)] if per_step_events else []
     total = evs[0].elapsed_time(evs[steps])
     time_steps.launches = comm.launches - launches0  # kernels this process launched inside the timed region
     return gather_max(comm, total), per
@@ -223,7 +226,7 @@ def run_own(args) -> dict:
 
     if rank == 0:
         sampler.start()  # runs across all timed regions below (each alone is shorter than one sample period)
-    total_ms, per = time_steps(comm, torch, step, args.steps, args.warmup)
+    total_ms, per = time_steps(comm, torch, step, args.steps, args.warmup, per_step_events=False)
     launches = time_steps.launches * (1 if emulated else ranks)  # every rank launches the same count
     variant = comm.last_call()
     ok = all(ext.validate_sum(t, torch.float32, 0, 1234, ranks)["mismatches"] == 0 for t in aslist(recv))
