@@ -94,6 +94,7 @@ inline const char* KernelLabel(yali::Variant v, uint32_t flags) {
         case yali::Variant::NvlsTwoShot: return "NVLS2";
         case yali::Variant::FlashPull: return "FlashPull";
         case yali::Variant::StreamDirect: return "StreamDirect";
+        case yali::Variant::CopyEngine: return "CopyEngine";
     }
     return "?";
 }

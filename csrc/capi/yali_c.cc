@@ -84,6 +84,7 @@ int yali_c_make_plan(int world, uint64_t count, int in_dt, int out_dt, int epilo
     caps.ll_cap = c->ll_cap;
     caps.peer_send = c->peer_send != 0;
     caps.in_place = c->in_place != 0;
+    caps.one_gpu_per_rank = c->one_gpu_per_rank != 0;
     TuningTable table;
     const TuningTable* tp = nullptr;
     std::string e;

@@ -50,14 +50,15 @@ typedef struct YaliPlanCaps {
     uint32_t max_ctas;
     uint64_t ll_cap;
     int peer_send, in_place; /* every input peer-addressable; some rank reduces in place */
+    int one_gpu_per_rank;    /* every rank is a process with a GPU of its own (needed by the copy-engine path) */
 } YaliPlanCaps;
 typedef struct YaliPlan {
-    int variant; /* 0 flash, 1 stream, 2 nvls one-shot, 3 nvls two-shot, 4 pipelined one-shot pull, 5 pipelined two-shot */
+    int variant; /* 0 flash, 1 stream, 2 nvls one-shot, 3 nvls two-shot, 4 pipelined one-shot pull, 5 pipelined two-shot, 6 copy engines */
     uint32_t ctas, slot_bytes, max_iters, flags;
     uint64_t shard_elems;
     uint32_t stages, smem_bytes;
 } YaliPlan;
-/* mode: 0 auto, 1 flash, 2 stream, 3 nvls, 4 flash_pull, 5 stream_direct.  tuning_json may be NULL.  Returns a Result code. */
+/* mode: 0 auto, 1 flash, 2 stream, 3 nvls, 4 flash_pull, 5 stream_direct, 6 copy_engine.  tuning_json may be NULL.  Returns a Result code. */
 int yali_c_make_plan(int world, uint64_t count, int in_dtype, int out_dtype, int epilogue, int mode,
                      const YaliPlanCaps* caps, const char* tuning_json, YaliPlan* plan, char* err, size_t err_len);
 int yali_c_heap_layout(int world, uint64_t requested_total, uint64_t* fields /* 16 values: the 12 region fields, then ll_off, ll_cap, gemm_ll_off, gemm_ll_cap */);

@@ -202,6 +202,7 @@ Communicator::~Communicator() {
     for (Local& l : local_) {
         if (cudaSetDevice(l.device) == cudaSuccess) cudaDeviceSynchronize();
     }
+    DestroyCopyEngineState();
     // Nobody unmaps or unbinds while a peer may still touch this rank's heap.
     if (bs_) bs_->barrier();
     for (void* p : ipc_opened_) cudaIpcCloseMemHandle(p);
@@ -363,6 +364,9 @@ Result Communicator::Launch(const Plan& plan, Dtype in, Dtype out, int epilogue,
                 if (dev_threads >= 64 && dev_threads <= kNvlsThreads) threads = static_cast<int>(dev_threads) / 32 * 32;
             }
             break;
+        case Variant::CopyEngine:
+            if (in != out || epilogue != kEpiIdentity) return Fail(Result::Unsupported, "the copy-engine path only sums");
+            return LaunchCopyEngine(plan, in, args, streams);
         case Variant::FlashPull:
         case Variant::StreamDirect:
             fn = DirectKernelFor(in, out, world_, plan.variant == Variant::FlashPull, emulated_);
@@ -461,6 +465,10 @@ Result Communicator::Collective(const void* const* send, void* const* recv, uint
     caps.peer_recv = peer_recv && !rs_only;
     caps.peer_send = peer_recv;  // ResolvePeers fills both tables or neither
     caps.in_place = in_place;
+    // One process that drives several GPUs issues the ranks' work one after the other; the copy-engine
+    // path's kernels wait for the peers' kernels, and on 2 x B200 rank 0 ran into its deadline before
+    // the host got to launch rank 1.  One process per rank only.
+    caps.one_gpu_per_rank = !emulated_ && nlocal() == 1;
     caps.half_collective = rs_only || ag_only;
     caps.sm_count = sm_count_;
     caps.max_ctas = max_ctas_;
@@ -625,20 +633,22 @@ Result Communicator::Sync(const cudaStream_t* streams) {
 std::string Communicator::DescribeStatus() const {
     static const char* const sites[] = {"none",          "one-shot arrival", "ring credit", "reduce-scatter slot",
                                         "all-gather slot", "ring drain",       "CTA barrier", "GEMM partials",
-                                        "GEMM done",     "mbarrier"};
+                                        "GEMM done",     "mbarrier",         "copy-engine: peer entered",
+                                        "copy-engine: peer read chunk", "copy-engine: peer finished"};
     for (const Local& l : local_) {
         const DeviceStatus s = *l.status;
         if (s.code == 0) continue;
         char buf[512];
         int len = std::snprintf(buf, sizeof(buf),
                                 "rank %u gave up waiting for rank %u at '%s' (cta/lane %u): wanted %u, saw %u", s.rank, s.peer,
-                                s.code < 10 ? sites[s.code] : "?", s.cta, s.wanted, s.observed);
+                                s.code < 13 ? sites[s.code] : "?", s.cta, s.wanted, s.observed);
         if (s.my_plan != 0 && s.peer_plan != 0 && s.my_plan != s.peer_plan) {
             static const char* const kernels[] = {"flash", "flash (flag in data)", "stream", "stream", "nvls1", "nvls1",
-                                                  "nvls2", "nvls2", "flash_pull", "flash_pull", "stream_direct", "stream_direct"};
+                                                  "nvls2", "nvls2", "flash_pull", "flash_pull", "stream_direct", "stream_direct",
+                                                  "copy_engine", "copy_engine"};
             auto name = [&](uint32_t w) {
                 const uint32_t k = (w >> 28) - 1;
-                return k < 12 ? kernels[k] : "?";
+                return k < 14 ? kernels[k] : "?";
             };
             std::snprintf(buf + len, sizeof(buf) - len,
                           "; the ranks ran different kernels (rank %u: %s on %u CTAs, rank %u: %s on %u CTAs): their "

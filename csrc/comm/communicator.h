@@ -165,6 +165,11 @@ class Communicator {
     Result ResolvePeers(const void* const* send, void* const* recv, uint64_t send_bytes, uint64_t recv_bytes,
                         bool stable, CollArgs* args, bool* peer_recv, bool* symmetric);
     Result EnsureSmemAttr(const void* fn, uint32_t smem_bytes);
+    // Copy-engine all-reduce (copy_engine_path.cc): streams, events and staging per local rank, made on first use.
+    struct CeState;
+    Result LaunchCopyEngine(const Plan& plan, Dtype dt, CollArgs* args, const cudaStream_t* streams);
+    void DestroyCopyEngineState();
+    std::vector<CeState*> ce_;
     Result Fail(Result r, const std::string& what) {
         err_ = what;
         return r;

@@ -36,6 +36,7 @@ constexpr uint32_t kCallGemmDone = 8;     // [kMaxRanks] rows each owner has bee
 constexpr uint32_t kCallDoneCtas = 16;    // [4] CTAs of the running launch that have finished, per kernel kind
 constexpr uint32_t kCallTraceIdx = 20;    // traced calls so far (index into the kTraceOff ring)
 constexpr uint32_t kCallPlanWord = 21;    // what this rank's running (or last) collective is: PlanWord() of its plan
+constexpr uint32_t kCallCeCalls = 22;     // copy-engine all-reduce calls so far
 constexpr uint32_t kFlashFlagOff = 32;                                       // [kMaxFlashCtas][kMaxRanks]
 constexpr uint32_t kRsSeqOff = kFlashFlagOff + kMaxFlashCtas * kMaxRanks;    // [kMaxLanes][kMaxRanks]
 constexpr uint32_t kAgSeqOff = kRsSeqOff + kMaxLanes * kMaxRanks;            // [kMaxLanes][kMaxRanks]
@@ -48,7 +49,11 @@ constexpr uint32_t kStatusCntOff = kGemmDoneOff + kGemmRowBlocks * kMaxRanks;  /
 // its first CTA and at the check-out of its last CTA into entry i % kTraceCap.
 constexpr uint32_t kTraceCap = 4096;
 constexpr uint32_t kTraceOff = kStatusCntOff + 8;              // [kTraceCap][2] uint64 = 4 words per call
-constexpr uint32_t kFlagWords = kTraceOff + kTraceCap * 4;
+// Copy-engine all-reduce (kernels/copy_engine.cu): progress words written by the peers, one per source.
+constexpr uint32_t kCeEnterOff = kTraceOff + kTraceCap * 4;  // [kMaxRanks] call the source has entered
+constexpr uint32_t kCePulledOff = kCeEnterOff + kMaxRanks;   // [kMaxRanks] (call << 8) | chunks the source has read here
+constexpr uint32_t kCeDoneOff = kCePulledOff + kMaxRanks;    // [kMaxRanks] call the source has finished with this rank
+constexpr uint32_t kFlagWords = kCeDoneOff + kMaxRanks;
 constexpr uint64_t kFlagRegionBytes = 1ull << 20;
 static_assert(kFlagWords * 4ull <= kFlagRegionBytes, "flag region too small");
 static_assert(kTraceOff % 2 == 0, "the timeline entries are 64-bit words");
@@ -95,6 +100,9 @@ enum WaitSite : uint32_t {
     kSiteGemmPartials = 7,
     kSiteGemmDone = 8,
     kSiteMbar = 9,
+    kSiteCeEnter = 10,
+    kSiteCePulled = 11,
+    kSiteCeExit = 12,
 };
 struct DeviceStatus {
     uint32_t code;      // 0 = ok, otherwise a WaitSite

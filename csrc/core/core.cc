@@ -34,6 +34,7 @@ bool ParseKernelMode(const char* s, KernelMode* out) {
     else if (!strcasecmp(s, "nvls")) *out = KernelMode::NVLS;
     else if (!strcasecmp(s, "flash_pull")) *out = KernelMode::FlashPull;
     else if (!strcasecmp(s, "stream_direct")) *out = KernelMode::StreamDirect;
+    else if (!strcasecmp(s, "copy_engine") || !strcasecmp(s, "ce")) *out = KernelMode::CopyEngine;
     else return false;
     return true;
 }

@@ -55,8 +55,9 @@ bool ParseDtype(const char* s, Dtype* out);
 enum class DataType : int { Float32 = 0, Float16 = 1, BFloat16 = 2 };
 enum class ReduceOp : int { Sum = 0 };
 // FlashPull / StreamDirect force the pipelined kernels that read the peers' inputs in place
-// (they need buffers every rank can address); Auto picks them when they apply.
-enum class KernelMode : int { Auto = 0, Flash = 1, Stream = 2, NVLS = 3, FlashPull = 4, StreamDirect = 5 };
+// (they need buffers every rank can address); Auto picks them when they apply.  CopyEngine lets
+// cudaMemcpyAsync move the payload between the GPUs and keeps kernels for the additions and the flags.
+enum class KernelMode : int { Auto = 0, Flash = 1, Stream = 2, NVLS = 3, FlashPull = 4, StreamDirect = 5, CopyEngine = 6 };
 
 inline Dtype ToDtype(DataType d) { return static_cast<Dtype>(static_cast<int>(d)); }
 inline DataType ToDataType(Dtype d) { return static_cast<DataType>(static_cast<int>(d)); }
@@ -69,6 +70,7 @@ inline const char* KernelModeName(KernelMode m) {
         case KernelMode::NVLS: return "nvls";
         case KernelMode::FlashPull: return "flash_pull";
         case KernelMode::StreamDirect: return "stream_direct";
+        case KernelMode::CopyEngine: return "copy_engine";
         case KernelMode::Auto: break;
     }
     return "auto";

@@ -7,16 +7,23 @@
 // fence plus a counter round trip before the reduction.  This form is built for latency:
 //
 //   * tiles are 128 (padded rows) x 32 columns, so N/32 = 128 CTAs each stream 1/128 of
-//     the weight slice: warp 0 feeds an 8-stage shared-memory ring with TMA
-//     (cp.async.bulk.tensor, 128-byte swizzle, no multicast; the box of x has 32 or 64
-//     rows, rows beyond T are out of bounds and arrive as zeros, the rest of the 128-row
-//     operand is zeroed once), warp 1 issues tcgen05.mma (M = 128, N = 32,
-//     bf16 x bf16 -> fp32) into a 32-column TMEM accumulator, and of warps 2..5 the ones
-//     whose TMEM lane quarter holds real rows read the accumulator back (tcgen05.ld);
+//     the weight slice: warp 0 feeds a shared-memory ring of 24 (T <= 32) or 16 stages
+//     with TMA (cp.async.bulk.tensor, 128-byte swizzle, no multicast; the box of x has 8, 16,
+//     32 or 64 rows, rows beyond T are out of bounds and arrive as zeros), warp 1 issues
+//     tcgen05.mma (M = 128, N = 32, bf16 x bf16 -> fp32) into a 32-column TMEM
+//     accumulator, and of warps 2..5 the ones whose TMEM lane quarter holds real rows
+//     read the accumulator back (tcgen05.ld).  A stage holds only the rows the box brings
+//     in: the 128-row operand the MMA reads runs on into the following stages, and what it
+//     finds there only reaches accumulator rows that nobody reads (rows are independent).
+//     That keeps a stage at 8 or 12 KiB, so the whole K extent of a 2048-deep slice is in
+//     flight at once instead of going four times round an 8-stage ring;
 //   * every row of the partial tile (32 bf16 = 64 bytes) goes to EVERY rank, this one
 //     included, as eight 16-byte lines that carry 8 bytes of payload and the 64-bit call
 //     number {data, call_lo, data, call_hi}: the flag travels in the data, so there is no
-//     release fence, no counter and no barrier between the GEMM and the reduction;
+//     release fence, no counter and no barrier between the GEMM and the reduction.  The
+//     landing zone is tile-major ([tile][row][8 lines]) and the lines pass through shared
+//     memory on their way out, so one store instruction of a warp covers 512 contiguous
+//     bytes of the peer's memory instead of 32 pieces of 16 bytes 4*N bytes apart;
 //   * CTA t (t < T) then owns row t on this rank: its 512 threads poll the lines of all
 //     ranks for one 16-byte output vector each (all loads of a vector in flight together),
 //     add them in fp32 in rank order, add the residual, normalise and store the row.
@@ -33,14 +40,27 @@ namespace yali {
 namespace {
 
 constexpr int DBM = 128, DBN = kGemmDecodeTileN, DBK = 64;
-constexpr int kDStages = 8;
-constexpr uint32_t kDStageA = DBM * DBK * 2, kDStageB = DBN * DBK * 2, kDStageBytes = kDStageA + kDStageB;
-constexpr uint32_t kDSmemBytes = kDStages * kDStageBytes + 1024;  // + slack to align the base
-constexpr uint32_t kDTmemCols = 64;                               // two accumulators of 32 fp32 columns
+constexpr int kDMaxStages = 24;
+constexpr uint32_t kDStageB = DBN * DBK * 2;
+// All A tiles first (a_box_rows * 128 bytes each), then all B tiles: 24 x (1..4 + 4) KiB or 16 x (8 + 4) KiB.
+// The MMA reads 128 rows (16 KiB) from the start of an A tile; past the last A tile that runs into the
+// B tiles (at least 64 KiB of them), never past the allocation.
+constexpr uint32_t kDRingBytes = 192 * 1024;
+constexpr uint32_t kDSmemBytes = kDRingBytes + 1024;  // + slack to align the base
+// MMAs that add into one accumulator run one after the other, each for its full pipeline latency: with
+// N = 32 there is hardly any arithmetic to hide it (measured 85 ns per MMA, 0.34 us per 64-deep k-block,
+// whatever M, the tile's bytes or the depth of the ring).  The four k-steps of a k-block therefore add
+// into four accumulators of their own, which the epilogue sums.
+constexpr uint32_t kDAccs = DBK / 16;
+constexpr uint32_t kDTmemCols = 2 * kDAccs * DBN;  // two tiles in flight x four accumulators x 32 fp32 columns
 
-// D = fp32, A = B = bf16, both K-major, N at bit 17 (>>3), M at bit 24 (>>4).
-constexpr uint32_t kDIdesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(DBN >> 3) << 17) |
-                             (static_cast<uint32_t>(DBM >> 4) << 24);
+// D = fp32, A = B = bf16, both K-major, N at bit 17 (>>3), M at bit 24 (>>4).  M is 128, or 64 for up to
+// 16 rows: an MMA streams its M x 16 operand out of shared memory whatever N is, so with N = 32 that
+// stream sets the pace (measured 0.27 us per 64-deep k-block with M = 128), and rows 0..15 sit in TMEM
+// lanes 0..15 with either M.
+__device__ __forceinline__ uint32_t decode_idesc(uint32_t m) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(DBN >> 3) << 17) | ((m >> 4) << 24);
+}
 
 __device__ __forceinline__ uint64_t desc_sw128(uint32_t smem_addr) {
     uint64_t d = 0;
@@ -59,8 +79,8 @@ __device__ __forceinline__ uint4 ld_volatile16(const void* p) {
     return v;
 }
 
-// Flag-in-data landing zone on `on_rank` for the partial rows of `src`: line i (16 bytes) holds
-// columns 4i..4i+3 of the row-major [T, N] partial.
+// Flag-in-data landing zone on `on_rank` for the partial rows of `src`, tile-major: line
+// ((tile * T + row) * 8 + j) (16 bytes) holds columns 32 * tile + 4j .. 4j+3 of row `row`.
 __device__ __forceinline__ char* ll_landing(const GemmDecodeArgs& a, int on_rank, int src, uint32_t parity) {
     return a.cv.heap[on_rank] + a.cv.lay.gemm_ll_off +
            (static_cast<uint64_t>(parity) * a.cv.world + src) * a.cv.lay.gemm_ll_cap;
@@ -69,7 +89,8 @@ __device__ __forceinline__ char* ll_landing(const GemmDecodeArgs& a, int on_rank
 __device__ __forceinline__ void decode_body(const GemmDecodeArgs& a, const CUtensorMap* tmap_a,
                                             const CUtensorMap* tmap_b, uint32_t cta, uint32_t nctas) {
     extern __shared__ uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t full_bar[kDStages], empty_bar[kDStages], tmem_full_bar[2], tmem_empty_bar[2];
+    __shared__ __align__(8) uint64_t full_bar[kDMaxStages], empty_bar[kDMaxStages], tmem_full_bar[2], tmem_empty_bar[2];
+    __shared__ __align__(16) uint4 s_lines[2][32 * 8];  // per active epilogue warp: 32 rows x 8 lines, swizzled
     __shared__ uint32_t s_tmem;
     __shared__ int s_abort;
     __shared__ float s_red[32];
@@ -90,7 +111,7 @@ __device__ __forceinline__ void decode_body(const GemmDecodeArgs& a, const CUten
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     if (tid == 0) {
         s_abort = 0;
-        for (int s = 0; s < kDStages; ++s) {
+        for (int s = 0; s < kDMaxStages; ++s) {
             ptx::mbar_init(&full_bar[s], 1);
             ptx::mbar_init(&empty_bar[s], 1);
         }
@@ -116,42 +137,35 @@ __device__ __forceinline__ void decode_body(const GemmDecodeArgs& a, const CUten
     YALI_DSTAMP(1, 0);
 
     const uint32_t ntn = a.N / DBN, kblocks = a.K / DBK;
-    // The TMA box of x holds a.a_box_rows (32 or 64) rows, not 128: the copy engine spends its time per
-    // 128-byte row, real or out of bounds, so a 128-row box would cost four times the B tile.  The MMA
-    // still reads 128 rows; the rows the copies never touch are zeroed once here (with the 128-byte
-    // swizzle a box of 32 or 64 rows fills whole 1024-byte groups, so they stay zero).
+    // The TMA box of x holds a.a_box_rows (8, 16, 32 or 64) rows, not 128: the copy engine spends its time per
+    // 128-byte row, real or out of bounds, so a 128-row box would cost four times the B tile.
     const uint32_t a_bytes = a.a_box_rows * DBK * 2;
-    {
-        const uint32_t first = a_bytes / 16, per_stage = kDStageA / 16;  // 16-byte words
-        for (uint32_t i = tid; i < kDStages * (per_stage - first); i += blockDim.x) {
-            const uint32_t s = i / (per_stage - first), w = first + i % (per_stage - first);
-            *reinterpret_cast<uint4*>(smem + s * kDStageBytes + w * 16) = make_uint4(0, 0, 0, 0);
-        }
-        ptx::fence_proxy_async();  // generic-proxy zeros before the tensor cores read them
-        __syncthreads();
-    }
+    const uint32_t stages = min(kDRingBytes / (a_bytes + kDStageB), static_cast<uint32_t>(kDMaxStages));  // 24 or 16
+    uint8_t* const smem_b = smem + stages * a_bytes;
 
     // ------------------------------------------------------------------ phase 1: GEMM tiles [128 x 32]
     if (warp == 0) {
         if (lane == 0) {
-            uint32_t g = 0;
+            uint32_t s = 0, round = 0;
             for (uint32_t tile = cta; tile < ntn && !*abort_flag; tile += nctas) {
-                for (uint32_t kb = 0; kb < kblocks; ++kb, ++g) {
-                    const uint32_t s = g % kDStages;
-                    if (!mbar_wait_deadline(&empty_bar[s], ((g / kDStages) & 1u) ^ 1u, deadline, abort_flag)) {
-                        if (!*abort_flag) report_timeout(cv, kSiteMbar, r, cta, 11, g);
+                for (uint32_t kb = 0; kb < kblocks; ++kb) {
+                    if (!mbar_wait_deadline(&empty_bar[s], (round & 1u) ^ 1u, deadline, abort_flag)) {
+                        if (!*abort_flag) report_timeout(cv, kSiteMbar, r, cta, 11, round * stages + s);
                         *abort_flag = 1;
                         break;
                     }
                     ptx::mbar_expect_tx(&full_bar[s], a_bytes + kDStageB);
-                    ptx::tma_load_2d(smem + s * kDStageBytes, tmap_a, kb * DBK, 0, &full_bar[s]);
-                    ptx::tma_load_2d(smem + s * kDStageBytes + kDStageA, tmap_b, kb * DBK, tile * DBN, &full_bar[s]);
+                    // The weights come from HBM, x from L2: ask for the weights first.
+                    ptx::tma_load_2d(smem_b + s * kDStageB, tmap_b, kb * DBK, tile * DBN, &full_bar[s]);
+                    ptx::tma_load_2d(smem + s * a_bytes, tmap_a, kb * DBK, 0, &full_bar[s]);
+                    if (++s == stages) s = 0, ++round;
                 }
+                if (tile == cta) YALI_DSTAMP(5, 0);  // all copies of the first tile requested
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            uint32_t g = 0, it = 0;
+            uint32_t s = 0, round = 0, it = 0;
             for (uint32_t tile = cta; tile < ntn && !*abort_flag; tile += nctas, ++it) {
                 const uint32_t b = it & 1u;
                 if (!mbar_wait_deadline(&tmem_empty_bar[b], ((it >> 1) & 1u) ^ 1u, deadline, abort_flag)) {
@@ -160,23 +174,26 @@ __device__ __forceinline__ void decode_body(const GemmDecodeArgs& a, const CUten
                     break;
                 }
                 ptx::tc_fence_after_sync();
-                const uint32_t d_tmem = tmem + b * DBN;
-                for (uint32_t kb = 0; kb < kblocks; ++kb, ++g) {
-                    const uint32_t s = g % kDStages;
-                    if (!mbar_wait_deadline(&full_bar[s], (g / kDStages) & 1u, deadline, abort_flag)) {
-                        if (!*abort_flag) report_timeout(cv, kSiteMbar, r, cta, 12, g);
+                const uint32_t d_tmem = tmem + b * kDAccs * DBN;
+                const uint32_t idesc = decode_idesc(a.mma_m);
+                for (uint32_t kb = 0; kb < kblocks; ++kb) {
+                    if (!mbar_wait_deadline(&full_bar[s], round & 1u, deadline, abort_flag)) {
+                        if (!*abort_flag) report_timeout(cv, kSiteMbar, r, cta, 12, round * stages + s);
                         *abort_flag = 1;
                         break;
                     }
                     ptx::tc_fence_after_sync();
-                    const uint32_t a_addr = ptx::smem_u32(smem + s * kDStageBytes);
-                    const uint64_t da = desc_sw128(a_addr), db = desc_sw128(a_addr + kDStageA);
+                    if (it == 0 && kb == 0) YALI_DSTAMP(6, 32);  // first stage has arrived
+                    const uint64_t da = desc_sw128(ptx::smem_u32(smem + s * a_bytes));
+                    const uint64_t db = desc_sw128(ptx::smem_u32(smem_b + s * kDStageB));
 #pragma unroll
                     for (int k = 0; k < DBK / 16; ++k)
-                        ptx::tc_mma_f16(d_tmem, da + 2 * k, db + 2 * k, kDIdesc, (kb | k) != 0 ? 1u : 0u);
+                        ptx::tc_mma_f16(d_tmem + k * DBN, da + 2 * k, db + 2 * k, idesc, kb != 0 ? 1u : 0u);
                     ptx::tc_commit(&empty_bar[s]);
+                    if (++s == stages) s = 0, ++round;
                 }
                 if (*abort_flag) break;
+                if (it == 0) YALI_DSTAMP(7, 32);  // all MMAs of the first tile issued
                 ptx::tc_commit(&tmem_full_bar[b]);
             }
         }
@@ -192,30 +209,53 @@ __device__ __forceinline__ void decode_body(const GemmDecodeArgs& a, const CUten
             }
             ptx::tc_fence_after_sync();
             if (it == 0) YALI_DSTAMP(2, 64);  // first accumulator complete
-            const uint32_t row = q * 32 + lane;
             if (static_cast<uint32_t>(q) * 32 < a.T) {  // this quarter holds real rows
                 uint32_t v[32];
-                ptx::tmem_ld_32x32(tmem + b * DBN + (static_cast<uint32_t>(q * 32) << 16), v);
-                ptx::tmem_ld_wait();
+                {
+                    const uint32_t base = tmem + b * kDAccs * DBN + (static_cast<uint32_t>(q * 32) << 16);
+                    uint32_t u[32];
+                    ptx::tmem_ld_32x32(base, v);
+                    ptx::tmem_ld_32x32(base + DBN, u);
+                    ptx::tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) + __uint_as_float(u[i]));
+#pragma unroll
+                    for (int h = 2; h < static_cast<int>(kDAccs); ++h) {
+                        ptx::tmem_ld_32x32(base + h * DBN, u);
+                        ptx::tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) + __uint_as_float(u[i]));
+                    }
+                }
                 ptx::tc_fence_before_sync();
                 __syncwarp();
                 if (lane == 0) ptx::mbar_arrive(&tmem_empty_bar[b]);
-                if (row < a.T) {
-                    // 32 fp32 -> 32 bf16 -> eight lines {2 bf16, call_lo, 2 bf16, call_hi}
-                    uint32_t packed[16];
+                // 32 fp32 -> 32 bf16 -> eight lines {2 bf16, call_lo, 2 bf16, call_hi}, lane = row; through
+                // shared memory (line j of row at j ^ (row & 7)) they come back as lane = (row % 4, line).
+                uint4* stage = s_lines[q];
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
-                        packed[i] = *reinterpret_cast<const uint32_t*>(&h);
-                    }
-                    const uint64_t line0 = (static_cast<uint64_t>(row) * a.N + static_cast<uint64_t>(tile) * DBN) / 4;
-                    for (int k = 0; k < W; ++k) {
-                        const int d = (r + k) % W;  // own copy first, then the right-hand neighbour
-                        char* dst = ll_landing(a, d, r, parity) + line0 * 16;
+                for (int j = 0; j < 8; ++j) {
+                    const __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]));
+                    const __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+                    stage[lane * 8 + (j ^ (lane & 7))] = make_uint4(*reinterpret_cast<const uint32_t*>(&h0), lo,
+                                                                   *reinterpret_cast<const uint32_t*>(&h1), hi);
+                }
+                __syncwarp();
+                uint4 mine[8];
 #pragma unroll
-                        for (int j = 0; j < 8; ++j)
-                            ptx::st_v4(dst + j * 16, make_uint4(packed[2 * j], lo, packed[2 * j + 1], hi));
-                    }
+                for (int i = 0; i < 8; ++i) {
+                    const int rl = i * 4 + (lane >> 3);
+                    mine[i] = stage[rl * 8 + ((lane & 7) ^ (rl & 7))];
+                }
+                __syncwarp();  // the next tile may overwrite the staging lines
+                // This warp's rows of this tile are one contiguous block of the landing zone.
+                const uint64_t block = (static_cast<uint64_t>(tile) * a.T + static_cast<uint64_t>(q) * 32) * 128;
+                for (int k = 0; k < W; ++k) {
+                    const int d = (r + k) % W;  // own copy first, then the right-hand neighbour
+                    char* dst = ll_landing(a, d, r, parity) + block + lane * 16;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i)
+                        if (static_cast<uint32_t>(q * 32 + i * 4 + (lane >> 3)) < a.T) ptx::st_v4(dst + i * 512, mine[i]);
                 }
             } else {
                 ptx::tc_fence_before_sync();
@@ -248,8 +288,8 @@ __device__ __forceinline__ void decode_body(const GemmDecodeArgs& a, const CUten
         for (int j = 0; j < kGemmDecodeVecPerThread; ++j) {
             const uint32_t c = tid + j * nt;
             if (c < vec_per_row && !timed_out) {
-                // Output vector c = columns 8c..8c+7 = lines 2c and 2c+1 of the row, from every rank.
-                const uint64_t off = ((static_cast<uint64_t>(row) * a.N + static_cast<uint64_t>(c) * VEC) / 4) * 16;
+                // Output vector c = columns 8c..8c+7 = lines 2 (c % 4) and the next of tile c / 4, from every rank.
+                const uint64_t off = ((static_cast<uint64_t>(c >> 2) * a.T + row) * 8 + (c & 3u) * 2) * 16;
                 uint4 l0[kMaxRanks], l1[kMaxRanks];
                 uint32_t pending = (1u << W) - 1u, polls = 0;
                 const uint4 rv = res ? ptx::ld_cg_v4(res + (static_cast<uint64_t>(row) * a.N + static_cast<uint64_t>(c) * VEC) * 2)

@@ -62,7 +62,8 @@ struct alignas(64) GemmDecodeArgs {
     const void* norm_weight;  // [N] bf16
     void* out;                // [T, N] bf16, this rank's
     uint32_t T, N, K;
-    uint32_t a_box_rows;  // rows of x one TMA copy brings in: 32 (T <= 32) or 64
+    uint32_t a_box_rows;  // rows of x one TMA copy brings in: 8, 16, 32 or 64 (the smallest that holds T)
+    uint32_t mma_m;       // rows of one MMA: 64 (T <= 16) or 128
     float eps;
     unsigned long long* trace;  // optional: %globaltimer of CTA 0 at the phase boundaries
 };

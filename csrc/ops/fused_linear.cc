@@ -55,11 +55,14 @@ Result LaunchDecode(Communicator& comm, const DriverApi* drv, const FusedLinearD
         std::memset(&a, 0, sizeof(a));
         const FusedLinearDesc& d = descs[i];
         if (nlocal > 1) cudaSetDevice(comm.device_of(i));
-        const uint32_t a_box_rows = T <= 32 ? 32u : 64u;
+        const uint32_t a_box_rows = T <= 8 ? 8u : T <= 16 ? 16u : T <= 32 ? 32u : 64u;
         if (!EncodeTileMap(drv, &a.tmap_a, d.x, T, K, a_box_rows, &derr) ||
             !EncodeTileMap(drv, &a.tmap_b, d.w, N, K, kGemmDecodeTileN, &derr))
             return fail(Result::CudaError, derr);
         a.a_box_rows = a_box_rows;
+        static const long long force_m = env::GetInt("YALI_GEMM_DECODE_M", 0);  // measurements only
+        a.mma_m = force_m == 64 || force_m == 128 ? static_cast<uint32_t>(force_m) : (T <= 16 ? 64u : 128u);
+        if (T > 16) a.mma_m = 128;
         a.cv = comm.View(i);
         a.residual = d.residual;
         a.residual_out = d.residual_out;

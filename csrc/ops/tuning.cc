@@ -20,6 +20,7 @@ const char* VariantName(Variant v) {
         case Variant::NvlsTwoShot: return "nvls2";
         case Variant::FlashPull: return "flash_pull";
         case Variant::StreamDirect: return "stream_direct";
+        case Variant::CopyEngine: return "copy_engine";
     }
     return "?";
 }
@@ -96,6 +97,12 @@ uint64_t PullCrossoverBytes(int /*world*/) {
     return e >= 0 ? static_cast<uint64_t>(e) : 0;
 }
 
+uint64_t CopyEngineMinBytes(int /*world*/) {
+    // Off by size unless YALI_CE_MIN_BYTES says from where; the forced mode selects it at any size.
+    const long long e = env::GetInt("YALI_CE_MIN_BYTES", -1);
+    return e >= 0 ? static_cast<uint64_t>(e) : ~0ull;
+}
+
 void DirectPreset(uint64_t bytes, int world, bool one_shot, uint32_t sm_count, uint32_t* ctas, uint32_t* chunk_bytes,
                   uint32_t* stages) {
     // A stage holds one chunk of every rank's input.  Measured on 2 and 4 x B200: one CTA per SM is
@@ -168,6 +175,7 @@ bool ParseVariant(const std::string& v, Variant* out) {
     else if (v == "nvls2") *out = Variant::NvlsTwoShot;
     else if (v == "flash_pull") *out = Variant::FlashPull;
     else if (v == "stream_direct") *out = Variant::StreamDirect;
+    else if (v == "copy_engine") *out = Variant::CopyEngine;
     else return false;
     return true;
 }
@@ -292,6 +300,9 @@ Result MakePlan(int world, uint64_t count, Dtype in, Dtype out, int epilogue, Ke
     const bool direct_ok = !rows && world > 1 && caps.peer_send && caps.peer_recv && caps.vec_ok &&
                            !caps.half_collective;
     const bool pull_ok = direct_ok && !caps.in_place;
+    // The copy-engine path: one GPU per rank, plain sum, every rank's shard non-empty.
+    const bool ce_ok = direct_ok && caps.one_gpu_per_rank && in == out && epilogue == kEpiIdentity &&
+                       static_cast<uint64_t>(world - 1) * ShardElems(count, world) < count;
 
     Variant v;
     const TuningRow* row = (table && forced == KernelMode::Auto) ? table->Find(world, static_cast<int>(in_b), bytes)
@@ -301,6 +312,7 @@ Result MakePlan(int world, uint64_t count, Dtype in, Dtype out, int epilogue, Ke
     else if (forced == KernelMode::NVLS) v = bytes <= (128ull << 10) ? Variant::NvlsOneShot : Variant::NvlsTwoShot;
     else if (forced == KernelMode::FlashPull) v = Variant::FlashPull;
     else if (forced == KernelMode::StreamDirect) v = Variant::StreamDirect;
+    else if (forced == KernelMode::CopyEngine) v = Variant::CopyEngine;
     else if (row) v = row->variant;
     // Measured on 8 x B200 with symmetric buffers: the flag-in-data one-shot wins up to 64 KiB
     // (8.3-13.5 us against 11-15 us), the in-switch forms from 128 KiB (16 us against 16-21 us).
@@ -313,6 +325,7 @@ Result MakePlan(int world, uint64_t count, Dtype in, Dtype out, int epilogue, Ke
     else if (bytes <= (direct_ok && world == 2 ? std::min<uint64_t>(12ull << 20, FlashCrossoverBytes(in, world))
                                                : FlashCrossoverBytes(in, world)))
         v = Variant::Flash;
+    else if (ce_ok && bytes >= CopyEngineMinBytes(world)) v = Variant::CopyEngine;
     else if (nvls_ok && world > 2) v = Variant::NvlsTwoShot;
     else if (direct_ok) v = Variant::StreamDirect;
     else v = Variant::Stream;
@@ -328,6 +341,7 @@ Result MakePlan(int world, uint64_t count, Dtype in, Dtype out, int epilogue, Ke
             case Variant::Stream: return stream_ok;
             case Variant::FlashPull: return pull_ok;
             case Variant::StreamDirect: return direct_ok;
+            case Variant::CopyEngine: return ce_ok;
             default: return nvls_ok;
         }
     };
@@ -421,6 +435,25 @@ Result MakePlan(int world, uint64_t count, Dtype in, Dtype out, int epilogue, Ke
             p.ctas = std::max<uint32_t>(1, std::min<uint32_t>(std::min<uint32_t>(c, share), std::min<uint32_t>(resident, kBarSlots)));
             p.slot_bytes = chunk;
             p.stages = st;
+            if (one_shot) p.flags |= kFlagPullOneShot;
+            break;
+        }
+        case Variant::CopyEngine: {
+            // Two ranks: every rank copies the peer's whole input (S bytes per direction, one phase).
+            // More ranks: two-shot over shards.  About eight chunks per rank keep the host's work per call
+            // (six to twenty API calls per chunk) well below the time the copies take.
+            const bool one_shot = world == 2;
+            p.shard_elems = ShardElems(count, world);
+            const uint64_t region = one_shot ? bytes : p.shard_elems * in_b;
+            uint64_t chunk = std::min<uint64_t>(std::max<uint64_t>(RoundUp(CeilDiv(region, 8), 1ull << 20), 1ull << 20), 16ull << 20);
+            if (dev_slot > 0) chunk = RoundUp(static_cast<uint64_t>(dev_slot), 16);
+            chunk = std::max<uint64_t>(chunk, RoundUp(CeilDiv(region, 64), 16));  // at most 64 chunks per rank
+            p.slot_bytes = static_cast<uint32_t>(chunk);
+            p.stages = 3;  // staging slots per source
+            if (env::GetInt("YALI_DEV_STAGES", 0) > 1) p.stages = static_cast<uint32_t>(std::min<long long>(env::GetInt("YALI_DEV_STAGES", 0), 8));
+            uint32_t c = 2 * std::max<uint32_t>(caps.sm_count, 1);
+            if (dev_ctas > 0) c = dev_ctas;
+            p.ctas = std::max<uint32_t>(1, static_cast<uint32_t>(std::min<uint64_t>(c, CeilDiv(chunk, 16 * 512))));
             if (one_shot) p.flags |= kFlagPullOneShot;
             break;
         }

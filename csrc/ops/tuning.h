@@ -18,7 +18,7 @@
 
 namespace yali {
 
-enum class Variant : int { Flash = 0, Stream = 1, NvlsOneShot = 2, NvlsTwoShot = 3, FlashPull = 4, StreamDirect = 5 };
+enum class Variant : int { Flash = 0, Stream = 1, NvlsOneShot = 2, NvlsTwoShot = 3, FlashPull = 4, StreamDirect = 5, CopyEngine = 6 };
 const char* VariantName(Variant v);
 
 // What the communicator can offer for this call.
@@ -32,6 +32,7 @@ struct PlanCaps {
     bool peer_recv = false;        // every rank's recv is peer-addressable (direct all-gather possible)
     bool peer_send = false;        // every rank's send is peer-addressable (the pipelined kernels can pull it)
     bool in_place = false;         // some rank's send and recv ranges overlap
+    bool one_gpu_per_rank = false; // every rank is a process with a GPU of its own (the copy-engine path needs it)
     bool half_collective = false;  // reduce-scatter-only / all-gather-only call (ring kernel only)
     uint32_t sm_count = 148;       // SMs of the GPU (resident CTAs of the pipelined kernels)
     bool vec_ok = true;            // all pointers 16-byte aligned
@@ -68,6 +69,8 @@ int AutoCtasPerLane(bool use_flash, int lanes, uint64_t max_lane_elems, uint64_t
 
 // Largest message (bytes) for which the one-shot pull beats the two-shot direct form.
 uint64_t PullCrossoverBytes(int world);
+// Smallest message the copy-engine path takes in auto mode.
+uint64_t CopyEngineMinBytes(int world);
 // CTAs, bytes per source and stage, and stages of the pipelined kernels.
 void DirectPreset(uint64_t bytes, int world, bool one_shot, uint32_t sm_count, uint32_t* ctas, uint32_t* chunk_bytes,
                   uint32_t* stages);

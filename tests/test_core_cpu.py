@@ -96,6 +96,38 @@ def test_heap_layout(native_lib):
             assert off % 4096 == 0, (world, off)
 
 
+def test_plan_copy_engine_path(native_lib, monkeypatch):
+    """The copy-engine path: one-shot at two ranks, two-shot over shards above, at most 64 chunks per
+    rank, only for plain sums between addressable buffers of ranks that each own a GPU."""
+    lib = native_lib
+    ok = dict(peer_recv=1, peer_send=1, one_gpu_per_rank=1)
+    rc, p, _ = make_plan(lib, 2, 32 * MiB, mode=6, cp=caps(2, **ok))  # 128 MiB
+    assert rc == 0 and p.variant == 6 and p.flags & 256 and p.slot_bytes == 16 * MiB and p.stages == 3
+    rc, p, _ = make_plan(lib, 2, 32 * MiB, mode=6, cp=caps(2, in_place=1, **ok))
+    assert rc == 0 and p.variant == 6  # in place is handled by a per-chunk handshake
+    rc, p, _ = make_plan(lib, 4, 32 * MiB, mode=6, cp=caps(4, **ok))
+    assert rc == 0 and p.variant == 6 and not (p.flags & 256) and p.shard_elems == 8 * MiB and p.slot_bytes == 4 * MiB
+    rc, p, _ = make_plan(lib, 2, 1 << 30, mode=6, cp=caps(2, **ok))  # 4 GiB: the chunk grows to keep 64 chunks
+    assert rc == 0 and p.slot_bytes == 64 * MiB
+    rc, p, _ = make_plan(lib, 2, 100001, mode=6, cp=caps(2, **ok))
+    assert rc == 0 and p.slot_bytes == MiB and p.ctas >= 1
+    for bad in (dict(ok, one_gpu_per_rank=0), dict(ok, peer_send=0), dict(ok, vec_ok=0)):
+        rc, _, msg = make_plan(lib, 2, 32 * MiB, mode=6, cp=caps(2, **bad))
+        assert rc != 0 and "cannot run" in msg
+    rc, _, msg = make_plan(lib, 4, 40, mode=6, cp=caps(4, **ok))  # the last rank's shard would be empty
+    assert rc != 0
+    rc, _, msg = make_plan(lib, 2, 32 * MiB, out_dt=BF16, mode=6, cp=caps(2, **ok))
+    assert rc != 0  # no conversion on this path
+    # by size only from YALI_CE_MIN_BYTES on
+    rc, p, _ = make_plan(lib, 2, 32 * MiB, cp=caps(2, **ok))
+    assert rc == 0 and p.variant == 5
+    monkeypatch.setenv("YALI_CE_MIN_BYTES", str(64 * MiB))
+    rc, p, _ = make_plan(lib, 2, 32 * MiB, cp=caps(2, **ok))
+    assert rc == 0 and p.variant == 6
+    rc, p, _ = make_plan(lib, 2, 8 * MiB, cp=caps(2, **ok))
+    assert rc == 0 and p.variant != 6
+
+
 def test_plan_pipelined_variants_need_addressable_buffers(native_lib):
     lib = native_lib
     addressable = dict(peer_recv=1, peer_send=1)

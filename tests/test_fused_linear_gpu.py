@@ -57,7 +57,7 @@ def test_fused_linear_matches_reference(comm, T, oneshot):
         assert torch.equal(o, outs[0])
 
 
-@pytest.mark.parametrize("T", [1, 2, 16, 31, 33, 64])
+@pytest.mark.parametrize("T", [1, 2, 9, 16, 17, 31, 33, 64])
 def test_few_token_form_matches_reference(comm, T):
     """T <= 64: 128 x 32 tiles, partial rows to every rank as flag-in-data lines, every rank normalises all rows."""
     K, N = 512, 4096

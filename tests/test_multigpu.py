@@ -82,6 +82,9 @@ def test_single_process_all_variants(world):
             comm.sync()
             assert comm.last_call()["variant"] == "nvls2"
             _check([t.clone() for t in small], torch.bfloat16, world, dist=1, seed=4242)
+        # the copy-engine path is for one process per GPU only
+        with pytest.raises(RuntimeError, match="cannot run"):
+            comm.all_reduce(send, recv, mode="copy_engine")
         # one rank's buffers one element off a 16-byte boundary (cudaMalloc memory, all variants by size)
         for n in (4096, 100001, 1 << 20):
             xs, outs = [], []
@@ -151,6 +154,19 @@ def _rank_main(rank, world, port, q, scenario):
                     comm.all_reduce(s, r, mode=mode)
                 comm.sync()
                 ok &= ext.validate_sum(r, torch.float32, 1, 99, world)["mismatches"] == 0
+            # the copy-engine path: out of place, then in place with fresh data per call, several chunks per rank
+            for _ in range(3):
+                comm.all_reduce(s, r, mode="copy_engine", slot_bytes=512 << 10)
+            comm.sync()
+            ok &= comm.last_call()["variant"] == "copy_engine"
+            ok &= ext.validate_sum(r, torch.float32, 1, 99, world)["mismatches"] == 0
+            t = comm.symm_empty(n, torch.float32)
+            for rep in range(3):
+                ext.fill_random(t, 1, 300 + 10 * rep + rank)
+                comm.all_reduce(t, t, mode="copy_engine", slot_bytes=512 << 10)
+                comm.sync()
+                ok &= ext.validate_sum(t.clone(), torch.float32, 1, 300 + 10 * rep, world)["mismatches"] == 0
+                comm.barrier()  # nobody refills its buffer while a peer still reads the sums out of its own
             sh = comm.reduce_scatter(s)
             full = comm.all_gather(sh, n)
             comm.sync()

@@ -35,6 +35,7 @@ LIB_SOURCES = [
     "comm/symm_heap.cc",
     "comm/communicator.cc",
     "comm/mp_comm.cc",
+    "comm/copy_engine_path.cc",
     "ops/tuning.cc",
     "ops/buffer_ops.cc",
     "ops/host_oracle.cc",
@@ -48,6 +49,7 @@ LIB_SOURCES = [
     "kernels/stream_twoshot.cu",
     "kernels/nvls.cu",
     "kernels/direct_pipeline.cu",
+    "kernels/copy_engine.cu",
     "kernels/util_kernels.cu",
     "kernels/gemm_ar_rmsnorm.cu",
     "kernels/gemm_ar_decode.cu",

@@ -18,7 +18,7 @@ class PlanCaps(ctypes.Structure):
     _fields_ = [("flash_cap", ctypes.c_uint64), ("ring_bytes", ctypes.c_uint64), ("nvls_cap", ctypes.c_uint64),
                 ("has_multicast", ctypes.c_int), ("symmetric", ctypes.c_int), ("peer_recv", ctypes.c_int),
                 ("vec_ok", ctypes.c_int), ("max_ctas", ctypes.c_uint32), ("ll_cap", ctypes.c_uint64),
-                ("peer_send", ctypes.c_int), ("in_place", ctypes.c_int)]
+                ("peer_send", ctypes.c_int), ("in_place", ctypes.c_int), ("one_gpu_per_rank", ctypes.c_int)]
 
 
 class Plan(ctypes.Structure):
