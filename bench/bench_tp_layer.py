@@ -130,7 +130,7 @@ def main():
                 continue
             arms[label] = lambda oneshot=oneshot, nvls=nvls: comm.fused_linear_rmsnorm(
                 one(xs), one(ws), one(nw), one(res), out=one(outs), oneshot=oneshot, nvls=nvls, decode=False)
-        if T <= 64 and W > 1:  # the few-token form: hidden/32 CTAs, partial rows as flag-in-data lines
+        if T <= 64 and W > 1:  # the few-token form: 256-column tiles split along K, partial rows as flag-in-data lines
             arms["fused_decode"] = lambda: comm.fused_linear_rmsnorm(one(xs), one(ws), one(nw), one(res), out=one(outs),
                                                                      decode=True)
         # What RowParallelLinearNorm runs: the form picked by size.

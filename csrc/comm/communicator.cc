@@ -44,7 +44,7 @@ bool MakeHeapLayout(int world, uint64_t requested_total, uint64_t granularity, H
         l.ll_cap = 1 * MiB;
         off += 2ull * (world - 1) * 2 * l.ll_cap;
         l.gemm_ll_off = off;
-        l.gemm_ll_cap = 1 * MiB;  // 64 rows of 4096 bf16 as flag-in-data lines
+        l.gemm_ll_cap = 4 * MiB;  // per source rank: 64 rows of 4096 bf16 as flag-in-data lines from four K splits
         off += 2ull * world * l.gemm_ll_cap;
     }
     l.user_off = off;

@@ -4,29 +4,35 @@
 //
 // The full-size kernel (gemm_ar_rmsnorm.cu) cuts the output into 128x128 tiles, which for a
 // handful of tokens leaves N/128 = 32 CTAs streaming the weight slice and pays a release
-// fence plus a counter round trip before the reduction.  This form is built for latency:
+// fence plus a counter round trip before the reduction.  This form is built for latency.
 //
-//   * tiles are 128 (padded rows) x 32 columns, so N/32 = 128 CTAs each stream 1/128 of
-//     the weight slice: warp 0 feeds a shared-memory ring of 24 (T <= 32) or 16 stages
-//     with TMA (cp.async.bulk.tensor, 128-byte swizzle, no multicast; the box of x has 8, 16,
-//     32 or 64 rows, rows beyond T are out of bounds and arrive as zeros), warp 1 issues
-//     tcgen05.mma (M = 128, N = 32, bf16 x bf16 -> fp32) into a 32-column TMEM
-//     accumulator, and of warps 2..5 the ones whose TMEM lane quarter holds real rows
-//     read the accumulator back (tcgen05.ld).  A stage holds only the rows the box brings
-//     in: the 128-row operand the MMA reads runs on into the following stages, and what it
-//     finds there only reaches accumulator rows that nobody reads (rows are independent).
-//     That keeps a stage at 8 or 12 KiB, so the whole K extent of a 2048-deep slice is in
-//     flight at once instead of going four times round an 8-stage ring;
-//   * every row of the partial tile (32 bf16 = 64 bytes) goes to EVERY rank, this one
-//     included, as eight 16-byte lines that carry 8 bytes of payload and the 64-bit call
-//     number {data, call_lo, data, call_hi}: the flag travels in the data, so there is no
-//     release fence, no counter and no barrier between the GEMM and the reduction.  The
-//     landing zone is tile-major ([tile][row][8 lines]) and the lines pass through shared
-//     memory on their way out, so one store instruction of a warp covers 512 contiguous
-//     bytes of the peer's memory instead of 32 pieces of 16 bytes 4*N bytes apart;
+// What sets the pace of a GEMM with so few rows is the number of tcgen05.mma instructions one
+// CTA issues: measured on B200, an MMA of K = 16 costs about 90 ns whether it computes 32 or
+// 128 columns, 64 or 128 rows, and whether consecutive MMAs add into one accumulator or
+// into four (0.36 us per 64-deep k-block; a slice of K = 2048 in 128x32 tiles took 11.6 us).
+// So every MMA here computes as many columns as the instruction allows (N = 256), and the K
+// extent of a tile is split over several CTAs instead:
+//
+//   * a work item is (tile of 128 padded rows x 256 columns, K split ks of `ksplit`); with
+//     N = 4096 and K = 2048 per rank that is 16 x 8 = 128 items of four k-blocks each, one
+//     per CTA.  Warp 2 feeds a shared-memory ring with TMA (cp.async.bulk.tensor, 128-byte
+//     swizzle, no multicast; the box of x has 8, 16, 32 or 64 rows, rows beyond T are out of
+//     bounds and arrive as zeros; the box of W has 256 rows), warp 3 issues the MMAs
+//     (M = 128, N = 256, bf16 x bf16 -> fp32) into one of two 256-column TMEM accumulators.
+//     A stage holds only the rows the box of x brings in: the 128-row operand the MMA reads
+//     runs on into the following stages, and what it finds there only reaches accumulator
+//     rows that nobody reads (rows are independent);
+//   * the eight warps of TMEM lane quarters 0 and 1 read the accumulator back (tcgen05.ld,
+//     64 columns each) and send every row's partial sums to EVERY rank, this one included, as
+//     16-byte lines that carry 8 bytes of payload and the 64-bit call number {data, call_lo,
+//     data, call_hi}: the flag travels in the data, so there is no release fence, no counter
+//     and no barrier between the GEMM and the reduction.  The landing zone of a source
+//     (rank, ks) is cut into 32-column tiles ([tile][row][8 lines]) and the lines pass
+//     through shared memory on their way out, so one store instruction of a warp covers 512
+//     contiguous bytes of the peer's memory;
 //   * CTA t (t < T) then owns row t on this rank: its 512 threads poll the lines of all
-//     ranks for one 16-byte output vector each (all loads of a vector in flight together),
-//     add them in fp32 in rank order, add the residual, normalise and store the row.
+//     world x ksplit sources for one 16-byte output vector each (eight sources in flight
+//     together), add them in fp32 in source order, add the residual, normalise and store.
 // Every rank normalises all T rows for itself (one-shot), so nothing is sent back.
 //
 // Parity: none in the reference (no GEMM, no fused op, no tensor-core code there).
@@ -39,28 +45,20 @@ namespace yali {
 
 namespace {
 
-constexpr int DBM = 128, DBN = kGemmDecodeTileN, DBK = 64;
-constexpr int kDMaxStages = 24;
-constexpr uint32_t kDStageB = DBN * DBK * 2;
-// All A tiles first (a_box_rows * 128 bytes each), then all B tiles: 24 x (1..4 + 4) KiB or 16 x (8 + 4) KiB.
-// The MMA reads 128 rows (16 KiB) from the start of an A tile; past the last A tile that runs into the
-// B tiles (at least 64 KiB of them), never past the allocation.
-constexpr uint32_t kDRingBytes = 192 * 1024;
+constexpr int DBM = 128, DBN = kGemmDecodeMmaN, DBK = 64;
+constexpr int kLineTile = kGemmDecodeTileN;  // 32 columns = eight lines per row and landing tile
+constexpr int kDMaxStages = 8;
+constexpr uint32_t kDStageB = DBN * DBK * 2;  // 32 KiB
+// All A tiles first (a_box_rows * 128 bytes each), then all B tiles.  The MMA reads 128 rows (16 KiB)
+// from the start of an A tile; past the last A tile that runs into the B tiles, never past the allocation.
+constexpr uint32_t kDRingBytes = 160 * 1024;
 constexpr uint32_t kDSmemBytes = kDRingBytes + 1024;  // + slack to align the base
-// MMAs that add into one accumulator run one after the other, each for its full pipeline latency: with
-// N = 32 there is hardly any arithmetic to hide it (measured 85 ns per MMA, 0.34 us per 64-deep k-block,
-// whatever M, the tile's bytes or the depth of the ring).  The four k-steps of a k-block therefore add
-// into four accumulators of their own, which the epilogue sums.
-constexpr uint32_t kDAccs = DBK / 16;
-constexpr uint32_t kDTmemCols = 2 * kDAccs * DBN;  // two tiles in flight x four accumulators x 32 fp32 columns
+constexpr uint32_t kDTmemCols = 2 * DBN;              // two accumulators of 256 fp32 columns: all of TMEM
+constexpr int kDEpilogueWarps = 8;                    // lane quarters 0 and 1, four column groups of 64 each
 
-// D = fp32, A = B = bf16, both K-major, N at bit 17 (>>3), M at bit 24 (>>4).  M is 128, or 64 for up to
-// 16 rows: an MMA streams its M x 16 operand out of shared memory whatever N is, so with N = 32 that
-// stream sets the pace (measured 0.27 us per 64-deep k-block with M = 128), and rows 0..15 sit in TMEM
-// lanes 0..15 with either M.
-__device__ __forceinline__ uint32_t decode_idesc(uint32_t m) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(DBN >> 3) << 17) | ((m >> 4) << 24);
-}
+// D = fp32, A = B = bf16, both K-major, N at bit 17 (>>3), M at bit 24 (>>4).
+constexpr uint32_t kDIdesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(DBN >> 3) << 17) |
+                             (static_cast<uint32_t>(DBM >> 4) << 24);
 
 __device__ __forceinline__ uint64_t desc_sw128(uint32_t smem_addr) {
     uint64_t d = 0;
@@ -79,22 +77,25 @@ __device__ __forceinline__ uint4 ld_volatile16(const void* p) {
     return v;
 }
 
-// Flag-in-data landing zone on `on_rank` for the partial rows of `src`, tile-major: line
-// ((tile * T + row) * 8 + j) (16 bytes) holds columns 32 * tile + 4j .. 4j+3 of row `row`.
-__device__ __forceinline__ char* ll_landing(const GemmDecodeArgs& a, int on_rank, int src, uint32_t parity) {
-    return a.cv.heap[on_rank] + a.cv.lay.gemm_ll_off +
-           (static_cast<uint64_t>(parity) * a.cv.world + src) * a.cv.lay.gemm_ll_cap;
+// Flag-in-data landing zone on `on_rank` for the partial rows of source (rank `src`, K split `ks`),
+// cut into 32-column tiles: line ((tile * T + row) * 8 + j) (16 bytes) holds columns
+// 32 * tile + 4j .. 4j+3 of row `row`.
+__device__ __forceinline__ char* ll_landing(const GemmDecodeArgs& a, char* heap_of_rank, int src, uint32_t ks, uint32_t parity,
+                                            uint64_t split_bytes) {
+    return heap_of_rank + a.cv.lay.gemm_ll_off +
+           (static_cast<uint64_t>(parity) * a.cv.world + src) * a.cv.lay.gemm_ll_cap + static_cast<uint64_t>(ks) * split_bytes;
 }
 
 __device__ __forceinline__ void decode_body(const GemmDecodeArgs& a, const CUtensorMap* tmap_a,
                                             const CUtensorMap* tmap_b, uint32_t cta, uint32_t nctas) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t full_bar[kDMaxStages], empty_bar[kDMaxStages], tmem_full_bar[2], tmem_empty_bar[2];
-    __shared__ __align__(16) uint4 s_lines[2][32 * 8];  // per active epilogue warp: 32 rows x 8 lines, swizzled
+    __shared__ __align__(16) uint4 s_lines[kDEpilogueWarps][32 * 8];  // per epilogue warp: 32 rows x 8 lines, swizzled
     __shared__ uint32_t s_tmem;
     __shared__ int s_abort;
     __shared__ float s_red[32];
     __shared__ uint32_t s_call[2];
+    __shared__ char* s_heap[kMaxRanks];  // the heap bases, read with a run-time rank in the epilogue and the reduction
 
     const CommView& cv = a.cv;
     const int W = cv.world, r = cv.rank;
@@ -108,6 +109,7 @@ __device__ __forceinline__ void decode_body(const GemmDecodeArgs& a, const CUten
     YALI_DSTAMP(0, 0);
     if (tid < 2)
         s_call[tid] = *reinterpret_cast<volatile uint32_t*>(flag_word(cv, r, tid == 0 ? kCallGemmLLEpoch : kCallGemmLLEpochHi));
+    if (tid >= 32 && tid < 32 + kMaxRanks) s_heap[tid - 32] = cv.heap[tid - 32];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     if (tid == 0) {
         s_abort = 0;
@@ -117,13 +119,13 @@ __device__ __forceinline__ void decode_body(const GemmDecodeArgs& a, const CUten
         }
         for (int b = 0; b < 2; ++b) {
             ptx::mbar_init(&tmem_full_bar[b], 1);
-            ptx::mbar_init(&tmem_empty_bar[b], 4);  // the four epilogue warps
+            ptx::mbar_init(&tmem_empty_bar[b], kDEpilogueWarps);
         }
         ptx::mbar_fence_init();
         ptx::tma_prefetch_desc(tmap_a);
         ptx::tma_prefetch_desc(tmap_b);
     }
-    if (warp == 1) {
+    if (warp == 3) {
         ptx::tmem_alloc(&s_tmem, kDTmemCols);
         ptx::tmem_relinquish();
     }
@@ -136,37 +138,42 @@ __device__ __forceinline__ void decode_body(const GemmDecodeArgs& a, const CUten
     const uint32_t parity = lo & 1u;
     YALI_DSTAMP(1, 0);
 
-    const uint32_t ntn = a.N / DBN, kblocks = a.K / DBK;
+    const uint32_t ntn = (a.N + DBN - 1) / DBN, kblocks = a.K / DBK;
+    const uint32_t ksplit = a.ksplit, kper = a.kper;  // k-blocks [ks * kper, min(kblocks, (ks + 1) * kper)) per split
+    const uint32_t nitems = ntn * ksplit;
+    const uint64_t split_bytes = cv.lay.gemm_ll_cap >> (31 - __clz(ksplit));  // ksplit is a power of two
     // The TMA box of x holds a.a_box_rows (8, 16, 32 or 64) rows, not 128: the copy engine spends its time per
-    // 128-byte row, real or out of bounds, so a 128-row box would cost four times the B tile.
+    // 128-byte row, real or out of bounds.
     const uint32_t a_bytes = a.a_box_rows * DBK * 2;
-    const uint32_t stages = min(kDRingBytes / (a_bytes + kDStageB), static_cast<uint32_t>(kDMaxStages));  // 24 or 16
+    const uint32_t stages = min(kDRingBytes / (a_bytes + kDStageB), static_cast<uint32_t>(kDMaxStages));  // 4
     uint8_t* const smem_b = smem + stages * a_bytes;
 
-    // ------------------------------------------------------------------ phase 1: GEMM tiles [128 x 32]
-    if (warp == 0) {
+    // ------------------------------------------------------------------ phase 1: GEMM items [128 x 256 x K / ksplit]
+    if (warp == 2) {
         if (lane == 0) {
             uint32_t s = 0, round = 0;
-            for (uint32_t tile = cta; tile < ntn && !*abort_flag; tile += nctas) {
-                for (uint32_t kb = 0; kb < kblocks; ++kb) {
+            for (uint32_t item = cta; item < nitems && !*abort_flag; item += nctas) {
+                const uint32_t tile = item / ksplit, ks = item % ksplit;
+                const uint32_t kb_end = min(kblocks, (ks + 1) * kper);
+                for (uint32_t kb = ks * kper; kb < kb_end; ++kb) {
                     if (!mbar_wait_deadline(&empty_bar[s], (round & 1u) ^ 1u, deadline, abort_flag)) {
                         if (!*abort_flag) report_timeout(cv, kSiteMbar, r, cta, 11, round * stages + s);
                         *abort_flag = 1;
                         break;
                     }
                     ptx::mbar_expect_tx(&full_bar[s], a_bytes + kDStageB);
-                    // The weights come from HBM, x from L2: ask for the weights first.
                     ptx::tma_load_2d(smem_b + s * kDStageB, tmap_b, kb * DBK, tile * DBN, &full_bar[s]);
                     ptx::tma_load_2d(smem + s * a_bytes, tmap_a, kb * DBK, 0, &full_bar[s]);
                     if (++s == stages) s = 0, ++round;
                 }
-                if (tile == cta) YALI_DSTAMP(5, 0);  // all copies of the first tile requested
             }
         }
-    } else if (warp == 1) {
+    } else if (warp == 3) {
         if (lane == 0) {
             uint32_t s = 0, round = 0, it = 0;
-            for (uint32_t tile = cta; tile < ntn && !*abort_flag; tile += nctas, ++it) {
+            for (uint32_t item = cta; item < nitems && !*abort_flag; item += nctas, ++it) {
+                const uint32_t ks = item % ksplit;
+                const uint32_t kb_begin = ks * kper, kb_end = min(kblocks, (ks + 1) * kper);
                 const uint32_t b = it & 1u;
                 if (!mbar_wait_deadline(&tmem_empty_bar[b], ((it >> 1) & 1u) ^ 1u, deadline, abort_flag)) {
                     if (!*abort_flag) report_timeout(cv, kSiteMbar, r, cta, 14, it);
@@ -174,33 +181,33 @@ __device__ __forceinline__ void decode_body(const GemmDecodeArgs& a, const CUten
                     break;
                 }
                 ptx::tc_fence_after_sync();
-                const uint32_t d_tmem = tmem + b * kDAccs * DBN;
-                const uint32_t idesc = decode_idesc(a.mma_m);
-                for (uint32_t kb = 0; kb < kblocks; ++kb) {
+                const uint32_t d_tmem = tmem + b * DBN;
+                for (uint32_t kb = kb_begin; kb < kb_end; ++kb) {
                     if (!mbar_wait_deadline(&full_bar[s], round & 1u, deadline, abort_flag)) {
                         if (!*abort_flag) report_timeout(cv, kSiteMbar, r, cta, 12, round * stages + s);
                         *abort_flag = 1;
                         break;
                     }
                     ptx::tc_fence_after_sync();
-                    if (it == 0 && kb == 0) YALI_DSTAMP(6, 32);  // first stage has arrived
                     const uint64_t da = desc_sw128(ptx::smem_u32(smem + s * a_bytes));
                     const uint64_t db = desc_sw128(ptx::smem_u32(smem_b + s * kDStageB));
 #pragma unroll
                     for (int k = 0; k < DBK / 16; ++k)
-                        ptx::tc_mma_f16(d_tmem + k * DBN, da + 2 * k, db + 2 * k, idesc, kb != 0 ? 1u : 0u);
+                        ptx::tc_mma_f16(d_tmem, da + 2 * k, db + 2 * k, kDIdesc, (kb != kb_begin || k != 0) ? 1u : 0u);
                     ptx::tc_commit(&empty_bar[s]);
                     if (++s == stages) s = 0, ++round;
                 }
                 if (*abort_flag) break;
-                if (it == 0) YALI_DSTAMP(7, 32);  // all MMAs of the first tile issued
                 ptx::tc_commit(&tmem_full_bar[b]);
             }
         }
-    } else if (warp < 6) {
-        const int q = warp & 3;  // TMEM lane quarter this warp may read
+    } else if ((warp & 3) < 2) {
+        const int q = warp & 3;   // TMEM lane quarter this warp may read
+        const int g = warp >> 2;  // its 64 columns of the 256
+        const int ew = q * 4 + g;
         uint32_t it = 0;
-        for (uint32_t tile = cta; tile < ntn; tile += nctas, ++it) {
+        for (uint32_t item = cta; item < nitems; item += nctas, ++it) {
+            const uint32_t tile = item / ksplit, ks = item % ksplit;
             const uint32_t b = it & 1u;
             if (!mbar_wait_deadline(&tmem_full_bar[b], (it >> 1) & 1u, deadline, abort_flag)) {
                 if (lane == 0 && !*abort_flag) report_timeout(cv, kSiteMbar, r, cta, 13, it);
@@ -208,35 +215,31 @@ __device__ __forceinline__ void decode_body(const GemmDecodeArgs& a, const CUten
                 break;
             }
             ptx::tc_fence_after_sync();
-            if (it == 0) YALI_DSTAMP(2, 64);  // first accumulator complete
-            if (static_cast<uint32_t>(q) * 32 < a.T) {  // this quarter holds real rows
-                uint32_t v[32];
-                {
-                    const uint32_t base = tmem + b * kDAccs * DBN + (static_cast<uint32_t>(q * 32) << 16);
-                    uint32_t u[32];
-                    ptx::tmem_ld_32x32(base, v);
-                    ptx::tmem_ld_32x32(base + DBN, u);
-                    ptx::tmem_ld_wait();
+            if (it == 0) YALI_DSTAMP(2, 0);  // first accumulator complete
+            const uint32_t col0 = tile * DBN + g * 64;  // first of this warp's columns
+            const bool rows_here = static_cast<uint32_t>(q) * 32 < a.T && col0 < a.N;
+            uint32_t v[2][32];
+            if (rows_here) {
+                const uint32_t base = tmem + b * DBN + g * 64 + (static_cast<uint32_t>(q * 32) << 16);
+                ptx::tmem_ld_32x32(base, v[0]);
+                ptx::tmem_ld_32x32(base + 32, v[1]);
+                ptx::tmem_ld_wait();
+            }
+            ptx::tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(&tmem_empty_bar[b]);
+            if (it == 0) YALI_DSTAMP(5, 0);  // accumulator read back
+            if (!rows_here) continue;
+            uint4* stage = s_lines[ew];
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) + __uint_as_float(u[i]));
-#pragma unroll
-                    for (int h = 2; h < static_cast<int>(kDAccs); ++h) {
-                        ptx::tmem_ld_32x32(base + h * DBN, u);
-                        ptx::tmem_ld_wait();
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) + __uint_as_float(u[i]));
-                    }
-                }
-                ptx::tc_fence_before_sync();
-                __syncwarp();
-                if (lane == 0) ptx::mbar_arrive(&tmem_empty_bar[b]);
+            for (int h = 0; h < 2; ++h) {
+                if (col0 + h * 32 >= a.N) break;
                 // 32 fp32 -> 32 bf16 -> eight lines {2 bf16, call_lo, 2 bf16, call_hi}, lane = row; through
                 // shared memory (line j of row at j ^ (row & 7)) they come back as lane = (row % 4, line).
-                uint4* stage = s_lines[q];
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
-                    const __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]));
-                    const __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+                    const __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(v[h][4 * j]), __uint_as_float(v[h][4 * j + 1]));
+                    const __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(v[h][4 * j + 2]), __uint_as_float(v[h][4 * j + 3]));
                     stage[lane * 8 + (j ^ (lane & 7))] = make_uint4(*reinterpret_cast<const uint32_t*>(&h0), lo,
                                                                    *reinterpret_cast<const uint32_t*>(&h1), hi);
                 }
@@ -247,30 +250,29 @@ __device__ __forceinline__ void decode_body(const GemmDecodeArgs& a, const CUten
                     const int rl = i * 4 + (lane >> 3);
                     mine[i] = stage[rl * 8 + ((lane & 7) ^ (rl & 7))];
                 }
-                __syncwarp();  // the next tile may overwrite the staging lines
-                // This warp's rows of this tile are one contiguous block of the landing zone.
-                const uint64_t block = (static_cast<uint64_t>(tile) * a.T + static_cast<uint64_t>(q) * 32) * 128;
+                __syncwarp();  // the next half may overwrite the staging lines
+                if (it == 0 && h == 0) YALI_DSTAMP(7, 0);  // first half packed and transposed
+                // This warp's rows of this 32-column tile are one contiguous block of the landing zone.
+                const uint32_t ltile = (col0 + h * 32) / kLineTile;
+                const uint64_t block = (static_cast<uint64_t>(ltile) * a.T + static_cast<uint64_t>(q) * 32) * 128;
                 for (int k = 0; k < W; ++k) {
                     const int d = (r + k) % W;  // own copy first, then the right-hand neighbour
-                    char* dst = ll_landing(a, d, r, parity) + block + lane * 16;
+                    char* dst = ll_landing(a, s_heap[d], r, ks, parity, split_bytes) + block + lane * 16;
 #pragma unroll
                     for (int i = 0; i < 8; ++i)
                         if (static_cast<uint32_t>(q * 32 + i * 4 + (lane >> 3)) < a.T) ptx::st_v4(dst + i * 512, mine[i]);
                 }
-            } else {
-                ptx::tc_fence_before_sync();
-                __syncwarp();
-                if (lane == 0) ptx::mbar_arrive(&tmem_empty_bar[b]);
             }
         }
     }
 
     // TMEM is not needed any more (also on the abort path).
+    YALI_DSTAMP(6, 0);  // this warp's pushes issued
     ptx::tc_fence_before_sync();
     __syncthreads();
-    if (warp == 1) ptx::tmem_dealloc(tmem, kDTmemCols);
+    if (warp == 3) ptx::tmem_dealloc(tmem, kDTmemCols);
     if (s_abort) return;
-    YALI_DSTAMP(3, 0);  // all tiles of this CTA pushed
+    YALI_DSTAMP(3, 0);  // all items of this CTA pushed
 
     // ------------------------------------------------------------------ phase 2: rows, all threads
     constexpr int VEC = 8;  // bf16 per 16 bytes
@@ -279,54 +281,58 @@ __device__ __forceinline__ void decode_body(const GemmDecodeArgs& a, const CUten
     char* res_out = static_cast<char*>(a.residual_out);
     const char* wgt = static_cast<const char*>(a.norm_weight);
     const float inv_n = 1.f / static_cast<float>(a.N);
-    const int nt = blockDim.x;
+    const uint32_t nsrc = static_cast<uint32_t>(W) * ksplit;  // source s = rank s / ksplit, K split s % ksplit
+    const char* const landing0 = s_heap[r] + cv.lay.gemm_ll_off + static_cast<uint64_t>(parity) * W * cv.lay.gemm_ll_cap;
     for (uint32_t row = cta; row < a.T; row += nctas) {
-        float f[kGemmDecodeVecPerThread][VEC];
+        float f[VEC];
         float ss = 0.f;
         bool timed_out = false;
+        const uint32_t c = tid;
 #pragma unroll
-        for (int j = 0; j < kGemmDecodeVecPerThread; ++j) {
-            const uint32_t c = tid + j * nt;
-            if (c < vec_per_row && !timed_out) {
-                // Output vector c = columns 8c..8c+7 = lines 2 (c % 4) and the next of tile c / 4, from every rank.
-                const uint64_t off = ((static_cast<uint64_t>(c >> 2) * a.T + row) * 8 + (c & 3u) * 2) * 16;
-                uint4 l0[kMaxRanks], l1[kMaxRanks];
-                uint32_t pending = (1u << W) - 1u, polls = 0;
-                const uint4 rv = res ? ptx::ld_cg_v4(res + (static_cast<uint64_t>(row) * a.N + static_cast<uint64_t>(c) * VEC) * 2)
-                                     : make_uint4(0, 0, 0, 0);
+        for (int i = 0; i < VEC; ++i) f[i] = 0.f;
+        if (c < vec_per_row) {
+            // Output vector c = columns 8c..8c+7 = lines 2 (c % 4) and the next of 32-column tile c / 4, from every source.
+            const uint64_t off = ((static_cast<uint64_t>(c >> 2) * a.T + row) * 8 + (c & 3u) * 2) * 16;
+            const uint4 rv = res ? ptx::ld_cg_v4(res + (static_cast<uint64_t>(row) * a.N + static_cast<uint64_t>(c) * VEC) * 2)
+                                 : make_uint4(0, 0, 0, 0);
+            for (uint32_t s0 = 0; s0 < nsrc && !timed_out; s0 += 8) {
+                const uint32_t n = min(8u, nsrc - s0);
+                uint4 l0[8], l1[8];
+                uint32_t pending = (1u << n) - 1u, polls = 0;
                 while (pending) {
 #pragma unroll
-                    for (int q = 0; q < kMaxRanks; ++q) {
-                        if (q < W && (pending >> q & 1u)) {
-                            const char* p = ll_landing(a, r, q, parity) + off;
+                    for (int q = 0; q < 8; ++q) {
+                        if (static_cast<uint32_t>(q) < n && (pending >> q & 1u)) {
+                            const char* p = landing0 + static_cast<uint64_t>(s0 + q) * split_bytes + off;
                             l0[q] = ld_volatile16(p);
                             l1[q] = ld_volatile16(p + 16);
                         }
                     }
 #pragma unroll
-                    for (int q = 0; q < kMaxRanks; ++q) {
-                        if (q < W && (pending >> q & 1u) && l0[q].y == lo && l0[q].w == hi && l1[q].y == lo && l1[q].w == hi)
+                    for (int q = 0; q < 8; ++q) {
+                        if (static_cast<uint32_t>(q) < n && (pending >> q & 1u) && l0[q].y == lo && l0[q].w == hi &&
+                            l1[q].y == lo && l1[q].w == hi)
                             pending &= ~(1u << q);
                     }
                     if (pending && (++polls & 63u) == 0u && (*abort_flag || ptx::globaltimer() > deadline)) {
-                        if (!*abort_flag) report_timeout(cv, kSiteGemmPartials, __ffs(pending) - 1, cta, lo, 0u);
+                        if (!*abort_flag) report_timeout(cv, kSiteGemmPartials, (s0 + __ffs(pending) - 1) / ksplit, cta, lo, 0u);
                         timed_out = true;
                         break;
                     }
                 }
-#pragma unroll
-                for (int i = 0; i < VEC; ++i) f[j][i] = 0.f;
                 if (!timed_out) {
 #pragma unroll
-                    for (int q = 0; q < kMaxRanks; ++q)
-                        if (q < W) accumulate<__nv_bfloat16>(f[j], make_uint4(l0[q].x, l0[q].z, l1[q].x, l1[q].z));
-                    if (res) accumulate<__nv_bfloat16>(f[j], rv);
-                    if (res_out)
-                        ptx::st_v4(res_out + (static_cast<uint64_t>(row) * a.N + static_cast<uint64_t>(c) * VEC) * 2,
-                                   pack16<__nv_bfloat16>(f[j]));
-#pragma unroll
-                    for (int i = 0; i < VEC; ++i) ss += f[j][i] * f[j][i];
+                    for (int q = 0; q < 8; ++q)
+                        if (static_cast<uint32_t>(q) < n) accumulate<__nv_bfloat16>(f, make_uint4(l0[q].x, l0[q].z, l1[q].x, l1[q].z));
                 }
+            }
+            if (!timed_out) {
+                if (res) accumulate<__nv_bfloat16>(f, rv);
+                if (res_out)
+                    ptx::st_v4(res_out + (static_cast<uint64_t>(row) * a.N + static_cast<uint64_t>(c) * VEC) * 2,
+                               pack16<__nv_bfloat16>(f));
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) ss += f[i] * f[i];
             }
         }
         if (__syncthreads_or(timed_out ? 1 : 0)) {
@@ -334,19 +340,15 @@ __device__ __forceinline__ void decode_body(const GemmDecodeArgs& a, const CUten
             break;
         }
         const float inv_rms = rsqrtf(block_sum(ss, s_red) * inv_n + a.eps);
+        if (c < vec_per_row) {
+            float w[VEC];
 #pragma unroll
-        for (int j = 0; j < kGemmDecodeVecPerThread; ++j) {
-            const uint32_t c = tid + j * nt;
-            if (c < vec_per_row) {
-                float w[VEC];
+            for (int i = 0; i < VEC; ++i) w[i] = 0.f;
+            accumulate<__nv_bfloat16>(w, *reinterpret_cast<const uint4*>(wgt + static_cast<uint64_t>(c) * 16));
 #pragma unroll
-                for (int i = 0; i < VEC; ++i) w[i] = 0.f;
-                accumulate<__nv_bfloat16>(w, *reinterpret_cast<const uint4*>(wgt + static_cast<uint64_t>(c) * 16));
-#pragma unroll
-                for (int i = 0; i < VEC; ++i) f[j][i] = f[j][i] * inv_rms * w[i];
-                ptx::st_v4(static_cast<char*>(a.out) + (static_cast<uint64_t>(row) * a.N + static_cast<uint64_t>(c) * VEC) * 2,
-                           pack16<__nv_bfloat16>(f[j]));
-            }
+            for (int i = 0; i < VEC; ++i) f[i] = f[i] * inv_rms * w[i];
+            ptx::st_v4(static_cast<char*>(a.out) + (static_cast<uint64_t>(row) * a.N + static_cast<uint64_t>(c) * VEC) * 2,
+                       pack16<__nv_bfloat16>(f));
         }
     }
     __syncthreads();

@@ -7,12 +7,15 @@
 // [N, K] (this rank's slice of the row-parallel weight, K contiguous, the layout of
 // torch.nn.Linear.weight), both bf16; the sum runs over the ranks.
 //
-// Phase 1 (GEMM): a persistent grid (one 11-warp CTA per SM) walks 128x128 output
-// tiles, warp-specialised.  Warp 0 feeds a 5-stage shared-memory pipeline with TMA
+// Phase 1 (GEMM): a persistent grid (one 11-warp CTA per SM) walks 128x256 output
+// tiles, warp-specialised.  Warp 0 feeds a 4-stage shared-memory pipeline with TMA
 // (cp.async.bulk.tensor, 128-byte swizzle, no multicast); warp 1 issues tcgen05.mma
-// (bf16 x bf16 -> fp32) into one of two 128-column TMEM accumulators and signals
-// stage release and accumulator completion through tcgen05.commit on mbarriers;
-// warps 2..9 (two per TMEM lane quarter, each taking half of the columns) read a
+// (bf16 x bf16 -> fp32, M = 128, N = 256: an MMA of K = 16 was measured at about 90 ns
+// whether it computes 32 or 128 columns, so the widest instruction halves the GEMM
+// phase of 128-column tiles) into one of two 256-column TMEM accumulators (all of
+// TMEM) and signals stage release and accumulator completion through tcgen05.commit
+// on mbarriers; warps 2..9 (two per TMEM lane quarter, each taking half of the columns
+// in two passes of 64) read a
 // finished accumulator back with tcgen05.ld while the next tile's MMAs run into the
 // other one, round to bf16, transpose through swizzled shared memory and PUSH every
 // row straight into the landing zone of the rank that owns that row (peer stores
@@ -49,13 +52,15 @@ namespace yali {
 namespace {
 
 constexpr int BM = kGemmTileM, BN = kGemmTileN, BK = 64;  // BK bf16 = one 128-byte swizzle row
-constexpr int kStages = 5;
+constexpr int kStages = 4;
 constexpr int kEpilogueWarps = 8;  // two per TMEM lane quarter, each takes half of the tile's columns
 constexpr uint32_t kStageABytes = BM * BK * 2, kStageBBytes = BN * BK * 2;
 constexpr uint32_t kStageBytes = kStageABytes + kStageBBytes;
-constexpr uint32_t kEpiStageBytes = kEpilogueWarps * 32 * (BN / 2) * 2;  // transposition buffers of the epilogue warps
+constexpr int kEpiPassCols = 64;  // columns an epilogue warp moves per pass: 128 bytes of bf16 per row
+constexpr uint32_t kEpiStageBytes = kEpilogueWarps * 32 * kEpiPassCols * 2;  // transposition buffers of the epilogue warps
 constexpr uint32_t kSmemBytes = kStages * kStageBytes + kEpiStageBytes + 1024;  // + slack to align the base
-constexpr uint32_t kTmemCols = 256;  // two accumulators of BN fp32 columns
+constexpr uint32_t kTmemCols = 2 * BN;  // two accumulators of BN fp32 columns
+static_assert(kTmemCols == 512 && kSmemBytes <= 227 * 1024, "one CTA per SM: all of TMEM, at most 227 KiB of shared memory");
 
 // tcgen05 instruction descriptor: D = fp32, A = B = bf16, both K-major, N at bit 17 (>>3), M at bit 24 (>>4).
 constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) |
@@ -148,7 +153,7 @@ __device__ __forceinline__ void gemm_ar_body(const GemmArArgs& a, const CUtensor
     const uint32_t tmem = s_tmem;
     YALI_STAMP(1, 0);  // barriers initialised, TMEM allocated
 
-    const uint32_t ntm = (a.T + BM - 1) / BM, ntn = a.N / BN, kblocks = a.K / BK;
+    const uint32_t ntm = (a.T + BM - 1) / BM, ntn = (a.N + BN - 1) / BN, kblocks = a.K / BK;
     const uint32_t ntiles = ntm * ntn;
     const uint32_t Rs = a.rows_per_owner;
     // Two-shot: every rank starts with the row blocks owned by its right-hand neighbour and walks
@@ -238,8 +243,9 @@ __device__ __forceinline__ void gemm_ar_body(const GemmArArgs& a, const CUtensor
         }
     } else {
         const int q = warp & 3;         // TMEM lane quarter this warp may read
-        const int h = (warp - 2) >> 2;  // column half of the tile this warp handles: [64h, 64h + 64)
-        constexpr int HN = BN / 2;      // 64 columns = 128 bytes of bf16 per row
+        const int h = (warp - 2) >> 2;  // column half of the tile this warp handles: [128h, 128h + 128)
+        constexpr int HN = kEpiPassCols;  // 64 columns = 128 bytes of bf16 per row and pass
+        constexpr int kPasses = BN / 2 / HN;
         uint8_t* stage = smem + kStages * kStageBytes + (warp - 2) * (32 * HN * 2);  // 32 rows x 128 bytes per warp
         uint32_t it = 0;
         for (uint32_t tile = cta; tile < ntiles; tile += nctas, ++it) {
@@ -251,50 +257,57 @@ __device__ __forceinline__ void gemm_ar_body(const GemmArArgs& a, const CUtensor
             }
             ptx::tc_fence_after_sync();
             if (it == 0) YALI_STAMP(2, 64);  // first accumulator complete
-            // Warps whose 32 rows lie entirely beyond T (small batches) have nothing to read back.
-            const bool warp_has_rows = mt * BM + q * 32 < a.T;
+            // Warps whose 32 rows lie entirely beyond T (small batches) or whose columns lie beyond N (the
+            // last tile of an N that is not a multiple of 256) have nothing to read back.
+            const bool warp_has_rows = mt * BM + q * 32 < a.T && nt * BN + h * (BN / 2) < a.N;
 #pragma unroll
-            for (int c = 0; c < HN / 32; ++c) {
-                if (!warp_has_rows) break;
-                uint32_t v[32];
-                ptx::tmem_ld_32x32(tmem + b * BN + (static_cast<uint32_t>(q * 32) << 16) + h * HN + c * 32, v);
-                ptx::tmem_ld_wait();
-                if (mt * BM + q * 32 + lane >= a.T) continue;  // this lane's row is padding
+            for (int p = 0; p < kPasses; ++p) {
+                const int cb = h * (BN / 2) + p * HN;  // first column of this pass inside the tile
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {  // 4 chunks of 8 columns = 16 bytes of bf16
-                    float f[8];
+                for (int c = 0; c < HN / 32; ++c) {
+                    if (!warp_has_rows) break;
+                    uint32_t v[32];
+                    ptx::tmem_ld_32x32(tmem + b * BN + (static_cast<uint32_t>(q * 32) << 16) + cb + c * 32, v);
+                    ptx::tmem_ld_wait();
+                    if (mt * BM + q * 32 + lane >= a.T) continue;  // this lane's row is padding
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(v[j * 8 + i]);
-                    const int chunk = c * 4 + j;  // logical 16-byte chunk of the 128-byte row
-                    *reinterpret_cast<uint4*>(stage + lane * (HN * 2) + ((chunk ^ (lane & 7)) << 4)) =
-                        pack16<__nv_bfloat16>(f);
-                }
-            }
-            // The accumulator half is in shared memory now: hand it back to the MMA warp.
-            ptx::tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(&tmem_empty_bar[b]);
-            const int rsub = lane >> 3, c16 = lane & 7;  // four rows per step, eight 16-byte chunks per row
-#pragma unroll 4
-            for (int rr = 0; rr < 32; rr += 4) {
-                const int row_in_warp = rr + rsub;
-                const uint32_t grow = mt * BM + q * 32 + row_in_warp;  // global row
-                if (grow < a.T) {
-                    const uint4 x = *reinterpret_cast<const uint4*>(stage + row_in_warp * (HN * 2) +
-                                                                    ((c16 ^ (row_in_warp & 7)) << 4));
-                    const uint64_t col_off = (static_cast<uint64_t>(nt) * BN + h * HN) * 2 + c16 * 16;
-                    if (a.nvls) {
-                        ptx::st_v4(cv.heap[r] + landing_nvls_off(a, parity) + static_cast<uint64_t>(grow) * a.N * 2 + col_off, x);
-                    } else if (a.oneshot) {
-                        for (int k = 0; k < W; ++k) {
-                            const int d = (r + k) % W;
-                            ptx::st_v4(landing(a, d, r, parity) + static_cast<uint64_t>(grow) * a.N * 2 + col_off, x);
-                        }
-                    } else {
-                        const int d = grow / Rs;
-                        ptx::st_v4(landing(a, d, r, parity) + static_cast<uint64_t>(grow - d * Rs) * a.N * 2 + col_off, x);
+                    for (int j = 0; j < 4; ++j) {  // 4 chunks of 8 columns = 16 bytes of bf16
+                        float f[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(v[j * 8 + i]);
+                        const int chunk = c * 4 + j;  // logical 16-byte chunk of the 128-byte row
+                        *reinterpret_cast<uint4*>(stage + lane * (HN * 2) + ((chunk ^ (lane & 7)) << 4)) =
+                            pack16<__nv_bfloat16>(f);
                     }
                 }
+                ptx::tc_fence_before_sync();
+                __syncwarp();
+                // After the last pass the accumulator half is out of TMEM: hand it back to the MMA warp.
+                if (p == kPasses - 1 && lane == 0) ptx::mbar_arrive(&tmem_empty_bar[b]);
+                if (!warp_has_rows) continue;
+                const int rsub = lane >> 3, c16 = lane & 7;  // four rows per step, eight 16-byte chunks per row
+#pragma unroll 4
+                for (int rr = 0; rr < 32; rr += 4) {
+                    const int row_in_warp = rr + rsub;
+                    const uint32_t grow = mt * BM + q * 32 + row_in_warp;  // global row
+                    if (grow < a.T) {
+                        const uint4 x = *reinterpret_cast<const uint4*>(stage + row_in_warp * (HN * 2) +
+                                                                        ((c16 ^ (row_in_warp & 7)) << 4));
+                        const uint64_t col_off = (static_cast<uint64_t>(nt) * BN + cb) * 2 + c16 * 16;
+                        if (a.nvls) {
+                            ptx::st_v4(cv.heap[r] + landing_nvls_off(a, parity) + static_cast<uint64_t>(grow) * a.N * 2 + col_off, x);
+                        } else if (a.oneshot) {
+                            for (int k = 0; k < W; ++k) {
+                                const int d = (r + k) % W;
+                                ptx::st_v4(landing(a, d, r, parity) + static_cast<uint64_t>(grow) * a.N * 2 + col_off, x);
+                            }
+                        } else {
+                            const int d = grow / Rs;
+                            ptx::st_v4(landing(a, d, r, parity) + static_cast<uint64_t>(grow - d * Rs) * a.N * 2 + col_off, x);
+                        }
+                    }
+                }
+                __syncwarp();  // the next pass overwrites the transposition buffer
             }
             // This warp's pushes of the tile are issued: hand the tile to the announcer warp.  Its
             // barrier for this parity must have been consumed for the tile before last (it has, unless

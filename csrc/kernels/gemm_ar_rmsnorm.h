@@ -11,13 +11,13 @@
 namespace yali {
 
 constexpr int kGemmTileM = 128;
-constexpr int kGemmTileN = 128;
+constexpr int kGemmTileN = 256;
 constexpr int kGemmThreads = 352;  // TMA warp, MMA warp, eight epilogue warps, announcer warp
 constexpr int kGemmMaxVecPerThread = 2;  // N <= 2 * 352 threads * 8 bf16 = 5632 (the host caps N at 4096)
 
 struct alignas(64) GemmArArgs {
     CUtensorMap tmap_a;  // x  [T, K] bf16, box 64 x 128, 128-byte swizzle
-    CUtensorMap tmap_b;  // W  [N, K] bf16, box 64 x 128, 128-byte swizzle
+    CUtensorMap tmap_b;  // W  [N, K] bf16, box 64 x 256 (rows beyond N read as zeros), 128-byte swizzle
     CommView cv;
     const void* residual;     // [T, N] bf16 or nullptr
     void* residual_out;       // [T, N] bf16 or nullptr (sum + residual), this rank's copy
@@ -47,15 +47,18 @@ struct GemmArEmuArgs {
 const void* GemmArKernel(bool emu);
 uint32_t GemmArSmemBytes();
 
-// ---- few-token form (gemm_ar_decode.cu): 128 x 32 tiles, partial rows travel as flag-in-data lines
+// ---- few-token form (gemm_ar_decode.cu): 128 x 256 tiles with the K extent split over CTAs, partial rows
+// travel as flag-in-data lines in landing tiles of 32 columns
 constexpr int kGemmDecodeTileN = 32;
-constexpr int kGemmDecodeThreads = 512;       // TMA warp, MMA warp, four epilogue warps; all 16 warps reduce rows
+constexpr int kGemmDecodeMmaN = 256;
+constexpr uint32_t kGemmDecodeMaxSplit = 8;   // K splits per tile (sources per rank of the reduction)
+constexpr int kGemmDecodeThreads = 512;       // TMA warp, MMA warp, eight epilogue warps; all 16 warps reduce rows
 constexpr int kGemmDecodeVecPerThread = 1;    // N <= 512 threads * 8 bf16 = 4096
 constexpr uint32_t kGemmDecodeMaxRows = 64;   // two TMEM lane quarters
 
 struct alignas(64) GemmDecodeArgs {
     CUtensorMap tmap_a;  // x  [T, K] bf16, box 64 x a_box_rows (rows beyond T read as zeros), 128-byte swizzle
-    CUtensorMap tmap_b;  // W  [N, K] bf16, box 64 x 32, 128-byte swizzle
+    CUtensorMap tmap_b;  // W  [N, K] bf16, box 64 x 256 (rows beyond N read as zeros), 128-byte swizzle
     CommView cv;
     const void* residual;     // [T, N] bf16 or nullptr
     void* residual_out;       // [T, N] bf16 or nullptr
@@ -63,7 +66,8 @@ struct alignas(64) GemmDecodeArgs {
     void* out;                // [T, N] bf16, this rank's
     uint32_t T, N, K;
     uint32_t a_box_rows;  // rows of x one TMA copy brings in: 8, 16, 32 or 64 (the smallest that holds T)
-    uint32_t mma_m;       // rows of one MMA: 64 (T <= 16) or 128
+    uint32_t ksplit;      // CTAs that share the K extent of one 256-column tile (1, 2, 4 or 8)
+    uint32_t kper;        // k-blocks (of 64) per split: split ks takes [ks * kper, min(K / 64, (ks + 1) * kper))
     float eps;
     unsigned long long* trace;  // optional: %globaltimer of CTA 0 at the phase boundaries
 };

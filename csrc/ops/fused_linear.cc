@@ -46,7 +46,29 @@ Result LaunchDecode(Communicator& comm, const DriverApi* drv, const FusedLinearD
     // One CTA per SM (160 KiB of stages each); emulated ranks share the GPU.
     uint32_t resident = static_cast<uint32_t>(std::max(1, sms));
     if (comm.emulated()) resident = std::max<uint32_t>(1, resident / W);
-    uint32_t ctas = std::min<uint32_t>(resident, N / kGemmDecodeTileN);
+    // Work items: 256-column tiles x K splits.  An MMA of K = 16 costs about 90 ns whatever its width, so the
+    // k-blocks a CTA walks set the length of the GEMM phase (0.36 us each); every split is one more source
+    // for the reduction, which takes its sources eight at a time (about 1.8 us per eight, measured).  So:
+    // world x ksplit = 8 sources where K allows (2 x B200, K = 2048, T = 1: 13.4 us with 4 splits, 13.7 with
+    // 8, 15.5 with 2, 20.6 with 1), as long as the landing zone holds T rows per split and the items fit
+    // the resident CTAs.
+    const uint32_t ntn = (N + kGemmDecodeMmaN - 1) / kGemmDecodeMmaN, kblocks = K / 64;
+    uint32_t ksplit = 1;
+    {
+        static const long long forced = env::GetInt("YALI_GEMM_DECODE_KSPLIT", 0);  // measurements only
+        const uint32_t want = forced > 0 ? static_cast<uint32_t>(forced)
+                                         : std::max<uint32_t>(1, std::min<uint32_t>(kblocks / 4, 8u / static_cast<uint32_t>(W)));
+        while (ksplit * 2 <= std::min<uint32_t>(want, kGemmDecodeMaxSplit)) ksplit *= 2;
+        auto fits = [&](uint32_t ks) {
+            const uint32_t kper = (kblocks + ks - 1) / ks;
+            return static_cast<uint64_t>(T) * N * 4 * ks <= comm.layout().gemm_ll_cap && ntn * ks <= resident &&
+                   static_cast<uint64_t>(ks - 1) * kper < kblocks;
+        };
+        while (ksplit > 1 && !fits(ksplit)) ksplit /= 2;
+    }
+    const uint32_t kper = (kblocks + ksplit - 1) / ksplit;
+    uint32_t ctas = std::min<uint32_t>(resident, ntn * ksplit);
+    ctas = std::max<uint32_t>(ctas, std::min<uint32_t>(resident, T));  // CTA t normalises row t
     if (opt.ctas > 0) ctas = std::min<uint32_t>(ctas, opt.ctas);
     std::string derr;
     std::vector<GemmDecodeArgs> args(nlocal);
@@ -57,12 +79,11 @@ Result LaunchDecode(Communicator& comm, const DriverApi* drv, const FusedLinearD
         if (nlocal > 1) cudaSetDevice(comm.device_of(i));
         const uint32_t a_box_rows = T <= 8 ? 8u : T <= 16 ? 16u : T <= 32 ? 32u : 64u;
         if (!EncodeTileMap(drv, &a.tmap_a, d.x, T, K, a_box_rows, &derr) ||
-            !EncodeTileMap(drv, &a.tmap_b, d.w, N, K, kGemmDecodeTileN, &derr))
+            !EncodeTileMap(drv, &a.tmap_b, d.w, N, K, kGemmDecodeMmaN, &derr))
             return fail(Result::CudaError, derr);
         a.a_box_rows = a_box_rows;
-        static const long long force_m = env::GetInt("YALI_GEMM_DECODE_M", 0);  // measurements only
-        a.mma_m = force_m == 64 || force_m == 128 ? static_cast<uint32_t>(force_m) : (T <= 16 ? 64u : 128u);
-        if (T > 16) a.mma_m = 128;
+        a.ksplit = ksplit;
+        a.kper = kper;
         a.cv = comm.View(i);
         a.residual = d.residual;
         a.residual_out = d.residual_out;
@@ -137,7 +158,7 @@ uint32_t FusedLinearDecodeMaxRows(const HeapLayout& lay, uint32_t N, int world) 
 // that has rows in the tile's row block (one-shot: to everybody), and every owner reports the
 // rows it delivered.  The kernel's announcer warp applies the same rule tile by tile.
 void FusedLinearCounts(uint32_t T, uint32_t N, int W, bool oneshot, uint32_t* arrivals, uint32_t* rows_of) {
-    const uint32_t ntm = (T + kGemmTileM - 1) / kGemmTileM, ntn = N / kGemmTileN;
+    const uint32_t ntm = (T + kGemmTileM - 1) / kGemmTileM, ntn = (N + kGemmTileN - 1) / kGemmTileN;
     const uint32_t Rs = oneshot ? T : (T + W - 1) / W;
     for (int q = 0; q < W; ++q) {
         arrivals[q] = rows_of[q] = 0;
@@ -173,7 +194,7 @@ Result FusedLinearAllReduceRmsNorm(Communicator& comm, const FusedLinearDesc* de
     };
     if (comm.poisoned()) return fail(Result::Timeout, "communicator is poisoned by an earlier timeout; call Reset()");
     if (T == 0) return Result::Success;
-    if (N % kGemmTileN != 0 || N > 4096 || K % 64 != 0 || K == 0)
+    if (N % 128 != 0 || N > 4096 || K % 64 != 0 || K == 0)
         return fail(Result::Unsupported, "fused linear needs N a multiple of 128 (at most 4096) and K a multiple of 64");
     const int W = comm.world(), nlocal = comm.nlocal();
     for (int i = 0; i < nlocal; ++i) {
@@ -271,7 +292,7 @@ Result FusedLinearAllReduceRmsNorm(Communicator& comm, const FusedLinearDesc* de
     }
     const bool nvls = mc_mode == 1;
 
-    const uint32_t ntm = (T + kGemmTileM - 1) / kGemmTileM, ntn = N / kGemmTileN;
+    const uint32_t ntm = (T + kGemmTileM - 1) / kGemmTileM, ntn = (N + kGemmTileN - 1) / kGemmTileN;
     // Arrivals owner q expects from every source in this call, and rows owner q delivers.
     uint32_t arrivals[kMaxRanks] = {}, rows_of[kMaxRanks] = {};
     FusedLinearCounts(T, N, W, oneshot, arrivals, rows_of);

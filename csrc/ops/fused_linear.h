@@ -23,7 +23,7 @@ struct FusedLinearDesc {
 
 struct FusedLinearOptions {
     int force_oneshot = -1;  // -1: by size; 0: two-shot; 1: one-shot
-    // Few-token form (128 x 32 tiles on N/32 CTAs, partial rows as flag-in-data lines, every rank
+    // Few-token form (128 x 256 tiles split along K over the CTAs, partial rows as flag-in-data lines, every rank
     // normalises all rows): -1 by size (T <= FusedLinearDecodeMaxRows), 0 never, 1 required.
     int decode = -1;
     int ctas = 0;            // 0: as many as are resident

@@ -353,14 +353,14 @@ def test_fused_linear_counter_targets_match_the_kernels_announcements(native_lib
     a mismatch would end in a bounded-wait timeout on the device."""
     import ctypes
     lib = native_lib
-    BM = BN = 128
-    N = 4096
-    for T in [1, 2, 7, 16, 100, 127, 128, 129, 255, 256, 300, 1000, 1024, 2047, 2048, 4099]:
+    BM, BN = 128, 256
+    for T, N in [(t, 4096) for t in [1, 2, 7, 16, 100, 127, 128, 129, 255, 256, 300, 1000, 1024, 2047, 2048, 4099]] + \
+            [(300, 128), (300, 384), (64, 2048)]:
         for oneshot in (0, 1):
             arr = (ctypes.c_uint32 * 8)()
             rows = (ctypes.c_uint32 * 8)()
             lib.yali_c_fused_linear_counts(T, N, world, oneshot, arr, rows)
-            ntm, ntn = -(-T // BM), N // BN
+            ntm, ntn = -(-T // BM), -(-N // BN)
             rs = T if oneshot else -(-T // world)
             want = [0] * world
             for mt in range(ntm):  # the announcer's rule, tile by tile (one source)

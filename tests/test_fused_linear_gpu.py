@@ -59,7 +59,7 @@ def test_fused_linear_matches_reference(comm, T, oneshot):
 
 @pytest.mark.parametrize("T", [1, 2, 9, 16, 17, 31, 33, 64])
 def test_few_token_form_matches_reference(comm, T):
-    """T <= 64: 128 x 32 tiles, partial rows to every rank as flag-in-data lines, every rank normalises all rows."""
+    """T <= 64: 128 x 256 tiles split along K, partial rows to every rank as flag-in-data lines, every rank normalises all rows."""
     K, N = 512, 4096
     W = comm.world
     xs, ws, nw, res = make_layer(W, T, K, N, seed=100 + T)

@@ -192,7 +192,7 @@ class Comm:
         two-shot form uses the NVSwitch multicast object: None = by measurement, 0/False = not at all
         (peer pushes and peer stores), 1/True = in-switch reduce + multicast store, 2 = peer pushes +
         multicast store; 1 and 2 need the multicast object and `out` from symm_empty().  `decode`: the
-        few-token form (up to 64 rows: 128 x 32 tiles on hidden/32 CTAs, partial rows sent to every rank as
+        few-token form (up to 64 rows: 128 x 256 tiles whose K extent is split over CTAs, partial rows sent to every rank as
         flag-in-data lines, every rank normalises all rows): None = by size, False = never, True = required."""
         xs, ws, nws = self._as_list(x, "x"), self._as_list(w, "w"), self._as_list(norm_weight, "norm_weight")
         if out is None:

@@ -39,8 +39,8 @@ class RowParallelLinearNorm(nn.Module):
         x2 = x_local.reshape(-1, shape[-1])
         if x2.is_cuda:
             r2 = None if residual is None else residual.reshape(x2.shape[0], -1)
-            # One kernel per rank for every token count: up to 64 rows the few-token form (hidden/32 CTAs,
-            # flag-in-data pushes), above that the 128 x 128 tile form.  No library GEMM on this path.
+            # One kernel per rank for every token count: up to 64 rows the few-token form (256-column tiles split
+            # along K, flag-in-data pushes), above that the 128 x 256 tile form.  No library GEMM on this path.
             y = comm.fused_linear_rmsnorm(x2, self.weight, self.norm_weight, r2, eps=self.eps, out=out,
                                           residual_out=residual_out)
         else:
