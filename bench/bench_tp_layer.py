@@ -93,7 +93,10 @@ def main():
     ap.add_argument("--trace", action="store_true",
                     help="also print the in-kernel timeline of the fused arms (CTA 0 of rank 0: microseconds from "
                          "kernel entry to barriers ready, first accumulator, first tile announced, all tiles done, "
-                         "partial rows present, own rows reduced, output complete)")
+                         "partial rows present, own rows reduced, output complete; the few-token form: entry, barriers "
+                         "ready, accumulator complete, all pushes issued and CTA synchronised, rows written, first "
+                         "half of the columns stored into the own landing zone, this warp's pushes issued, first half "
+                         "packed and transposed)")
     ap.add_argument("--out", default="")
     args = ap.parse_args()
     emu = args.emulate > 0

@@ -79,6 +79,9 @@ void yali_c_oracle_allreduce(const float* const* in, int world, size_t n, double
 void yali_c_oracle_residual_rmsnorm(const double* sum, const float* residual, const float* weight, size_t rows,
                                     size_t hidden, double eps, double* y, double* pre_norm);
 // Fused linear layer: counter targets per owner (arrays of `world`), default one-shot limit and multicast form.
+/* K splits per 256-column tile of the few-token fused layer (want = 0: the measured rule). */
+uint32_t yali_c_fused_decode_split(uint32_t T, uint32_t N, uint32_t K, int world, uint32_t resident_ctas, uint64_t ll_cap,
+                                   uint32_t want);
 void yali_c_fused_linear_counts(uint32_t T, uint32_t N, int world, int oneshot, uint32_t* arrivals, uint32_t* rows_of);
 uint32_t yali_c_fused_linear_oneshot_max_rows(int world);
 int yali_c_fused_linear_multicast_mode(int world, uint32_t T);

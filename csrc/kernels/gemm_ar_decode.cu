@@ -228,7 +228,6 @@ __device__ __forceinline__ void decode_body(const GemmDecodeArgs& a, const CUten
             ptx::tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(&tmem_empty_bar[b]);
-            if (it == 0) YALI_DSTAMP(5, 0);  // accumulator read back
             if (!rows_here) continue;
             uint4* stage = s_lines[ew];
 #pragma unroll
@@ -261,6 +260,7 @@ __device__ __forceinline__ void decode_body(const GemmDecodeArgs& a, const CUten
 #pragma unroll
                     for (int i = 0; i < 8; ++i)
                         if (static_cast<uint32_t>(q * 32 + i * 4 + (lane >> 3)) < a.T) ptx::st_v4(dst + i * 512, mine[i]);
+                    if (it == 0 && h == 0 && k == 0) YALI_DSTAMP(5, 0);  // first half stored into this rank's own zone
                 }
             }
         }

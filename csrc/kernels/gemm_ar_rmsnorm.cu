@@ -86,9 +86,9 @@ __device__ __forceinline__ bool mbar_wait_deadline(uint64_t* bar, uint32_t parit
     return true;
 }
 
-__device__ __forceinline__ char* landing(const GemmArArgs& a, int on_rank, int src, uint32_t parity) {
-    return a.cv.heap[on_rank] + a.cv.lay.gemm_off +
-           (static_cast<uint64_t>(parity) * a.cv.world + src) * a.cv.lay.gemm_cap;
+// Landing zone of the partial rows of source `src` on a rank, relative to that rank's heap base.
+__device__ __forceinline__ uint64_t landing_off(const GemmArArgs& a, int src, uint32_t parity) {
+    return a.cv.lay.gemm_off + (static_cast<uint64_t>(parity) * a.cv.world + src) * a.cv.lay.gemm_cap;
 }
 
 // NVLS form: one [T, N] bf16 image per call parity at the same offset of every rank's heap.
@@ -102,6 +102,7 @@ __device__ __forceinline__ void gemm_ar_body(const GemmArArgs& a, const CUtensor
     __shared__ __align__(8) uint64_t full_bar[kStages], empty_bar[kStages], tmem_full_bar[2], tmem_empty_bar[2];
     __shared__ __align__(8) uint64_t pushed_bar[2], announced_bar[2];  // epilogue warps -> announcer warp and back
     __shared__ uint32_t s_tmem;
+    __shared__ char* s_heap[kMaxRanks];  // the heap bases: read with a run-time rank by the epilogue warps
     __shared__ volatile int s_abort;
     __shared__ float s_red[32];
 
@@ -118,6 +119,7 @@ __device__ __forceinline__ void gemm_ar_body(const GemmArArgs& a, const CUtensor
     // Call number and counter targets come from this rank's call words (advanced by the last
     // CTA of the previous launch), so the launch itself carries no per-call state.
     __shared__ uint32_t s_call[2 + kMaxRanks];
+    if (tid >= 32 && tid < 32 + kMaxRanks) s_heap[tid - 32] = cv.heap[tid - 32];
     if (tid < 2 + W) {
         const uint32_t word = tid == 0 ? kCallGemmEpoch : (tid == 1 ? kCallGemmCnt : kCallGemmDone + (tid - 2));
         s_call[tid] = *reinterpret_cast<volatile uint32_t*>(flag_word(cv, r, word));
@@ -247,9 +249,19 @@ __device__ __forceinline__ void gemm_ar_body(const GemmArArgs& a, const CUtensor
         constexpr int HN = kEpiPassCols;  // 64 columns = 128 bytes of bf16 per row and pass
         constexpr int kPasses = BN / 2 / HN;
         uint8_t* stage = smem + kStages * kStageBytes + (warp - 2) * (32 * HN * 2);  // 32 rows x 128 bytes per warp
+        const int rsub = lane >> 3, c16 = lane & 7;  // four rows per step, eight 16-byte chunks per row
+        const uint64_t rowbytes = static_cast<uint64_t>(a.N) * 2;
+        const uint64_t land_off = landing_off(a, r, parity);  // where this rank's partial rows go on every owner
         uint32_t it = 0;
         for (uint32_t tile = cta; tile < ntiles; tile += nctas, ++it) {
             const uint32_t mt = (tile / ntn + mt_shift) % ntm, nt = tile % ntn, b = it & 1u;
+            // Address arithmetic of the pushes, done while the MMAs of the tile still run.
+            const uint32_t grow0 = mt * BM + q * 32 + rsub;  // this lane's first row
+            uint32_t d0 = 0, local0 = grow0;
+            if (!a.nvls && !a.oneshot) {
+                d0 = grow0 / Rs;
+                local0 = grow0 - d0 * Rs;
+            }
             if (!mbar_wait_deadline(&tmem_full_bar[b], (it >> 1) & 1u, deadline)) {
                 if (lane == 0 && !s_abort) report_timeout(cv, kSiteMbar, r, cta, 3, it);
                 s_abort = 1;
@@ -285,25 +297,43 @@ __device__ __forceinline__ void gemm_ar_body(const GemmArArgs& a, const CUtensor
                 // After the last pass the accumulator half is out of TMEM: hand it back to the MMA warp.
                 if (p == kPasses - 1 && lane == 0) ptx::mbar_arrive(&tmem_empty_bar[b]);
                 if (!warp_has_rows) continue;
-                const int rsub = lane >> 3, c16 = lane & 7;  // four rows per step, eight 16-byte chunks per row
-#pragma unroll 4
-                for (int rr = 0; rr < 32; rr += 4) {
-                    const int row_in_warp = rr + rsub;
-                    const uint32_t grow = mt * BM + q * 32 + row_in_warp;  // global row
-                    if (grow < a.T) {
-                        const uint4 x = *reinterpret_cast<const uint4*>(stage + row_in_warp * (HN * 2) +
-                                                                        ((c16 ^ (row_in_warp & 7)) << 4));
-                        const uint64_t col_off = (static_cast<uint64_t>(nt) * BN + cb) * 2 + c16 * 16;
-                        if (a.nvls) {
-                            ptx::st_v4(cv.heap[r] + landing_nvls_off(a, parity) + static_cast<uint64_t>(grow) * a.N * 2 + col_off, x);
-                        } else if (a.oneshot) {
-                            for (int k = 0; k < W; ++k) {
-                                const int d = (r + k) % W;
-                                ptx::st_v4(landing(a, d, r, parity) + static_cast<uint64_t>(grow) * a.N * 2 + col_off, x);
-                            }
-                        } else {
-                            const int d = grow / Rs;
-                            ptx::st_v4(landing(a, d, r, parity) + static_cast<uint64_t>(grow - d * Rs) * a.N * 2 + col_off, x);
+                // Lane = (row % 4, 16-byte chunk): eight steps of four rows.  A warp executes this part alone
+                // and every instruction waits for the one before it, so the loop carries pointers that grow
+                // by additions; the one division (owner of the first row) was made before the accumulator
+                // was awaited.
+                uint4 x[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int row_in_warp = i * 4 + rsub;
+                    x[i] = *reinterpret_cast<const uint4*>(stage + row_in_warp * (HN * 2) + ((c16 ^ (row_in_warp & 7)) << 4));
+                }
+                const uint64_t col_off = (static_cast<uint64_t>(nt) * BN + cb) * 2 + c16 * 16;
+                if (a.nvls) {
+                    char* p = s_heap[r] + landing_nvls_off(a, parity) + static_cast<uint64_t>(grow0) * rowbytes + col_off;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i)
+                        if (grow0 + 4 * i < a.T) ptx::st_v4(p + static_cast<uint64_t>(4 * i) * rowbytes, x[i]);
+                } else if (a.oneshot) {
+                    int d = r;
+                    for (int k = 0; k < W; ++k) {
+                        char* p = s_heap[d] + land_off + static_cast<uint64_t>(grow0) * rowbytes + col_off;
+#pragma unroll
+                        for (int i = 0; i < 8; ++i)
+                            if (grow0 + 4 * i < a.T) ptx::st_v4(p + static_cast<uint64_t>(4 * i) * rowbytes, x[i]);
+                        if (++d == W) d = 0;
+                    }
+                } else {
+                    uint32_t d = d0, local = local0;
+                    char* p = s_heap[d < static_cast<uint32_t>(W) ? d : 0] + land_off + static_cast<uint64_t>(local) * rowbytes + col_off;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        if (grow0 + 4 * i < a.T) ptx::st_v4(p, x[i]);
+                        local += 4;
+                        p += 4 * rowbytes;
+                        while (local >= Rs && d + 1 < static_cast<uint32_t>(W)) {  // the next rows belong to the next owner
+                            local -= Rs;
+                            ++d;
+                            p = s_heap[d] + land_off + static_cast<uint64_t>(local) * rowbytes + col_off;
                         }
                     }
                 }
@@ -418,7 +448,8 @@ __device__ __forceinline__ void gemm_ar_body(const GemmArArgs& a, const CUtensor
                     ++rows_done;
                 }
             }
-        } else
+        } else {
+        const char* const own_landing = s_heap[r] + landing_off(a, 0, parity);
         for (uint32_t lr = cta; lr < my_rows; lr += nctas) {
             const uint32_t grow = row_lo + lr;
             // Every load of the row (W partial vectors, residual, weight, for each of this thread's
@@ -432,7 +463,7 @@ __device__ __forceinline__ void gemm_ar_body(const GemmArArgs& a, const CUtensor
                     const uint64_t goff = (static_cast<uint64_t>(grow) * a.N + static_cast<uint64_t>(c) * VEC) * 2;
 #pragma unroll
                     for (int q = 0; q < kMaxRanks; ++q)
-                        if (q < W) part[j][q] = ptx::ld_cg_v4(landing(a, r, q, parity) + off);
+                        if (q < W) part[j][q] = ptx::ld_cg_v4(own_landing + static_cast<uint64_t>(q) * cv.lay.gemm_cap + off);  // source q
                     rv[j] = res ? ptx::ld_cg_v4(res + goff) : make_uint4(0, 0, 0, 0);
                     wv[j] = *reinterpret_cast<const uint4*>(wgt + static_cast<uint64_t>(c) * 16);
                 }
@@ -493,6 +524,7 @@ __device__ __forceinline__ void gemm_ar_body(const GemmArArgs& a, const CUtensor
                 }
             }
             ++rows_done;
+        }
         }
         YALI_STAMP(6, 0);  // own rows reduced and written
         // Two-shot: tell every rank how many of its output rows this CTA delivered.

@@ -46,26 +46,10 @@ Result LaunchDecode(Communicator& comm, const DriverApi* drv, const FusedLinearD
     // One CTA per SM (160 KiB of stages each); emulated ranks share the GPU.
     uint32_t resident = static_cast<uint32_t>(std::max(1, sms));
     if (comm.emulated()) resident = std::max<uint32_t>(1, resident / W);
-    // Work items: 256-column tiles x K splits.  An MMA of K = 16 costs about 90 ns whatever its width, so the
-    // k-blocks a CTA walks set the length of the GEMM phase (0.36 us each); every split is one more source
-    // for the reduction, which takes its sources eight at a time (about 1.8 us per eight, measured).  So:
-    // world x ksplit = 8 sources where K allows (2 x B200, K = 2048, T = 1: 13.4 us with 4 splits, 13.7 with
-    // 8, 15.5 with 2, 20.6 with 1), as long as the landing zone holds T rows per split and the items fit
-    // the resident CTAs.
     const uint32_t ntn = (N + kGemmDecodeMmaN - 1) / kGemmDecodeMmaN, kblocks = K / 64;
-    uint32_t ksplit = 1;
-    {
-        static const long long forced = env::GetInt("YALI_GEMM_DECODE_KSPLIT", 0);  // measurements only
-        const uint32_t want = forced > 0 ? static_cast<uint32_t>(forced)
-                                         : std::max<uint32_t>(1, std::min<uint32_t>(kblocks / 4, 8u / static_cast<uint32_t>(W)));
-        while (ksplit * 2 <= std::min<uint32_t>(want, kGemmDecodeMaxSplit)) ksplit *= 2;
-        auto fits = [&](uint32_t ks) {
-            const uint32_t kper = (kblocks + ks - 1) / ks;
-            return static_cast<uint64_t>(T) * N * 4 * ks <= comm.layout().gemm_ll_cap && ntn * ks <= resident &&
-                   static_cast<uint64_t>(ks - 1) * kper < kblocks;
-        };
-        while (ksplit > 1 && !fits(ksplit)) ksplit /= 2;
-    }
+    static const long long forced = env::GetInt("YALI_GEMM_DECODE_KSPLIT", 0);  // measurements only
+    const uint32_t ksplit = FusedLinearDecodeSplit(T, N, K, W, resident, comm.layout().gemm_ll_cap,
+                                                   forced > 0 ? static_cast<uint32_t>(forced) : 0u);
     const uint32_t kper = (kblocks + ksplit - 1) / ksplit;
     uint32_t ctas = std::min<uint32_t>(resident, ntn * ksplit);
     ctas = std::max<uint32_t>(ctas, std::min<uint32_t>(resident, T));  // CTA t normalises row t
@@ -144,6 +128,27 @@ bool EncodeTileMap(const DriverApi* d, CUtensorMap* map, const void* base, uint6
 }  // namespace
 
 uint32_t FusedLinearOneShotMaxRows(int world) { return world <= 2 ? 256u : 32u; }
+
+// K splits per 256-column tile of the few-token form.  An MMA of K = 16 costs about 90 ns whatever its
+// width, so the k-blocks a CTA walks set the length of the GEMM phase (0.36 us each); every split is one more
+// source for the reduction, which takes its sources eight at a time (about 1.8 us per eight, measured).  So:
+// world x ksplit = 8 sources where K allows (2 x B200, K = 2048, T = 1: 12.7 us with 4 splits, 13.2 with 8,
+// 15.5 with 2, 20.6 with 1), as long as the landing zone holds T rows per split, the work items fit the
+// resident CTAs and no split is empty.  `want` > 0 replaces the first rule (measurements).
+uint32_t FusedLinearDecodeSplit(uint32_t T, uint32_t N, uint32_t K, int world, uint32_t resident_ctas, uint64_t ll_cap,
+                                uint32_t want) {
+    const uint32_t ntn = (N + kGemmDecodeMmaN - 1) / kGemmDecodeMmaN, kblocks = K / 64;
+    if (want == 0) want = std::max<uint32_t>(1, std::min<uint32_t>(kblocks / 4, 8u / static_cast<uint32_t>(std::max(world, 1))));
+    uint32_t ksplit = 1;
+    while (ksplit * 2 <= std::min<uint32_t>(want, kGemmDecodeMaxSplit)) ksplit *= 2;
+    auto fits = [&](uint32_t ks) {
+        const uint32_t kper = (kblocks + ks - 1) / ks;
+        return static_cast<uint64_t>(T) * N * 4 * ks <= ll_cap && ntn * ks <= resident_ctas &&
+               static_cast<uint64_t>(ks - 1) * kper < kblocks;
+    };
+    while (ksplit > 1 && !fits(ksplit)) ksplit /= 2;
+    return ksplit;
+}
 
 uint32_t FusedLinearDecodeMaxRows(const HeapLayout& lay, uint32_t N, int world) {
     if (world < 2 || N == 0 || N % kGemmDecodeTileN != 0 ||

@@ -42,6 +42,9 @@ Result FusedLinearAllReduceRmsNorm(Communicator& comm, const FusedLinearDesc* de
 // Largest T the few-token form takes for rows of N elements (limited by its landing zone and by
 // the two TMEM lane quarters its epilogue reads); 0 when it cannot run.
 uint32_t FusedLinearDecodeMaxRows(const HeapLayout& lay, uint32_t N, int world);
+// K splits per 256-column tile of the few-token form (1, 2, 4 or 8); `want` = 0: by the measured rule.
+uint32_t FusedLinearDecodeSplit(uint32_t T, uint32_t N, uint32_t K, int world, uint32_t resident_ctas, uint64_t ll_cap,
+                                uint32_t want);
 // Rows from which the two-shot form is used when `force_oneshot` is -1.
 uint32_t FusedLinearOneShotMaxRows(int world);
 int FusedLinearAutoMulticastMode(int world, uint32_t T);

@@ -96,6 +96,29 @@ def test_heap_layout(native_lib):
             assert off % 4096 == 0, (world, off)
 
 
+def test_few_token_form_splits_k_to_eight_sources(native_lib):
+    """K splits per 256-column tile of the few-token fused layer: world x splits = 8 sources where K allows,
+    never more rows per split than the landing zone holds, never more work items than resident CTAs, no
+    empty split."""
+    f = native_lib.yali_c_fused_decode_split
+    cap = 4 * MiB
+    assert f(1, 4096, 2048, 2, 148, cap, 0) == 4      # TP = 2: 16 tiles x 4 splits of eight k-blocks
+    assert f(16, 4096, 1024, 4, 148, cap, 0) == 2     # TP = 4
+    assert f(16, 4096, 512, 8, 148, cap, 0) == 1      # TP = 8: eight sources already
+    assert f(64, 4096, 2048, 2, 148, cap, 0) == 4     # 64 rows x 4096 x 4 bytes x 4 splits = 4 MiB: just fits
+    assert f(64, 4096, 2048, 2, 148, 1 * MiB, 0) == 1
+    assert f(1, 4096, 2048, 2, 74, cap, 0) == 4       # two emulated ranks on one GPU: 64 items on 74 CTAs
+    assert f(1, 4096, 2048, 2, 37, cap, 0) == 2
+    assert f(1, 4096, 128, 2, 148, cap, 0) == 1       # two k-blocks: nothing to split
+    assert f(1, 4096, 2048, 2, 148, cap, 8) == 8      # forced (measurements)
+    assert f(1, 4096, 192, 2, 148, cap, 8) == 2       # three k-blocks: a third and fourth split would be empty
+    for T, N, K, W in [(5, 512, 192, 3), (40, 2048, 1024, 2), (8, 128, 64, 8), (33, 4096, 4096, 2)]:
+        ks = f(T, N, K, W, 148, cap, 0)
+        kblocks, ntn = K // 64, -(-N // 256)
+        kper = -(-kblocks // ks)
+        assert ks in (1, 2, 4, 8) and T * N * 4 * ks <= cap and ntn * ks <= 148 and (ks - 1) * kper < kblocks
+
+
 def test_plan_copy_engine_path(native_lib, monkeypatch):
     """The copy-engine path: one-shot at two ranks, two-shot over shards above, at most 64 chunks per
     rank, only for plain sums between addressable buffers of ranks that each own a GPU."""

@@ -162,9 +162,25 @@ def ptxas_report() -> str:
     return "\n".join(lines)
 
 
+def build_binaries(verbose: bool = True) -> None:
+    """The C++ benchmarks, examples and tests (build/bin).  They include the library's headers, so they are
+    rebuilt whenever one of those changed (the Makefile lists the headers as prerequisites): a binary built
+    against an older class layout crashes at its first call into the library."""
+    import shutil
+    root = CSRC.parent
+    if not shutil.which("make") or not (root / "Makefile").exists():
+        return
+    r = subprocess.run(["make", "-j8", "bench", "examples", "cpptests"], cwd=str(root), capture_output=True, text=True)
+    if verbose and r.stdout.strip():
+        print("  make bench examples cpptests: " + str(len(r.stdout.strip().splitlines())) + " step(s)")
+    if r.returncode != 0:
+        raise RuntimeError("make bench examples cpptests failed:\n" + r.stdout[-2000:] + r.stderr[-2000:])
+
+
 def build_all(verbose: bool = True) -> None:
     build_library(verbose)
     build_torch_extension(verbose)
+    build_binaries(verbose)
 
 
 if __name__ == "__main__":
