@@ -77,14 +77,9 @@ __device__ __forceinline__ uint4 ld_volatile16(const void* p) {
     return v;
 }
 
-// Flag-in-data landing zone on `on_rank` for the partial rows of source (rank `src`, K split `ks`),
-// cut into 32-column tiles: line ((tile * T + row) * 8 + j) (16 bytes) holds columns
-// 32 * tile + 4j .. 4j+3 of row `row`.
-__device__ __forceinline__ char* ll_landing(const GemmDecodeArgs& a, char* heap_of_rank, int src, uint32_t ks, uint32_t parity,
-                                            uint64_t split_bytes) {
-    return heap_of_rank + a.cv.lay.gemm_ll_off +
-           (static_cast<uint64_t>(parity) * a.cv.world + src) * a.cv.lay.gemm_ll_cap + static_cast<uint64_t>(ks) * split_bytes;
-}
+// Flag-in-data landing zone of source (rank `src`, K split `ks`) on every rank: at offset gemm_ll_off +
+// (parity * world + src) * gemm_ll_cap + ks * (gemm_ll_cap / ksplit) of the heap, cut into 32-column tiles:
+// line ((tile * T + row) * 8 + j) (16 bytes) holds columns 32 * tile + 4j .. 4j+3 of row `row`.
 
 __device__ __forceinline__ void decode_body(const GemmDecodeArgs& a, const CUtensorMap* tmap_a,
                                             const CUtensorMap* tmap_b, uint32_t cta, uint32_t nctas) {
@@ -209,6 +204,14 @@ __device__ __forceinline__ void decode_body(const GemmDecodeArgs& a, const CUten
         for (uint32_t item = cta; item < nitems; item += nctas, ++it) {
             const uint32_t tile = item / ksplit, ks = item % ksplit;
             const uint32_t b = it & 1u;
+            // Address arithmetic of the pushes, done while the MMAs still run: a warp executes its epilogue
+            // alone, every instruction waiting for the one before it, so what is left after the wait is
+            // one shared-memory load and one addition per destination.
+            const uint32_t col0 = tile * DBN + g * 64;  // first of this warp's columns
+            const uint64_t push_off = cv.lay.gemm_ll_off + (static_cast<uint64_t>(parity) * W + r) * cv.lay.gemm_ll_cap +
+                                      static_cast<uint64_t>(ks) * split_bytes + lane * 16 +
+                                      (static_cast<uint64_t>(col0 / kLineTile) * a.T + static_cast<uint64_t>(q) * 32) * 128;
+            const uint64_t half_step = static_cast<uint64_t>(a.T) * 128;  // the next 32-column landing tile
             if (!mbar_wait_deadline(&tmem_full_bar[b], (it >> 1) & 1u, deadline, abort_flag)) {
                 if (lane == 0 && !*abort_flag) report_timeout(cv, kSiteMbar, r, cta, 13, it);
                 *abort_flag = 1;
@@ -216,7 +219,6 @@ __device__ __forceinline__ void decode_body(const GemmDecodeArgs& a, const CUten
             }
             ptx::tc_fence_after_sync();
             if (it == 0) YALI_DSTAMP(2, 0);  // first accumulator complete
-            const uint32_t col0 = tile * DBN + g * 64;  // first of this warp's columns
             const bool rows_here = static_cast<uint32_t>(q) * 32 < a.T && col0 < a.N;
             uint32_t v[2][32];
             if (rows_here) {
@@ -252,15 +254,14 @@ __device__ __forceinline__ void decode_body(const GemmDecodeArgs& a, const CUten
                 __syncwarp();  // the next half may overwrite the staging lines
                 if (it == 0 && h == 0) YALI_DSTAMP(7, 0);  // first half packed and transposed
                 // This warp's rows of this 32-column tile are one contiguous block of the landing zone.
-                const uint32_t ltile = (col0 + h * 32) / kLineTile;
-                const uint64_t block = (static_cast<uint64_t>(ltile) * a.T + static_cast<uint64_t>(q) * 32) * 128;
+                int d = r;  // own copy first, then the right-hand neighbour
                 for (int k = 0; k < W; ++k) {
-                    const int d = (r + k) % W;  // own copy first, then the right-hand neighbour
-                    char* dst = ll_landing(a, s_heap[d], r, ks, parity, split_bytes) + block + lane * 16;
+                    char* dst = s_heap[d] + push_off + h * half_step;
 #pragma unroll
                     for (int i = 0; i < 8; ++i)
                         if (static_cast<uint32_t>(q * 32 + i * 4 + (lane >> 3)) < a.T) ptx::st_v4(dst + i * 512, mine[i]);
                     if (it == 0 && h == 0 && k == 0) YALI_DSTAMP(5, 0);  // first half stored into this rank's own zone
+                    if (++d == W) d = 0;
                 }
             }
         }
