@@ -10,20 +10,20 @@
 // CTA issues: measured on B200, an MMA of K = 16 costs about 90 ns whether it computes 32 or
 // 128 columns, 64 or 128 rows, and whether consecutive MMAs add into one accumulator or
 // into four (0.36 us per 64-deep k-block; a slice of K = 2048 in 128x32 tiles took 11.6 us).
-// So every MMA here computes as many columns as the instruction allows (N = 256), and the K
-// extent of a tile is split over several CTAs instead:
+// So the MMAs here are wide (N = 128, or 256 where a GPU holds few CTAs), and the K extent of a
+// tile is split over several CTAs instead:
 //
-//   * a work item is (tile of 128 padded rows x 256 columns, K split ks of `ksplit`); with
-//     N = 4096 and K = 2048 per rank that is 16 x 8 = 128 items of four k-blocks each, one
-//     per CTA.  Warp 2 feeds a shared-memory ring with TMA (cp.async.bulk.tensor, 128-byte
+//   * a work item is (tile of 128 padded rows x 128 or 256 columns, K split ks of `ksplit`);
+//     with N = 4096 and K = 2048 per rank that is 32 x 4 = 128 items of eight k-blocks each,
+//     one per CTA.  Warp 2 feeds a shared-memory ring with TMA (cp.async.bulk.tensor, 128-byte
 //     swizzle, no multicast; the box of x has 8, 16, 32 or 64 rows, rows beyond T are out of
-//     bounds and arrive as zeros; the box of W has 256 rows), warp 3 issues the MMAs
-//     (M = 128, N = 256, bf16 x bf16 -> fp32) into one of two 256-column TMEM accumulators.
+//     bounds and arrive as zeros; the box of W has as many rows as the tile has columns), warp 3
+//     issues the MMAs (M = 128, bf16 x bf16 -> fp32) into one of two TMEM accumulators.
 //     A stage holds only the rows the box of x brings in: the 128-row operand the MMA reads
 //     runs on into the following stages, and what it finds there only reaches accumulator
 //     rows that nobody reads (rows are independent);
 //   * the eight warps of TMEM lane quarters 0 and 1 read the accumulator back (tcgen05.ld,
-//     64 columns each) and send every row's partial sums to EVERY rank, this one included, as
+//     32 or 64 columns each) and send every row's partial sums to EVERY rank, this one included, as
 //     16-byte lines that carry 8 bytes of payload and the 64-bit call number {data, call_lo,
 //     data, call_hi}: the flag travels in the data, so there is no release fence, no counter
 //     and no barrier between the GEMM and the reduction.  The landing zone of a source
@@ -45,20 +45,20 @@ namespace yali {
 
 namespace {
 
-constexpr int DBM = 128, DBN = kGemmDecodeMmaN, DBK = 64;
+constexpr int DBM = 128, DBNMax = kGemmDecodeMmaN, DBK = 64;  // the tile is 128 or 256 columns wide (a.tile_n)
 constexpr int kLineTile = kGemmDecodeTileN;  // 32 columns = eight lines per row and landing tile
 constexpr int kDMaxStages = 8;
-constexpr uint32_t kDStageB = DBN * DBK * 2;  // 32 KiB
 // All A tiles first (a_box_rows * 128 bytes each), then all B tiles.  The MMA reads 128 rows (16 KiB)
 // from the start of an A tile; past the last A tile that runs into the B tiles, never past the allocation.
 constexpr uint32_t kDRingBytes = 160 * 1024;
 constexpr uint32_t kDSmemBytes = kDRingBytes + 1024;  // + slack to align the base
-constexpr uint32_t kDTmemCols = 2 * DBN;              // two accumulators of 256 fp32 columns: all of TMEM
-constexpr int kDEpilogueWarps = 8;                    // lane quarters 0 and 1, four column groups of 64 each
+constexpr uint32_t kDTmemCols = 2 * DBNMax;           // two accumulators of up to 256 fp32 columns: all of TMEM
+constexpr int kDEpilogueWarps = 8;                    // lane quarters 0 and 1, four column groups of 32 or 64 each
 
 // D = fp32, A = B = bf16, both K-major, N at bit 17 (>>3), M at bit 24 (>>4).
-constexpr uint32_t kDIdesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(DBN >> 3) << 17) |
-                             (static_cast<uint32_t>(DBM >> 4) << 24);
+__device__ __forceinline__ uint32_t decode_idesc(uint32_t n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((n >> 3) << 17) | (static_cast<uint32_t>(DBM >> 4) << 24);
+}
 
 __device__ __forceinline__ uint64_t desc_sw128(uint32_t smem_addr) {
     uint64_t d = 0;
@@ -133,6 +133,9 @@ __device__ __forceinline__ void decode_body(const GemmDecodeArgs& a, const CUten
     const uint32_t parity = lo & 1u;
     YALI_DSTAMP(1, 0);
 
+    const uint32_t DBN = a.tile_n;             // 128 or 256
+    const uint32_t kDStageB = DBN * DBK * 2;  // 16 or 32 KiB
+    const uint32_t wcols = DBN / 4;           // columns of an epilogue warp: one or two halves of 32
     const uint32_t ntn = (a.N + DBN - 1) / DBN, kblocks = a.K / DBK;
     const uint32_t ksplit = a.ksplit, kper = a.kper;  // k-blocks [ks * kper, min(kblocks, (ks + 1) * kper)) per split
     const uint32_t nitems = ntn * ksplit;
@@ -140,7 +143,7 @@ __device__ __forceinline__ void decode_body(const GemmDecodeArgs& a, const CUten
     // The TMA box of x holds a.a_box_rows (8, 16, 32 or 64) rows, not 128: the copy engine spends its time per
     // 128-byte row, real or out of bounds.
     const uint32_t a_bytes = a.a_box_rows * DBK * 2;
-    const uint32_t stages = min(kDRingBytes / (a_bytes + kDStageB), static_cast<uint32_t>(kDMaxStages));  // 4
+    const uint32_t stages = min(kDRingBytes / (a_bytes + kDStageB), static_cast<uint32_t>(kDMaxStages));  // 4 to 8
     uint8_t* const smem_b = smem + stages * a_bytes;
 
     // ------------------------------------------------------------------ phase 1: GEMM items [128 x 256 x K / ksplit]
@@ -176,7 +179,8 @@ __device__ __forceinline__ void decode_body(const GemmDecodeArgs& a, const CUten
                     break;
                 }
                 ptx::tc_fence_after_sync();
-                const uint32_t d_tmem = tmem + b * DBN;
+                const uint32_t d_tmem = tmem + b * DBNMax;
+                const uint32_t idesc = decode_idesc(DBN);
                 for (uint32_t kb = kb_begin; kb < kb_end; ++kb) {
                     if (!mbar_wait_deadline(&full_bar[s], round & 1u, deadline, abort_flag)) {
                         if (!*abort_flag) report_timeout(cv, kSiteMbar, r, cta, 12, round * stages + s);
@@ -188,7 +192,7 @@ __device__ __forceinline__ void decode_body(const GemmDecodeArgs& a, const CUten
                     const uint64_t db = desc_sw128(ptx::smem_u32(smem_b + s * kDStageB));
 #pragma unroll
                     for (int k = 0; k < DBK / 16; ++k)
-                        ptx::tc_mma_f16(d_tmem, da + 2 * k, db + 2 * k, kDIdesc, (kb != kb_begin || k != 0) ? 1u : 0u);
+                        ptx::tc_mma_f16(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb != kb_begin || k != 0) ? 1u : 0u);
                     ptx::tc_commit(&empty_bar[s]);
                     if (++s == stages) s = 0, ++round;
                 }
@@ -207,7 +211,7 @@ __device__ __forceinline__ void decode_body(const GemmDecodeArgs& a, const CUten
             // Address arithmetic of the pushes, done while the MMAs still run: a warp executes its epilogue
             // alone, every instruction waiting for the one before it, so what is left after the wait is
             // one shared-memory load and one addition per destination.
-            const uint32_t col0 = tile * DBN + g * 64;  // first of this warp's columns
+            const uint32_t col0 = tile * DBN + g * wcols;  // first of this warp's columns
             const uint64_t push_off = cv.lay.gemm_ll_off + (static_cast<uint64_t>(parity) * W + r) * cv.lay.gemm_ll_cap +
                                       static_cast<uint64_t>(ks) * split_bytes + lane * 16 +
                                       (static_cast<uint64_t>(col0 / kLineTile) * a.T + static_cast<uint64_t>(q) * 32) * 128;
@@ -222,9 +226,9 @@ __device__ __forceinline__ void decode_body(const GemmDecodeArgs& a, const CUten
             const bool rows_here = static_cast<uint32_t>(q) * 32 < a.T && col0 < a.N;
             uint32_t v[2][32];
             if (rows_here) {
-                const uint32_t base = tmem + b * DBN + g * 64 + (static_cast<uint32_t>(q * 32) << 16);
+                const uint32_t base = tmem + b * DBNMax + g * wcols + (static_cast<uint32_t>(q * 32) << 16);
                 ptx::tmem_ld_32x32(base, v[0]);
-                ptx::tmem_ld_32x32(base + 32, v[1]);
+                if (wcols > 32) ptx::tmem_ld_32x32(base + 32, v[1]);
                 ptx::tmem_ld_wait();
             }
             ptx::tc_fence_before_sync();
@@ -234,7 +238,7 @@ __device__ __forceinline__ void decode_body(const GemmDecodeArgs& a, const CUten
             uint4* stage = s_lines[ew];
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
-                if (col0 + h * 32 >= a.N) break;
+                if (h * 32 >= static_cast<int>(wcols) || col0 + h * 32 >= a.N) break;
                 // 32 fp32 -> 32 bf16 -> eight lines {2 bf16, call_lo, 2 bf16, call_hi}, lane = row; through
                 // shared memory (line j of row at j ^ (row & 7)) they come back as lane = (row % 4, line).
 #pragma unroll
@@ -254,6 +258,27 @@ __device__ __forceinline__ void decode_body(const GemmDecodeArgs& a, const CUten
                 __syncwarp();  // the next half may overwrite the staging lines
                 if (it == 0 && h == 0) YALI_DSTAMP(7, 0);  // first half packed and transposed
                 // This warp's rows of this 32-column tile are one contiguous block of the landing zone.
+                if (a.T <= 2) {
+                    // One or two rows fill 8 or 16 lanes of a store: the other lanes take the same lines to
+                    // further destinations, so one instruction serves four (two) ranks instead of one.
+                    const uint32_t lanes_per_dst = 8 * a.T, dst_per_store = 32 / lanes_per_dst;
+                    const uint32_t src_lane = lane % lanes_per_dst, slot = lane / lanes_per_dst;
+                    uint4 y;
+                    y.x = __shfl_sync(0xffffffffu, mine[0].x, src_lane);
+                    y.y = __shfl_sync(0xffffffffu, mine[0].y, src_lane);
+                    y.z = __shfl_sync(0xffffffffu, mine[0].z, src_lane);
+                    y.w = __shfl_sync(0xffffffffu, mine[0].w, src_lane);
+                    const uint64_t off = push_off - lane * 16 + src_lane * 16 + h * half_step;
+                    for (uint32_t k0 = 0; k0 < static_cast<uint32_t>(W); k0 += dst_per_store) {
+                        const uint32_t k = k0 + slot;
+                        if (k < static_cast<uint32_t>(W)) {
+                            uint32_t d = static_cast<uint32_t>(r) + k;
+                            if (d >= static_cast<uint32_t>(W)) d -= W;
+                            ptx::st_v4(s_heap[d] + off, y);
+                        }
+                    }
+                    continue;
+                }
                 int d = r;  // own copy first, then the right-hand neighbour
                 for (int k = 0; k < W; ++k) {
                     char* dst = s_heap[d] + push_off + h * half_step;

@@ -58,7 +58,7 @@ constexpr uint32_t kGemmDecodeMaxRows = 64;   // two TMEM lane quarters
 
 struct alignas(64) GemmDecodeArgs {
     CUtensorMap tmap_a;  // x  [T, K] bf16, box 64 x a_box_rows (rows beyond T read as zeros), 128-byte swizzle
-    CUtensorMap tmap_b;  // W  [N, K] bf16, box 64 x 256 (rows beyond N read as zeros), 128-byte swizzle
+    CUtensorMap tmap_b;  // W  [N, K] bf16, box 64 x tile_n (rows beyond N read as zeros), 128-byte swizzle
     CommView cv;
     const void* residual;     // [T, N] bf16 or nullptr
     void* residual_out;       // [T, N] bf16 or nullptr
@@ -66,7 +66,8 @@ struct alignas(64) GemmDecodeArgs {
     void* out;                // [T, N] bf16, this rank's
     uint32_t T, N, K;
     uint32_t a_box_rows;  // rows of x one TMA copy brings in: 8, 16, 32 or 64 (the smallest that holds T)
-    uint32_t ksplit;      // CTAs that share the K extent of one 256-column tile (1, 2, 4 or 8)
+    uint32_t tile_n;      // columns of a tile = N of the MMA and rows of the box of W: 128 or 256
+    uint32_t ksplit;      // CTAs that share the K extent of one tile (1, 2, 4 or 8)
     uint32_t kper;        // k-blocks (of 64) per split: split ks takes [ks * kper, min(K / 64, (ks + 1) * kper))
     float eps;
     unsigned long long* trace;  // optional: %globaltimer of CTA 0 at the phase boundaries

@@ -46,10 +46,14 @@ Result LaunchDecode(Communicator& comm, const DriverApi* drv, const FusedLinearD
     // One CTA per SM (160 KiB of stages each); emulated ranks share the GPU.
     uint32_t resident = static_cast<uint32_t>(std::max(1, sms));
     if (comm.emulated()) resident = std::max<uint32_t>(1, resident / W);
-    const uint32_t ntn = (N + kGemmDecodeMmaN - 1) / kGemmDecodeMmaN, kblocks = K / 64;
+    const uint32_t kblocks = K / 64;
     static const long long forced = env::GetInt("YALI_GEMM_DECODE_KSPLIT", 0);  // measurements only
+    static const long long forced_tile = env::GetInt("YALI_GEMM_DECODE_TILE", 0);
     const uint32_t ksplit = FusedLinearDecodeSplit(T, N, K, W, resident, comm.layout().gemm_ll_cap,
                                                    forced > 0 ? static_cast<uint32_t>(forced) : 0u);
+    uint32_t tile_n = FusedLinearDecodeTile(N, ksplit, resident);
+    if (forced_tile == 128 || forced_tile == 256) tile_n = static_cast<uint32_t>(forced_tile);
+    const uint32_t ntn = (N + tile_n - 1) / tile_n;
     const uint32_t kper = (kblocks + ksplit - 1) / ksplit;
     uint32_t ctas = std::min<uint32_t>(resident, ntn * ksplit);
     ctas = std::max<uint32_t>(ctas, std::min<uint32_t>(resident, T));  // CTA t normalises row t
@@ -63,9 +67,10 @@ Result LaunchDecode(Communicator& comm, const DriverApi* drv, const FusedLinearD
         if (nlocal > 1) cudaSetDevice(comm.device_of(i));
         const uint32_t a_box_rows = T <= 8 ? 8u : T <= 16 ? 16u : T <= 32 ? 32u : 64u;
         if (!EncodeTileMap(drv, &a.tmap_a, d.x, T, K, a_box_rows, &derr) ||
-            !EncodeTileMap(drv, &a.tmap_b, d.w, N, K, kGemmDecodeMmaN, &derr))
+            !EncodeTileMap(drv, &a.tmap_b, d.w, N, K, tile_n, &derr))
             return fail(Result::CudaError, derr);
         a.a_box_rows = a_box_rows;
+        a.tile_n = tile_n;
         a.ksplit = ksplit;
         a.kper = kper;
         a.cv = comm.View(i);
@@ -135,6 +140,14 @@ uint32_t FusedLinearOneShotMaxRows(int world) { return world <= 2 ? 256u : 32u; 
 // world x ksplit = 8 sources where K allows (2 x B200, K = 2048, T = 1: 12.7 us with 4 splits, 13.2 with 8,
 // 15.5 with 2, 20.6 with 1), as long as the landing zone holds T rows per split, the work items fit the
 // resident CTAs and no split is empty.  `want` > 0 replaces the first rule (measurements).
+// Width of a tile of the few-token form: an MMA costs the same for 128 and for 256 columns, so the narrower
+// tile is free for the GEMM and halves what an epilogue warp has to convert and push (32 columns instead of
+// 64, to every rank); the wide one is for GPUs that hold fewer CTAs than there are narrow work items
+// (several emulated ranks on one GPU).
+uint32_t FusedLinearDecodeTile(uint32_t N, uint32_t ksplit, uint32_t resident_ctas) {
+    return ((N + 127) / 128) * ksplit <= resident_ctas ? 128u : 256u;
+}
+
 uint32_t FusedLinearDecodeSplit(uint32_t T, uint32_t N, uint32_t K, int world, uint32_t resident_ctas, uint64_t ll_cap,
                                 uint32_t want) {
     const uint32_t ntn = (N + kGemmDecodeMmaN - 1) / kGemmDecodeMmaN, kblocks = K / 64;

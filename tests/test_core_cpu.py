@@ -111,6 +111,8 @@ def test_few_token_form_splits_k_to_eight_sources(native_lib):
     assert f(1, 4096, 2048, 2, 37, cap, 0) == 2
     assert f(1, 4096, 128, 2, 148, cap, 0) == 1       # two k-blocks: nothing to split
     assert f(1, 4096, 2048, 2, 148, cap, 8) == 8      # forced (measurements)
+    tile = native_lib.yali_c_fused_decode_tile
+    assert tile(4096, 4, 148) == 128 and tile(4096, 8, 148) == 256 and tile(4096, 1, 18) == 256 and tile(1024, 2, 74) == 128
     assert f(1, 4096, 192, 2, 148, cap, 8) == 2       # three k-blocks: a third and fourth split would be empty
     for T, N, K, W in [(5, 512, 192, 3), (40, 2048, 1024, 2), (8, 128, 64, 8), (33, 4096, 4096, 2)]:
         ks = f(T, N, K, W, 148, cap, 0)
