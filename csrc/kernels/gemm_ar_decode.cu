@@ -314,9 +314,11 @@ __device__ __forceinline__ void decode_body(const GemmDecodeArgs& a, const CUten
         float ss = 0.f;
         bool timed_out = false;
         const uint32_t c = tid;
+        uint4 wv = make_uint4(0, 0, 0, 0);  // the norm weights of this thread's columns, fetched before the wait
 #pragma unroll
         for (int i = 0; i < VEC; ++i) f[i] = 0.f;
         if (c < vec_per_row) {
+            wv = *reinterpret_cast<const uint4*>(wgt + static_cast<uint64_t>(c) * 16);
             // Output vector c = columns 8c..8c+7 = lines 2 (c % 4) and the next of 32-column tile c / 4, from every source.
             const uint64_t off = ((static_cast<uint64_t>(c >> 2) * a.T + row) * 8 + (c & 3u) * 2) * 16;
             const uint4 rv = res ? ptx::ld_cg_v4(res + (static_cast<uint64_t>(row) * a.N + static_cast<uint64_t>(c) * VEC) * 2)
@@ -370,7 +372,7 @@ __device__ __forceinline__ void decode_body(const GemmDecodeArgs& a, const CUten
             float w[VEC];
 #pragma unroll
             for (int i = 0; i < VEC; ++i) w[i] = 0.f;
-            accumulate<__nv_bfloat16>(w, *reinterpret_cast<const uint4*>(wgt + static_cast<uint64_t>(c) * 16));
+            accumulate<__nv_bfloat16>(w, wv);
 #pragma unroll
             for (int i = 0; i < VEC; ++i) f[i] = f[i] * inv_rms * w[i];
             ptx::st_v4(static_cast<char*>(a.out) + (static_cast<uint64_t>(row) * a.N + static_cast<uint64_t>(c) * VEC) * 2,
