@@ -133,6 +133,8 @@ typedef struct YaliFusedSimConfig {
     int slow_rank, single_parity;
     int timeout_ms;
     int in_switch; /* 1: partial rows stay in the producer's own image and the owner reads all ranks' images */
+    int ksplit;    /* > 0: the few-token form instead (flag-in-data lines from world x ksplit sources to every rank,
+                      CTA t sums row t; rows <= 64; flag_writes counts lines; fault 2 loses the lines of one item) */
 } YaliFusedSimConfig;
 int yali_c_simulate_fused(const YaliFusedSimConfig* cfg, YaliSimReport* rep);
 

@@ -229,6 +229,164 @@ void FusedCta(FusedShared& s, std::vector<RankStop>& stop, int r, int c) {
     }
 }
 
+// ---- the few-token form (kernels/gemm_ar_decode.cu): flag-in-data lines, no counters.
+// A line is one 64-bit word {call number, value}: the device writes 16 bytes with one store, so the
+// number and the payload arrive together.  Source (rank, K split) owns one landing zone per call
+// parity on every rank.  A work item is (column tile, K split); CTA c takes items c, c + C, ...,
+// pushes the partial of every row to every rank, then CTA t < T sums row t over all sources.
+struct DecodeShared {
+    YaliFusedSimConfig cfg;
+    int W, C;
+    uint32_t T, ntn, ks;
+    // lines[on_rank]: [parity][src rank][split][row][tile]
+    std::vector<std::unique_ptr<std::atomic<uint64_t>[]>> lines;
+    std::vector<std::unique_ptr<Cell[]>> out;  // [row][tile]
+    std::unique_ptr<std::atomic<uint32_t>[]> call_word;  // per rank: calls completed
+    std::vector<std::unique_ptr<RankBarrier>> barrier;
+    std::atomic<uint64_t> timeouts{0}, violations{0}, mismatches{0}, line_writes{0};
+    std::atomic<int> t_rank{-1}, t_peer{-1}, t_site{0};
+    std::atomic<bool> abort{false};
+    size_t Line(uint32_t parity, int src, uint32_t split, uint32_t row, uint32_t tile) const {
+        return ((((static_cast<size_t>(parity) * W + src) * ks + split) * T + row) * ntn + tile);
+    }
+};
+
+float PartialSplit(int rank, int call, uint32_t row, uint32_t nt, uint32_t split) {
+    return static_cast<float>((rank * 131 + call * 17 + row * 7 + nt * 3 + split * 29) % 251) * 0.125f - 9.0f;
+}
+
+void DecodeCta(DecodeShared& s, std::vector<RankStop>& stop, int r, int c) {
+    const int W = s.W, C = s.C;
+    const uint32_t T = s.T, ntn = s.ntn, ks = s.ks;
+    for (int call = 0; call < s.cfg.calls; ++call) {
+        if (s.cfg.fault == 1 && r == s.cfg.fault_rank && call >= s.cfg.fault_call) break;  // stops launching
+        const uint32_t number = s.call_word[r].load(std::memory_order_acquire) + 1u;  // this call, never 0
+        const uint32_t parity = s.cfg.single_parity ? 0u : (number & 1u);
+        // ---- phase 1: every row of every item of this CTA to every rank
+        for (uint32_t item = c; item < ntn * ks; item += C) {
+            const uint32_t tile = item / ks, split = item % ks;
+            if (s.cfg.fault == 2 && r == s.cfg.fault_rank && call == s.cfg.fault_call && item == static_cast<uint32_t>(c))
+                continue;  // the lines of this item are lost
+            for (int k = 0; k < W; ++k) {
+                const int d = (r + k) % W;
+                for (uint32_t row = 0; row < T; ++row) {
+                    float v = PartialSplit(r, call, row, tile, split);
+                    uint32_t bits;
+                    std::memcpy(&bits, &v, 4);
+                    s.lines[d][s.Line(parity, r, split, row, tile)].store((static_cast<uint64_t>(number) << 32) | bits,
+                                                                         std::memory_order_release);
+                    s.line_writes.fetch_add(1, std::memory_order_relaxed);
+                }
+            }
+        }
+        if (r == s.cfg.slow_rank) std::this_thread::sleep_for(std::chrono::milliseconds(2));
+        // ---- phase 2: CTA t sums row t on this rank
+        bool ok = true;
+        const auto deadline = Clock::now() + std::chrono::milliseconds(s.cfg.timeout_ms);
+        for (uint32_t row = c; ok && row < T; row += C) {
+            for (uint32_t tile = 0; ok && tile < ntn; ++tile) {
+                float sum = 0.f;
+                for (int src = 0; ok && src < W; ++src) {
+                    for (uint32_t split = 0; ok && split < ks; ++split) {
+                        std::atomic<uint64_t>& line = s.lines[r][s.Line(parity, src, split, row, tile)];
+                        uint32_t spins = 0;
+                        uint64_t w;
+                        while (static_cast<uint32_t>((w = line.load(std::memory_order_acquire)) >> 32) != number) {
+                            // A later call's number here means that the zone was reused before this reader was done.
+                            if (static_cast<int32_t>(static_cast<uint32_t>(w >> 32) - number) > 0 && (w >> 32) != 0) {
+                                s.violations.fetch_add(1);
+                                ok = false;
+                                break;
+                            }
+                            if ((++spins & 255u) == 0) {
+                                if (s.abort.load() || Clock::now() > deadline) {
+                                    if (s.timeouts.fetch_add(1) == 0) {
+                                        s.t_rank = r;
+                                        s.t_peer = src;
+                                        s.t_site = 1;
+                                    }
+                                    s.abort = true;
+                                    ok = false;
+                                    break;
+                                }
+                                std::this_thread::yield();
+                            }
+                        }
+                        if (!ok) break;
+                        const uint32_t bits = static_cast<uint32_t>(w);
+                        float v;
+                        std::memcpy(&v, &bits, 4);
+                        sum += v;
+                    }
+                }
+                if (!ok) break;
+                Cell& o = s.out[r][static_cast<size_t>(row) * ntn + tile];
+                if (o.stamp.load(std::memory_order_acquire) != 0) s.violations.fetch_add(1);  // not consumed yet
+                o.value = sum;
+                o.stamp.store(static_cast<uint64_t>(call) + 1, std::memory_order_release);
+            }
+        }
+        // ---- end of the launch: the last CTA advances the call word; the stream consumes the output
+        s.barrier[r]->wait();
+        if (c == 0) {
+            const bool aborted = s.abort.load();
+            if (!aborted) {
+                s.call_word[r].fetch_add(1, std::memory_order_release);
+                for (uint32_t row = 0; row < T; ++row)
+                    for (uint32_t tile = 0; tile < ntn; ++tile) {
+                        Cell& o = s.out[r][static_cast<size_t>(row) * ntn + tile];
+                        float want = 0.f;
+                        for (int q = 0; q < W; ++q)
+                            for (uint32_t split = 0; split < ks; ++split) want += PartialSplit(q, call, row, tile, split);
+                        if (o.stamp.load(std::memory_order_acquire) != static_cast<uint64_t>(call) + 1) s.violations.fetch_add(1);
+                        else if (std::fabs(o.value - want) > 1e-3f) s.mismatches.fetch_add(1);
+                        o.stamp.store(0, std::memory_order_release);
+                    }
+            }
+            stop[r].v.store(aborted ? 1 : 0);
+        }
+        s.barrier[r]->wait();
+        if (stop[r].v.load()) break;
+    }
+}
+
+int SimulateDecode(const YaliFusedSimConfig* cfg, YaliSimReport* rep) {
+    if (cfg->rows > yali::kGemmDecodeMaxRows || cfg->ksplit > static_cast<int>(yali::kGemmDecodeMaxSplit)) return -1;
+    DecodeShared s;
+    s.cfg = *cfg;
+    s.W = cfg->world;
+    s.C = cfg->ctas;
+    s.T = cfg->rows;
+    s.ntn = cfg->col_tiles;
+    s.ks = static_cast<uint32_t>(cfg->ksplit);
+    const size_t nlines = 2ull * s.W * s.ks * s.T * s.ntn;
+    s.call_word.reset(new std::atomic<uint32_t>[s.W]);
+    for (int r = 0; r < s.W; ++r) {
+        s.lines.emplace_back(new std::atomic<uint64_t>[nlines]);
+        for (size_t i = 0; i < nlines; ++i) s.lines[r][i].store(0);
+        s.out.emplace_back(new Cell[static_cast<size_t>(s.T) * s.ntn]);
+        s.call_word[r].store(0);
+        s.barrier.emplace_back(new RankBarrier(s.C));
+    }
+    std::vector<RankStop> stop(s.W);
+    std::vector<std::thread> threads;
+    for (int r = 0; r < s.W; ++r)
+        for (int c = 0; c < s.C; ++c) threads.emplace_back(DecodeCta, std::ref(s), std::ref(stop), r, c);
+    for (auto& t : threads) t.join();
+    rep->timeouts = s.timeouts.load();
+    rep->flag_writes = s.line_writes.load();
+    rep->timeout_rank = s.t_rank.load();
+    rep->timeout_peer = s.t_peer.load();
+    rep->timeout_site = s.t_site.load();
+    if (s.violations.load()) {
+        rep->mismatches = s.violations.load();
+        return rep->status = 3;
+    }
+    if (rep->timeouts) return rep->status = 2;
+    rep->mismatches = s.mismatches.load();
+    return rep->status = rep->mismatches ? 1 : 0;
+}
+
 }  // namespace
 
 extern "C" int yali_c_simulate_fused(const YaliFusedSimConfig* cfg, YaliSimReport* rep) {
@@ -237,6 +395,7 @@ extern "C" int yali_c_simulate_fused(const YaliFusedSimConfig* cfg, YaliSimRepor
     if (!cfg || cfg->world < 1 || cfg->world > yali::kMaxRanks || cfg->ctas < 1 || cfg->ctas > 64 || cfg->rows == 0 ||
         cfg->col_tiles == 0 || cfg->calls < 1)
         return -1;
+    if (cfg->ksplit > 0) return SimulateDecode(cfg, rep);
     FusedShared s;
     s.cfg = *cfg;
     s.W = cfg->world;

@@ -93,7 +93,7 @@ from yali_b200._native import FusedSimConfig  # noqa: E402
 
 def simulate_fused(**kw):
     cfg = FusedSimConfig(world=2, ctas=3, calls=4, oneshot=0, rows=300, col_tiles=2, fault=0, fault_rank=0,
-                         fault_call=0, slow_rank=-1, single_parity=0, timeout_ms=5000, in_switch=0)
+                         fault_call=0, slow_rank=-1, single_parity=0, timeout_ms=5000, in_switch=0, ksplit=0)
     for k, v in kw.items():
         setattr(cfg, k, v)
     rep = SimReport()
@@ -145,6 +145,39 @@ def test_fused_layer_rank_that_stops_launching_times_out_its_peers():
 def test_fused_layer_lost_announcement_times_out():
     rc, rep = simulate_fused(world=2, rows=300, calls=3, fault=2, fault_rank=0, fault_call=1, timeout_ms=300)
     assert rc == 2 and rep.timeout_peer == 0 and rep.timeout_site == 1
+
+
+# ---- few-token form of the fused layer: flag-in-data lines from world x ksplit sources, no counters ----
+@pytest.mark.parametrize("world", [2, 3, 4, 8])
+@pytest.mark.parametrize("ksplit", [1, 2, 4])
+def test_few_token_form_protocol_back_to_back_calls(world, ksplit):
+    for rows, tiles in ((1, 16), (16, 8), (64, 4)):
+        rc, rep = simulate_fused(world=world, rows=rows, col_tiles=tiles, ksplit=ksplit, calls=6, ctas=4)
+        assert rc == 0 and rep.mismatches == 0 and rep.timeouts == 0, (rows, rc, rep.mismatches, rep.timeout_site)
+        assert rep.flag_writes == 6 * world * world * ksplit * rows * tiles  # every line to every rank, once per call
+
+
+def test_few_token_form_with_a_slow_rank_needs_both_parities():
+    # The fast ranks run ahead into the next call: their lines go to the other parity and wait there.
+    rc, rep = simulate_fused(world=4, rows=16, col_tiles=8, ksplit=2, calls=10, slow_rank=2, ctas=3)
+    assert rc == 0 and rep.mismatches == 0
+    # Negative control: with one landing zone per source the next call's lines overwrite unread ones.
+    hits = 0
+    for _ in range(3):
+        rc, rep = simulate_fused(world=2, rows=64, col_tiles=8, ksplit=4, calls=10, slow_rank=1, single_parity=1, ctas=2)
+        hits += rc in (2, 3)
+    assert hits >= 1
+
+
+def test_few_token_form_failures_time_out():
+    rc, rep = simulate_fused(world=4, rows=8, col_tiles=8, ksplit=2, calls=4, fault=1, fault_rank=3, fault_call=2,
+                             timeout_ms=300)
+    assert rc == 2 and rep.timeouts >= 1 and rep.timeout_peer == 3
+    rc, rep = simulate_fused(world=2, rows=8, col_tiles=8, ksplit=2, calls=3, fault=2, fault_rank=0, fault_call=1,
+                             timeout_ms=300)
+    assert rc == 2 and rep.timeout_peer == 0
+    rc, _ = simulate_fused(world=2, rows=65, col_tiles=8, ksplit=2)  # more rows than the form takes
+    assert rc == -1
 
 
 # ---- flag-in-data form of the one-shot (mode 2): the call number travels inside every pushed word ----

@@ -39,7 +39,7 @@ class FusedSimConfig(ctypes.Structure):
                 ("rows", ctypes.c_uint32), ("col_tiles", ctypes.c_uint32),
                 ("fault", ctypes.c_int), ("fault_rank", ctypes.c_int), ("fault_call", ctypes.c_int),
                 ("slow_rank", ctypes.c_int), ("single_parity", ctypes.c_int), ("timeout_ms", ctypes.c_int),
-                ("in_switch", ctypes.c_int)]
+                ("in_switch", ctypes.c_int), ("ksplit", ctypes.c_int)]
 
 
 class SimReport(ctypes.Structure):
