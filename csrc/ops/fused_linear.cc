@@ -132,7 +132,10 @@ bool EncodeTileMap(const DriverApi* d, CUtensorMap* map, const void* base, uint6
 
 }  // namespace
 
-uint32_t FusedLinearOneShotMaxRows(int world) { return world <= 2 ? 256u : 32u; }
+// Up to how many rows every rank receives all partial rows and normalises all of them itself (one NVLink
+// phase instead of two, (W - 1) times the bytes).  Measured with 128 x 256 tiles, us one-shot / two-shot:
+// 2 ranks T = 128: 25.3 / 30.8, T = 512: 35.0 / 36.5; 4 ranks T = 128: 25.0 / 27.5, T = 512: 42.3 / 33.6.
+uint32_t FusedLinearOneShotMaxRows(int world) { return world <= 2 ? 256u : world <= 4 ? 128u : 32u; }
 
 // K splits per 256-column tile of the few-token form.  An MMA of K = 16 costs about 90 ns whatever its
 // width, so the k-blocks a CTA walks set the length of the GEMM phase (0.36 us each); every split is one more
@@ -198,8 +201,10 @@ void FusedLinearCounts(uint32_t T, uint32_t N, int W, bool oneshot, uint32_t* ar
 // 8 x B200, K = 512 per rank, N = 4096, CUDA-graph timing (us, modes 0 / 1 / 2): T = 128: 31.4 / 28.9 /
 // 29.5; T = 512: 37.4 / 36.0 / 35.6; T = 2048: 80.1 / 78.7 / 78.1.  2 x B200 (K = 2048): mode 1 loses
 // (109 against 90 us at T = 2048, the switch adds a hop and saves no bytes), mode 2 ties with mode 0.
+// 4 x B200 (K = 1024, 128 x 256 tiles): T = 512: 33.6 / 35.4 / 33.9; T = 2048: 65.9 / 73.0 / 68.6: the peer
+// pushes win or tie, so the switch is used from 8 ranks on.
 int FusedLinearAutoMulticastMode(int world, uint32_t T) {
-    if (world < 4) return 0;
+    if (world < 8) return 0;
     return T < 512 ? 1 : 2;
 }
 
