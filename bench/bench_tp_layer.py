@@ -95,7 +95,7 @@ def main():
                          "kernel entry to barriers ready, first accumulator, first tile announced, all tiles done, "
                          "partial rows present, own rows reduced, output complete; the few-token form: entry, barriers "
                          "ready, accumulator complete, all pushes issued and CTA synchronised, rows written, first "
-                         "half of the columns stored into the own landing zone, this warp's pushes issued, first half "
+                         "half of the columns stored into the first peer landing zone, this warp pushes issued, first half "
                          "packed and transposed)")
     ap.add_argument("--out", default="")
     args = ap.parse_args()

@@ -279,13 +279,13 @@ __device__ __forceinline__ void decode_body(const GemmDecodeArgs& a, const CUten
                     }
                     continue;
                 }
-                int d = r;  // own copy first, then the right-hand neighbour
+                int d = r + 1 == W ? 0 : r + 1;  // the peers first (their lines have the longer way), the own copy last
                 for (int k = 0; k < W; ++k) {
                     char* dst = s_heap[d] + push_off + h * half_step;
 #pragma unroll
                     for (int i = 0; i < 8; ++i)
                         if (static_cast<uint32_t>(q * 32 + i * 4 + (lane >> 3)) < a.T) ptx::st_v4(dst + i * 512, mine[i]);
-                    if (it == 0 && h == 0 && k == 0) YALI_DSTAMP(5, 0);  // first half stored into this rank's own zone
+                    if (it == 0 && h == 0 && k == 0) YALI_DSTAMP(5, 0);  // first half stored into the first peer's zone
                     if (++d == W) d = 0;
                 }
             }
