@@ -157,6 +157,10 @@ void yali_c_fused_linear_counts(uint32_t T, uint32_t N, int world, int oneshot, 
     FusedLinearCounts(T, N, world, oneshot != 0, arrivals, rows_of);
 }
 uint32_t yali_c_fused_linear_oneshot_max_rows(int world) { return FusedLinearOneShotMaxRows(world); }
+uint32_t yali_c_fused_tile_split(uint32_t T, uint32_t N, uint32_t K, int world, uint32_t resident_ctas, uint64_t gemm_cap,
+                                 uint32_t want) {
+    return FusedLinearTileSplit(T, N, K, world, resident_ctas, gemm_cap, want);
+}
 uint32_t yali_c_fused_decode_tile(uint32_t N, uint32_t ksplit, uint32_t resident_ctas) {
     return FusedLinearDecodeTile(N, ksplit, resident_ctas);
 }

@@ -80,6 +80,8 @@ void yali_c_oracle_residual_rmsnorm(const double* sum, const float* residual, co
                                     size_t hidden, double eps, double* y, double* pre_norm);
 // Fused linear layer: counter targets per owner (arrays of `world`), default one-shot limit and multicast form.
 /* K splits per 256-column tile of the few-token fused layer (want = 0: the measured rule). */
+uint32_t yali_c_fused_tile_split(uint32_t T, uint32_t N, uint32_t K, int world, uint32_t resident_ctas, uint64_t gemm_cap,
+                                 uint32_t want);
 uint32_t yali_c_fused_decode_tile(uint32_t N, uint32_t ksplit, uint32_t resident_ctas);
 uint32_t yali_c_fused_decode_split(uint32_t T, uint32_t N, uint32_t K, int world, uint32_t resident_ctas, uint64_t ll_cap,
                                    uint32_t want);

@@ -157,6 +157,13 @@ __device__ __forceinline__ void gemm_ar_body(const GemmArArgs& a, const CUtensor
 
     const uint32_t ntm = (a.T + BM - 1) / BM, ntn = (a.N + BN - 1) / BN, kblocks = a.K / BK;
     const uint32_t ntiles = ntm * ntn;
+    // One-shot calls of few tiles split the K extent of a tile over `ksplit` CTAs (an MMA costs the same
+    // 90 ns for every tile, so the k-blocks one CTA walks set the length of the GEMM phase): a work item is
+    // (tile, split), its partial rows land in a zone of their own (source rank r, split), and the reduction
+    // adds world x ksplit partial rows.  ksplit = 1 everywhere else.
+    const uint32_t ksplit = a.ksplit, ks_shift = 31 - __clz(ksplit), kper = a.kper;
+    const uint32_t nitems = ntiles << ks_shift;
+    const uint64_t split_cap = cv.lay.gemm_cap >> ks_shift;  // landing bytes per (source rank, split)
     const uint32_t Rs = a.rows_per_owner;
     // Two-shot: every rank starts with the row blocks owned by its right-hand neighbour and walks
     // on from there, so that at any moment the ranks push to different owners instead of all
@@ -171,9 +178,11 @@ __device__ __forceinline__ void gemm_ar_body(const GemmArArgs& a, const CUtensor
     if (warp == 0) {
         if (lane == 0) {
             uint32_t g = 0;  // k-blocks loaded so far
-            for (uint32_t tile = cta; tile < ntiles && !s_abort; tile += nctas) {
+            for (uint32_t item = cta; item < nitems && !s_abort; item += nctas) {
+                const uint32_t tile = item >> ks_shift, split = item & (ksplit - 1);
                 const uint32_t mt = (tile / ntn + mt_shift) % ntm, nt = tile % ntn;
-                for (uint32_t kb = 0; kb < kblocks; ++kb, ++g) {
+                const uint32_t kb_end = min(kblocks, (split + 1) * kper);
+                for (uint32_t kb = split * kper; kb < kb_end; ++kb, ++g) {
                     const uint32_t s = g % kStages;
                     if (!mbar_wait_deadline(&empty_bar[s], ((g / kStages) & 1u) ^ 1u, deadline)) {
                         report_timeout(cv, kSiteMbar, r, cta, 1, g);
@@ -189,7 +198,9 @@ __device__ __forceinline__ void gemm_ar_body(const GemmArArgs& a, const CUtensor
     } else if (warp == 1) {
         if (lane == 0) {
             uint32_t g = 0, it = 0;
-            for (uint32_t tile = cta; tile < ntiles && !s_abort; tile += nctas, ++it) {
+            for (uint32_t item = cta; item < nitems && !s_abort; item += nctas, ++it) {
+                const uint32_t split = item & (ksplit - 1);
+                const uint32_t kb_begin = split * kper, kb_end = min(kblocks, (split + 1) * kper);
                 const uint32_t b = it & 1u;
                 if (!mbar_wait_deadline(&tmem_empty_bar[b], ((it >> 1) & 1u) ^ 1u, deadline)) {
                     report_timeout(cv, kSiteMbar, r, cta, 4, it);
@@ -198,7 +209,7 @@ __device__ __forceinline__ void gemm_ar_body(const GemmArArgs& a, const CUtensor
                 }
                 ptx::tc_fence_after_sync();
                 const uint32_t d_tmem = tmem + b * BN;
-                for (uint32_t kb = 0; kb < kblocks; ++kb, ++g) {
+                for (uint32_t kb = kb_begin; kb < kb_end; ++kb, ++g) {
                     const uint32_t s = g % kStages;
                     if (!mbar_wait_deadline(&full_bar[s], (g / kStages) & 1u, deadline)) {
                         report_timeout(cv, kSiteMbar, r, cta, 2, g);
@@ -211,7 +222,7 @@ __device__ __forceinline__ void gemm_ar_body(const GemmArArgs& a, const CUtensor
 #pragma unroll
                     for (int k = 0; k < BK / 16; ++k) {
                         // 16 bf16 = 32 bytes further along K inside the swizzle row: +2 in the address field
-                        ptx::tc_mma_f16(d_tmem, da + 2 * k, db + 2 * k, kIdesc, (kb | k) != 0 ? 1u : 0u);
+                        ptx::tc_mma_f16(d_tmem, da + 2 * k, db + 2 * k, kIdesc, (kb != kb_begin || k != 0) ? 1u : 0u);
                     }
                     ptx::tc_commit(&empty_bar[s]);  // frees the stage when these MMAs have read it
                 }
@@ -225,7 +236,8 @@ __device__ __forceinline__ void gemm_ar_body(const GemmArArgs& a, const CUtensor
         // the mbarrier) before the counter; waiting for them costs an NVLink round trip, which this
         // warp absorbs instead of the epilogue warps.
         uint32_t it = 0;
-        for (uint32_t tile = cta; tile < ntiles; tile += nctas, ++it) {
+        for (uint32_t item = cta; item < nitems; item += nctas, ++it) {
+            const uint32_t tile = item >> ks_shift;
             const uint32_t mt = (tile / ntn + mt_shift) % ntm, b = it & 1u;
             if (!mbar_wait_deadline(&pushed_bar[b], (it >> 1) & 1u, deadline)) {
                 if (lane == 0 && !s_abort) report_timeout(cv, kSiteMbar, r, cta, 5, it);
@@ -253,7 +265,8 @@ __device__ __forceinline__ void gemm_ar_body(const GemmArArgs& a, const CUtensor
         const uint64_t rowbytes = static_cast<uint64_t>(a.N) * 2;
         const uint64_t land_off = landing_off(a, r, parity);  // where this rank's partial rows go on every owner
         uint32_t it = 0;
-        for (uint32_t tile = cta; tile < ntiles; tile += nctas, ++it) {
+        for (uint32_t item = cta; item < nitems; item += nctas, ++it) {
+            const uint32_t tile = item >> ks_shift, split = item & (ksplit - 1);
             const uint32_t mt = (tile / ntn + mt_shift) % ntm, nt = tile % ntn, b = it & 1u;
             // Address arithmetic of the pushes, done while the MMAs of the tile still run.
             const uint32_t grow0 = mt * BM + q * 32 + rsub;  // this lane's first row
@@ -316,7 +329,7 @@ __device__ __forceinline__ void gemm_ar_body(const GemmArArgs& a, const CUtensor
                 } else if (a.oneshot) {
                     int d = r;
                     for (int k = 0; k < W; ++k) {
-                        char* p = s_heap[d] + land_off + static_cast<uint64_t>(grow0) * rowbytes + col_off;
+                        char* p = s_heap[d] + land_off + split * split_cap + static_cast<uint64_t>(grow0) * rowbytes + col_off;
 #pragma unroll
                         for (int i = 0; i < 8; ++i)
                             if (grow0 + 4 * i < a.T) ptx::st_v4(p + static_cast<uint64_t>(4 * i) * rowbytes, x[i]);
@@ -450,6 +463,7 @@ __device__ __forceinline__ void gemm_ar_body(const GemmArArgs& a, const CUtensor
             }
         } else {
         const char* const own_landing = s_heap[r] + landing_off(a, 0, parity);
+        const int nsrc = W << ks_shift;  // at most kMaxRanks (the host keeps world x ksplit <= 8)
         for (uint32_t lr = cta; lr < my_rows; lr += nctas) {
             const uint32_t grow = row_lo + lr;
             // Every load of the row (W partial vectors, residual, weight, for each of this thread's
@@ -462,8 +476,10 @@ __device__ __forceinline__ void gemm_ar_body(const GemmArArgs& a, const CUtensor
                     const uint64_t off = (static_cast<uint64_t>(lr) * a.N + static_cast<uint64_t>(c) * VEC) * 2;
                     const uint64_t goff = (static_cast<uint64_t>(grow) * a.N + static_cast<uint64_t>(c) * VEC) * 2;
 #pragma unroll
-                    for (int q = 0; q < kMaxRanks; ++q)
-                        if (q < W) part[j][q] = ptx::ld_cg_v4(own_landing + static_cast<uint64_t>(q) * cv.lay.gemm_cap + off);  // source q
+                    for (int q = 0; q < kMaxRanks; ++q)  // source q = (rank q / ksplit, split q % ksplit)
+                        if (q < nsrc)
+                            part[j][q] = ptx::ld_cg_v4(own_landing + static_cast<uint64_t>(q >> ks_shift) * cv.lay.gemm_cap +
+                                                       (q & (ksplit - 1)) * split_cap + off);
                     rv[j] = res ? ptx::ld_cg_v4(res + goff) : make_uint4(0, 0, 0, 0);
                     wv[j] = *reinterpret_cast<const uint4*>(wgt + static_cast<uint64_t>(c) * 16);
                 }
@@ -478,7 +494,7 @@ __device__ __forceinline__ void gemm_ar_body(const GemmArArgs& a, const CUtensor
                     for (int i = 0; i < VEC; ++i) f[j][i] = 0.f;
 #pragma unroll
                     for (int q = 0; q < kMaxRanks; ++q)
-                        if (q < W) accumulate<__nv_bfloat16>(f[j], part[j][q]);
+                        if (q < nsrc) accumulate<__nv_bfloat16>(f[j], part[j][q]);
                     if (res) accumulate<__nv_bfloat16>(f[j], rv[j]);
                     if (res_out) {
                         const uint64_t goff = (static_cast<uint64_t>(grow) * a.N + static_cast<uint64_t>(c) * VEC) * 2;

@@ -27,6 +27,8 @@ struct alignas(64) GemmArArgs {
     uint32_t T, N, K;
     uint32_t rows_per_owner;  // two-shot: rows normalised by each rank
     uint32_t oneshot;         // 1: every rank receives all partial rows and normalises all of them
+    uint32_t ksplit;          // one-shot, few tiles: CTAs that share the K extent of a tile (1, 2 or 4; world x ksplit <= 8)
+    uint32_t kper;            // k-blocks (of 64) per split
     uint32_t cnt_inc;         // arrivals per source that complete this rank's partial rows in this call
     uint32_t done_inc[kMaxRanks];  // per owner: rows it delivers to every rank's output in this call
     float eps;

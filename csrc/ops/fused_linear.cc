@@ -196,6 +196,24 @@ void FusedLinearCounts(uint32_t T, uint32_t N, int W, bool oneshot, uint32_t* ar
     }
 }
 
+// K splits per tile of a one-shot call of the tile form: powers of two while world x ksplit <= 8 (the reduction
+// holds eight partial rows in registers), every split keeps at least four k-blocks, the work items fit the
+// resident CTAs and a split's partial rows fit its share of the landing zone.  `want` > 0 replaces the
+// k-block rule (measurements).
+uint32_t FusedLinearTileSplit(uint32_t T, uint32_t N, uint32_t K, int world, uint32_t resident_ctas, uint64_t gemm_cap,
+                              uint32_t want) {
+    const uint32_t ntiles = ((T + kGemmTileM - 1) / kGemmTileM) * ((N + kGemmTileN - 1) / kGemmTileN), kblocks = K / 64;
+    uint32_t ks = 1;
+    auto fits = [&](uint32_t s) {
+        const uint32_t kper = (kblocks + s - 1) / s;
+        return static_cast<uint32_t>(world) * s <= static_cast<uint32_t>(kMaxRanks) && (want > 0 ? s <= want : kblocks / s >= 4) &&
+               ntiles * s <= resident_ctas && static_cast<uint64_t>(T) * N * 2 * s <= gemm_cap &&
+               static_cast<uint64_t>(s - 1) * kper < kblocks;
+    };
+    while (ks < 4 && fits(ks * 2)) ks *= 2;
+    return ks;
+}
+
 // Which multicast form the two-shot takes by default (0 none, 1 in-switch reduce + multicast store,
 // 2 peer pushes + multicast store), from measurements on 2, 4 and 8 B200.
 // 8 x B200, K = 512 per rank, N = 4096, CUDA-graph timing (us, modes 0 / 1 / 2): T = 128: 31.4 / 28.9 /
@@ -346,7 +364,13 @@ Result FusedLinearAllReduceRmsNorm(Communicator& comm, const FusedLinearDesc* de
     const int per_sm = cached_per_sm[flavour], sms = cached_sms[flavour];
     uint32_t resident = static_cast<uint32_t>(std::max(1, per_sm) * std::max(1, sms));
     if (comm.emulated()) resident = std::max<uint32_t>(1, resident / W);
-    const uint32_t work = std::max<uint32_t>(ntm * ntn, oneshot ? T : Rs);
+    // One-shot calls split the K extent of their tiles while that shortens the GEMM phase (see FusedLinearTileSplit).
+    static const long long forced_split = env::GetInt("YALI_GEMM_KSPLIT", 0);  // measurements only
+    uint32_t ksplit = oneshot && mc_mode == 0 && W > 1
+                          ? FusedLinearTileSplit(T, N, K, W, resident, lay.gemm_cap, forced_split > 0 ? static_cast<uint32_t>(forced_split) : 0u)
+                          : 1u;
+    const uint32_t kper = (K / 64 + ksplit - 1) / ksplit;
+    const uint32_t work = std::max<uint32_t>(ntm * ntn * ksplit, oneshot ? T : Rs);
     uint32_t ctas = std::min<uint32_t>(resident, work);
     if (opt.ctas > 0) ctas = std::min<uint32_t>(ctas, opt.ctas);
 
@@ -385,7 +409,9 @@ Result FusedLinearAllReduceRmsNorm(Communicator& comm, const FusedLinearDesc* de
         a.K = K;
         a.rows_per_owner = Rs;
         a.oneshot = oneshot ? 1u : 0u;
-        a.cnt_inc = arrivals[rank];
+        a.ksplit = ksplit;
+        a.kper = kper;
+        a.cnt_inc = arrivals[rank] * ksplit;  // every (tile, split) is announced
         for (int q = 0; q < W; ++q) a.done_inc[q] = rows_of[q];
         a.eps = opt.eps;
         a.nvls = nvls ? 1u : 0u;

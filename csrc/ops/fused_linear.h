@@ -43,6 +43,9 @@ Result FusedLinearAllReduceRmsNorm(Communicator& comm, const FusedLinearDesc* de
 // the two TMEM lane quarters its epilogue reads); 0 when it cannot run.
 uint32_t FusedLinearDecodeMaxRows(const HeapLayout& lay, uint32_t N, int world);
 // K splits per 256-column tile of the few-token form (1, 2, 4 or 8); `want` = 0: by the measured rule.
+// K splits per tile of a one-shot call of the tile form (1, 2 or 4); `want` = 0: by the k-block rule.
+uint32_t FusedLinearTileSplit(uint32_t T, uint32_t N, uint32_t K, int world, uint32_t resident_ctas, uint64_t gemm_cap,
+                              uint32_t want);
 // Tile width of the few-token form for that split: 128 if the work items fit the resident CTAs, else 256.
 uint32_t FusedLinearDecodeTile(uint32_t N, uint32_t ksplit, uint32_t resident_ctas);
 uint32_t FusedLinearDecodeSplit(uint32_t T, uint32_t N, uint32_t K, int world, uint32_t resident_ctas, uint64_t ll_cap,

@@ -121,6 +121,22 @@ def test_few_token_form_splits_k_to_eight_sources(native_lib):
         assert ks in (1, 2, 4, 8) and T * N * 4 * ks <= cap and ntn * ks <= 148 and (ks - 1) * kper < kblocks
 
 
+def test_one_shot_tile_form_splits_k(native_lib):
+    """K splits per tile of a one-shot call of the tile form: only while world x splits <= 8, every split keeps
+    four k-blocks, the items fit the GPU and the partial rows fit the landing zone."""
+    f = native_lib.yali_c_fused_tile_split
+    cap2, cap4 = 8 * MiB, 4 * MiB  # 16 MiB / world
+    assert f(128, 4096, 2048, 2, 148, cap2, 0) == 4   # 16 tiles x 4 splits of eight k-blocks
+    assert f(256, 4096, 2048, 2, 148, cap2, 0) == 4   # 32 tiles x 4 = 128 items; 2 MiB x 4 = 8 MiB
+    assert f(128, 4096, 1024, 4, 148, cap4, 0) == 2   # world x splits = 8
+    assert f(32, 4096, 512, 8, 148, 2 * MiB, 0) == 1  # eight ranks: no room for splits
+    assert f(128, 4096, 512, 2, 148, cap2, 0) == 2    # eight k-blocks: two splits of four
+    assert f(128, 4096, 256, 2, 148, cap2, 0) == 1
+    assert f(128, 4096, 2048, 2, 37, cap2, 0) == 2    # 16 tiles x 2 on 37 resident CTAs
+    assert f(512, 4096, 2048, 2, 148, cap2, 0) == 2   # 64 tiles; 4 MiB of partial rows x 2 = 8 MiB
+    assert f(128, 4096, 2048, 2, 148, cap2, 2) == 2   # forced (measurements)
+
+
 def test_plan_copy_engine_path(native_lib, monkeypatch):
     """The copy-engine path: one-shot at two ranks, two-shot over shards above, at most 64 chunks per
     rank, only for plain sums between addressable buffers of ranks that each own a GPU."""

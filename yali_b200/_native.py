@@ -88,6 +88,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "yali_c_fused_linear_counts": (None, [c.c_uint32, c.c_uint32, i32, i32, vp, vp]),
         "yali_c_fused_decode_split": (u32, [u32, u32, u32, i32, u32, u64, u32]),
         "yali_c_fused_decode_tile": (u32, [u32, u32, u32]),
+        "yali_c_fused_tile_split": (u32, [u32, u32, u32, i32, u32, u64, u32]),
         "yali_c_fused_linear_oneshot_max_rows": (c.c_uint32, [i32]),
         "yali_c_fused_linear_multicast_mode": (i32, [i32, c.c_uint32]),
         "yali_c_oracle_gemm": (None, [vp, vp, c.c_size_t, c.c_size_t, c.c_size_t, vp]),
