@@ -198,15 +198,19 @@ void FusedLinearCounts(uint32_t T, uint32_t N, int W, bool oneshot, uint32_t* ar
 
 // K splits per tile of a one-shot call of the tile form: powers of two while world x ksplit <= 8 (the reduction
 // holds eight partial rows in registers), every split keeps at least four k-blocks, the work items fit the
-// resident CTAs and a split's partial rows fit its share of the landing zone.  `want` > 0 replaces the
-// k-block rule (measurements).
+// resident CTAs, a split's partial rows fit its share of the landing zone, and the partial rows a rank sends
+// to its peers (every split sends its own) stay within 2 MiB (4 MiB for two splits): measured on 2 x B200,
+// K = 2048, us with 1 / 2 / 4 splits: T = 128: 25.0 / 21.1 / 23.4; T = 256: - / 27.2 / 32.3 (two-shot: 30.8).
+// `want` > 0 replaces the k-block and traffic rules (measurements).
 uint32_t FusedLinearTileSplit(uint32_t T, uint32_t N, uint32_t K, int world, uint32_t resident_ctas, uint64_t gemm_cap,
                               uint32_t want) {
     const uint32_t ntiles = ((T + kGemmTileM - 1) / kGemmTileM) * ((N + kGemmTileN - 1) / kGemmTileN), kblocks = K / 64;
     uint32_t ks = 1;
     auto fits = [&](uint32_t s) {
         const uint32_t kper = (kblocks + s - 1) / s;
-        return static_cast<uint32_t>(world) * s <= static_cast<uint32_t>(kMaxRanks) && (want > 0 ? s <= want : kblocks / s >= 4) &&
+        const uint64_t sent = static_cast<uint64_t>(T) * N * 2 * s * static_cast<uint64_t>(std::max(world - 1, 1));
+        const bool by_rule = kblocks / s >= 4 && sent <= (s == 2 ? (4ull << 20) : (2ull << 20));
+        return static_cast<uint32_t>(world) * s <= static_cast<uint32_t>(kMaxRanks) && (want > 0 ? s <= want : by_rule) &&
                ntiles * s <= resident_ctas && static_cast<uint64_t>(T) * N * 2 * s <= gemm_cap &&
                static_cast<uint64_t>(s - 1) * kper < kblocks;
     };

@@ -126,14 +126,16 @@ def test_one_shot_tile_form_splits_k(native_lib):
     four k-blocks, the items fit the GPU and the partial rows fit the landing zone."""
     f = native_lib.yali_c_fused_tile_split
     cap2, cap4 = 8 * MiB, 4 * MiB  # 16 MiB / world
-    assert f(128, 4096, 2048, 2, 148, cap2, 0) == 4   # 16 tiles x 4 splits of eight k-blocks
-    assert f(256, 4096, 2048, 2, 148, cap2, 0) == 4   # 32 tiles x 4 = 128 items; 2 MiB x 4 = 8 MiB
-    assert f(128, 4096, 1024, 4, 148, cap4, 0) == 2   # world x splits = 8
+    assert f(64, 4096, 2048, 2, 148, cap2, 0) == 4    # 16 tiles x 4 splits of eight k-blocks, 2 MiB to the peer
+    assert f(128, 4096, 2048, 2, 148, cap2, 0) == 2   # four splits would send 4 MiB to the peer
+    assert f(256, 4096, 2048, 2, 148, cap2, 0) == 2   # 4 MiB with two splits: still ahead of the two-shot
+    assert f(128, 4096, 2048, 2, 148, cap2, 4) == 4   # forced (measurements)
+    assert f(32, 4096, 1024, 4, 148, cap4, 0) == 2    # world x splits = 8
     assert f(32, 4096, 512, 8, 148, 2 * MiB, 0) == 1  # eight ranks: no room for splits
     assert f(128, 4096, 512, 2, 148, cap2, 0) == 2    # eight k-blocks: two splits of four
     assert f(128, 4096, 256, 2, 148, cap2, 0) == 1
-    assert f(128, 4096, 2048, 2, 37, cap2, 0) == 2    # 16 tiles x 2 on 37 resident CTAs
-    assert f(512, 4096, 2048, 2, 148, cap2, 0) == 2   # 64 tiles; 4 MiB of partial rows x 2 = 8 MiB
+    assert f(64, 4096, 2048, 2, 37, cap2, 0) == 2     # 16 tiles x 2 on 37 resident CTAs
+    assert f(512, 4096, 2048, 2, 148, cap2, 0) == 1   # 8 MiB to the peer with two splits
     assert f(128, 4096, 2048, 2, 148, cap2, 2) == 2   # forced (measurements)
 
 
