@@ -224,10 +224,10 @@ uint32_t FusedLinearTileSplit(uint32_t T, uint32_t N, uint32_t K, int world, uin
 // 29.5; T = 512: 37.4 / 36.0 / 35.6; T = 2048: 80.1 / 78.7 / 78.1.  2 x B200 (K = 2048): mode 1 loses
 // (109 against 90 us at T = 2048, the switch adds a hop and saves no bytes), mode 2 ties with mode 0.
 // 4 x B200 (K = 1024, 128 x 256 tiles): T = 512: 33.6 / 35.4 / 33.9; T = 2048: 65.9 / 73.0 / 68.6: the peer
-// pushes win or tie, so the switch is used from 8 ranks on.
-int FusedLinearAutoMulticastMode(int world, uint32_t T) {
-    if (world < 8) return 0;
-    return T < 512 ? 1 : 2;
+// pushes win or tie, so the switch is used from 8 ranks on.  8 x B200 with 128 x 256 tiles: T = 128: 28.2 /
+// 28.4 / 27.2; T = 512: 36.5 / 35.5 / 35.9; T = 2048: 73.6 / 77.1 / 72.7: pushes + multicast delivery throughout.
+int FusedLinearAutoMulticastMode(int world, uint32_t /*T*/) {
+    return world < 8 ? 0 : 2;
 }
 
 Result FusedLinearAllReduceRmsNorm(Communicator& comm, const FusedLinearDesc* descs, uint32_t T, uint32_t N,
