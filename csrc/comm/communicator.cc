@@ -45,6 +45,8 @@ bool MakeHeapLayout(int world, uint64_t requested_total, uint64_t granularity, H
         off += 2ull * (world - 1) * 2 * l.ll_cap;
         l.gemm_ll_off = off;
         l.gemm_ll_cap = 4 * MiB;  // per source rank: 64 rows of 4096 bf16 as flag-in-data lines from four K splits
+        const long long ll_mib = env::GetInt("YALI_GEMM_LL_CAP_MIB", 0);  // measurements only (every rank alike)
+        if (ll_mib >= 1 && ll_mib <= 64) l.gemm_ll_cap = static_cast<uint64_t>(ll_mib) * MiB;
         off += 2ull * world * l.gemm_ll_cap;
     }
     l.user_off = off;
