@@ -97,7 +97,9 @@ int yali_c_verify_allreduce_sum(const float* host, size_t n, float expected, flo
  * the two-shot ring kernel (mode 1), the one-shot kernel (mode 0), its flag-in-data form (mode 2) or
  * the staged two-shot through the switch (mode 3: per-CTA barriers, sums written back to every rank), the
  * pipelined two-shot in place (mode 4) or the pipelined one-shot pull (mode 5; both: two per-CTA barriers
- * per call, chunks of slot_elems elements, every rank rewrites its input between calls) on host memory, `calls` back-to-back calls without any barrier between them, fp32 data
+ * per call, chunks of slot_elems elements, every rank rewrites its input between calls), or the copy-engine path
+ * in place (mode 6 one-shot, mode 7 two-shot; lanes = 2: the caller's stream and the stream of the incoming
+ * copies; direct_ag = 1 in mode 6 is the negative control without the wait before overwriting) on host memory, `calls` back-to-back calls without any barrier between them, fp32 data
  * from the generator.  fault: 0 none, 1 rank `fault_rank` never runs call
  * `fault_call` (its peers must time out, not hang), 2 one flag publication of
  * that rank is dropped.  Returns 0 when every output matches the fp64 oracle,

@@ -479,6 +479,156 @@ void DirectCta(Shared& s, int r, int cta) {
     }
 }
 
+// Copy-engine path (comm/copy_engine_path.cc), IN PLACE.  Two threads per rank: lane 0 is the caller's
+// stream (enter kernel, one reduce kernel per chunk, the outgoing copies of the two-shot form, exit
+// kernel), lane 1 the stream of the incoming copies.  mode 6, one-shot: every rank copies every peer's
+// whole buffer chunk by chunk into staging, announces each chunk as read, and overwrites its own chunk
+// with the sum only after every peer has announced the same.  mode 7, two-shot: rank r copies shard r of
+// every peer, writes the sums over its own shard and into every peer's shard r, then says "done".
+// Flags on rank p written by src: kFlash = call src has entered, kAg = (call << 8) | chunks src has read
+// on p, kRs = call src has finished with p.  Chunks are ordered between the two threads of a rank by the
+// `copied` / `reduced` words (the events of the real path); `lanes` staging slots per source.
+// direct_ag = 1 is the negative control of mode 6: no wait before overwriting, and rank 1 copies slowly.
+// Stamps per element as in the pipelined forms: 2*call+1 = input of the call, 2*call+2 = its result.
+struct CeRankState {
+    std::unique_ptr<std::atomic<uint32_t>[]> copied, reduced;  // per chunk: call number when done
+    std::vector<float> staging;                                // [W-1][slots][chunk]
+};
+std::vector<std::unique_ptr<CeRankState>> g_ce;  // set up by yali_c_simulate for modes 6 and 7
+
+bool CeWaitWord(Shared& s, std::atomic<uint32_t>& w, uint32_t wanted, int rank, int peer, int site) {
+    auto deadline = Clock::now() + std::chrono::milliseconds(s.cfg.timeout_ms);
+    uint32_t spins = 0;
+    while (!SeqReached(w.load(std::memory_order_acquire), wanted)) {
+        if ((++spins & 255u) == 0) {
+            if (s.abort.load() || Clock::now() > deadline) {
+                // A wait between the two streams of one rank (events on the device) only passes the failure on:
+                // the record names the cross-rank wait that caused it.
+                if (peer != rank && s.timeouts.fetch_add(1) == 0) {
+                    s.t_rank = rank;
+                    s.t_peer = peer;
+                    s.t_site = site;
+                }
+                if (peer != rank) s.abort = true;
+                if (peer == rank && !s.abort.load()) {  // give the cross-rank waiter time to report first
+                    std::this_thread::sleep_for(std::chrono::milliseconds(20));
+                    s.abort = true;
+                }
+                return false;
+            }
+            std::this_thread::yield();
+        }
+    }
+    return true;
+}
+
+void CopyEngineRank(Shared& s, int r, int lane) {
+    const YaliSimConfig& c = s.cfg;
+    const int W = s.W;
+    const bool one_shot = c.mode == 6;
+    constexpr uint32_t kSlots = 3;
+    const uint64_t S = ((c.count + W - 1) / W + 3) / 4 * 4;  // shard elements
+    const uint64_t chunk = std::max<uint64_t>(4, c.slot_elems ? c.slot_elems : 64);
+    const uint64_t range_b = one_shot ? 0 : std::min<uint64_t>(c.count, r * S);
+    const uint64_t range_e = one_shot ? c.count : std::min<uint64_t>(c.count, range_b + S);
+    const uint32_t chunks = static_cast<uint32_t>((range_e - range_b + chunk - 1) / chunk);
+    CeRankState& me = *g_ce[r];
+    auto stamp_at = [&](int rank, uint64_t e) -> std::atomic<uint64_t>& { return s.ll[rank][e]; };
+    auto slot_of = [&](int q, uint32_t ch) { return (static_cast<size_t>(yali::SrcSlot(q, r)) * kSlots + ch % kSlots) * chunk; };
+    for (int call = 0; call < c.calls; ++call) {
+        if (c.fault == 1 && r == c.fault_rank && call >= c.fault_call) return;
+        const uint32_t number = static_cast<uint32_t>(call) + 1;
+        const uint64_t in_stamp = 2ull * call + 1, out_stamp = 2ull * call + 2;
+        bool ok = true;
+        if (lane == 1) {
+            // ---- the stream of the incoming copies
+            for (int q = 0; q < W && ok; ++q)
+                if (q != r) ok = CeWaitWord(s, Flag(s, r, kFlash, 0, q), number, r, q, 1);
+            for (uint32_t ch = 0; ok && ch < chunks; ++ch) {
+                if (ch >= kSlots) ok = CeWaitWord(s, me.reduced[ch - kSlots], number, r, r, 5);  // the slot is free again
+                if (!ok) break;
+                if (c.direct_ag == 1 && r == 1) std::this_thread::sleep_for(std::chrono::microseconds(300));
+                const uint64_t b = range_b + ch * chunk, e = std::min(range_e, b + chunk);
+                for (int q = 0; q < W; ++q) {
+                    if (q == r) continue;
+                    for (uint64_t i = b; i < e; ++i) {
+                        // The peer's chunk must still hold this call's input: not yet its result, not the next input.
+                        if (stamp_at(q, i).load(std::memory_order_acquire) != in_stamp) s.violations.fetch_add(1);
+                        me.staging[slot_of(q, ch) + (i - b)] = s.send[q][i];
+                    }
+                }
+                me.copied[ch].store(number, std::memory_order_release);
+            }
+        } else {
+            // ---- the caller's stream
+            SignalPeers(s, r, kFlash, 0, number, call);  // enter
+            for (uint32_t ch = 0; ok && ch < chunks; ++ch) {
+                ok = CeWaitWord(s, me.copied[ch], number, r, r, 4);
+                if (!ok) break;
+                const uint64_t b = range_b + ch * chunk, e = std::min(range_e, b + chunk);
+                if (one_shot) {
+                    const uint32_t word = (number << 8) | (ch + 1);
+                    for (int p = 0; p < W; ++p)
+                        if (p != r) {
+                            Flag(s, p, kAg, 0, r).store(word, std::memory_order_release);  // chunk ch of p has been read
+                            s.flag_writes.fetch_add(1, std::memory_order_relaxed);
+                        }
+                    if (c.direct_ag != 1)
+                        for (int q = 0; q < W && ok; ++q)
+                            if (q != r) ok = CeWaitWord(s, Flag(s, r, kAg, 0, q), word, r, q, 2);
+                    if (!ok) break;
+                }
+                for (uint64_t i = b; i < e; ++i) {
+                    float acc = 0.f;
+                    for (int q = 0; q < W; ++q) {
+                        if (q == r) {
+                            if (stamp_at(r, i).load(std::memory_order_acquire) != in_stamp) s.violations.fetch_add(1);
+                            acc += s.send[r][i];
+                        } else {
+                            acc += me.staging[slot_of(q, ch) + (i - b)];
+                        }
+                    }
+                    s.send[r][i] = acc;  // in place
+                    stamp_at(r, i).store(out_stamp, std::memory_order_release);
+                    if (!one_shot) {
+                        for (int q = 0; q < W; ++q) {  // the outgoing copies: shard r of every peer
+                            if (q == r) continue;
+                            if (stamp_at(q, i).load(std::memory_order_acquire) != in_stamp) s.violations.fetch_add(1);
+                            s.send[q][i] = acc;
+                            stamp_at(q, i).store(out_stamp, std::memory_order_release);
+                        }
+                    }
+                }
+                me.reduced[ch].store(number, std::memory_order_release);
+            }
+            if (ok && !one_shot) SignalPeers(s, r, kRs, 0, number, call);  // done
+            // exit: every peer has read all of this rank's buffer (one-shot) or is done with this rank (two-shot)
+            for (int q = 0; q < W && ok; ++q) {
+                if (q == r) continue;
+                // every rank cuts the same message into the same number of chunks in the one-shot form
+                ok = one_shot ? CeWaitWord(s, Flag(s, r, kAg, 0, q), (number << 8) | chunks, r, q, 3)
+                              : CeWaitWord(s, Flag(s, r, kRs, 0, q), number, r, q, 3);
+            }
+        }
+        if (!ok) s.abort = true;
+        if (s.abort.load()) s.rank_abort[r].store(1);
+        s.rank_barrier[r]->wait();  // both streams of this rank are through the call
+        if (s.rank_abort[r].load()) return;
+        if (lane == 0) {
+            const bool last = call + 1 == c.calls;
+            for (uint64_t i = 0; i < c.count; ++i) {
+                if (stamp_at(r, i).load(std::memory_order_acquire) != out_stamp) s.violations.fetch_add(1);
+                if (last) s.recv[r][i] = s.send[r][i];
+                if (!last) {
+                    s.send[r][i] = yali::RandomValue(yali::kDistNormal, c.seed + r + 1000ull * (call + 1), i);
+                    stamp_at(r, i).store(in_stamp + 2, std::memory_order_release);
+                }
+            }
+        }
+        s.rank_barrier[r]->wait();
+    }
+}
+
 }  // namespace
 
 extern "C" int yali_c_simulate(const YaliSimConfig* cfg, YaliSimReport* rep) {
@@ -487,6 +637,8 @@ extern "C" int yali_c_simulate(const YaliSimConfig* cfg, YaliSimReport* rep) {
     if (!cfg || cfg->world < 2 || cfg->world > yali::kMaxRanks || cfg->lanes < 1 || cfg->lanes > 64 ||
         cfg->count == 0 || cfg->calls < 1 || (cfg->mode == 1 && (cfg->slot_elems == 0 || cfg->slot_elems % 4)))
         return -1;
+    const bool ce = cfg->mode == 6 || cfg->mode == 7;
+    if (ce && cfg->lanes != 2) return -1;  // the caller's stream and the stream of the incoming copies
     Shared s;
     s.cfg = *cfg;
     s.W = cfg->world;
@@ -506,7 +658,7 @@ extern "C" int yali_c_simulate(const YaliSimConfig* cfg, YaliSimReport* rep) {
             s.ring_stamp.emplace_back(new std::atomic<uint64_t>[nslots]);
             for (size_t i = 0; i < nslots; ++i) s.ring_stamp[r][i].store(0);
         } else {
-            if (cfg->mode == 4 || cfg->mode == 5) {
+            if (cfg->mode == 4 || cfg->mode == 5 || ce) {
                 s.ll.emplace_back(new std::atomic<uint64_t>[cfg->count]);
                 for (size_t i = 0; i < cfg->count; ++i) s.ll[r][i].store(1);  // input of call 0
             } else if (cfg->mode == 2 || cfg->mode == 3) {
@@ -522,6 +674,21 @@ extern "C" int yali_c_simulate(const YaliSimConfig* cfg, YaliSimReport* rep) {
     }
     s.rank_abort.reset(new std::atomic<int>[W]);
     for (int r = 0; r < W; ++r) s.rank_abort[r].store(0);
+    g_ce.clear();
+    if (ce) {
+        const uint64_t chunk = std::max<uint64_t>(4, cfg->slot_elems ? cfg->slot_elems : 64);
+        const size_t nchunks = static_cast<size_t>((cfg->count + chunk - 1) / chunk) + 1;
+        for (int r = 0; r < W; ++r) {
+            g_ce.emplace_back(new CeRankState());
+            g_ce[r]->copied.reset(new std::atomic<uint32_t>[nchunks]);
+            g_ce[r]->reduced.reset(new std::atomic<uint32_t>[nchunks]);
+            for (size_t i = 0; i < nchunks; ++i) {
+                g_ce[r]->copied[i].store(0);
+                g_ce[r]->reduced[i].store(0);
+            }
+            g_ce[r]->staging.assign(static_cast<size_t>(W - 1) * 3 * chunk, 0.f);
+        }
+    }
     std::vector<std::thread> threads;
     for (int r = 0; r < W; ++r)
         for (int l = 0; l < s.L; ++l)
@@ -529,6 +696,7 @@ extern "C" int yali_c_simulate(const YaliSimConfig* cfg, YaliSimReport* rep) {
                                  : cfg->mode == 2 ? FlashLLCta
                                  : cfg->mode == 3 ? NvlsCta
                                  : (cfg->mode == 4 || cfg->mode == 5) ? DirectCta
+                                 : ce                                 ? CopyEngineRank
                                                                       : FlashCta,
                                  std::ref(s), r, l);
     // A rank that stops launching leaves its lanes' barrier short-handed only for itself.
@@ -550,7 +718,7 @@ extern "C" int yali_c_simulate(const YaliSimConfig* cfg, YaliSimReport* rep) {
     }
     // Oracle: fp64 sum; fp32 rank-order accumulation differs from it by rounding only.
     uint64_t bad = 0;
-    const bool direct = cfg->mode == 4 || cfg->mode == 5;
+    const bool direct = cfg->mode == 4 || cfg->mode == 5 || ce;
     for (int r = 0; r < W; ++r) {
         for (uint64_t i = 0; i < cfg->count; ++i) {
             double e = 0.0;

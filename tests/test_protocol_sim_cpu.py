@@ -55,6 +55,39 @@ def test_pipelined_direct_protocols_back_to_back(world, mode):
         assert rc == 0 and rep.mismatches == 0 and rep.timeouts == 0, (count, lanes, chunk, rc, rep.mismatches)
 
 
+@pytest.mark.parametrize("world", [2, 3, 4, 8])
+@pytest.mark.parametrize("mode", [6, 7])
+def test_copy_engine_protocol_in_place_back_to_back(world, mode):
+    """One-shot (6) and two-shot (7) copy-engine path in place: two threads per rank (the caller's stream and the
+    stream of the incoming copies), three staging slots, fresh inputs per call.  The stamps catch a chunk that is
+    overwritten before every peer has copied it, and an input rewritten before the peers are done with it."""
+    for count, chunk in [(5, 4), (4099, 64), (50001, 1024), (20000, 256)]:
+        rc, rep = simulate(mode=mode, world=world, lanes=2, calls=5, count=count, slot_elems=chunk)
+        assert rc == 0 and rep.mismatches == 0 and rep.timeouts == 0, (count, chunk, rc, rep.mismatches, rep.timeout_site)
+        assert rep.flag_writes > 0
+
+
+def test_copy_engine_model_catches_a_missing_handshake():
+    # Negative control: without the wait before overwriting (and with a peer that copies slowly) a rank writes
+    # its sums over a chunk that the peer has not copied yet.
+    hits = 0
+    for _ in range(3):
+        rc, rep = simulate(mode=6, world=2, lanes=2, calls=3, count=20000, slot_elems=256, direct_ag=1)
+        hits += rc == 3
+    assert hits >= 1
+
+
+def test_copy_engine_failures_time_out():
+    rc, rep = simulate(mode=6, world=2, lanes=2, fault=1, fault_rank=1, fault_call=1, calls=3, count=5000, timeout_ms=300)
+    assert rc == 2 and rep.timeout_peer == 1 and rep.timeout_rank == 0
+    rc, rep = simulate(mode=7, world=4, lanes=2, fault=1, fault_rank=3, fault_call=1, calls=3, count=5000, timeout_ms=300)
+    assert rc == 2 and rep.timeout_peer == 3 and rep.timeout_rank != 3
+    rc, rep = simulate(mode=7, world=2, lanes=2, fault=2, fault_rank=0, fault_call=1, calls=3, count=5000, timeout_ms=300)
+    assert rc == 2 and rep.timeout_peer == 0  # the lost "entered" keeps rank 1 from copying
+    rc, _ = simulate(mode=6, world=2, lanes=3)  # two threads per rank, no other number
+    assert rc == -1
+
+
 def test_rank_that_never_launches_times_out_pipelined():
     rc, rep = simulate(mode=4, world=4, lanes=2, fault=1, fault_rank=3, fault_call=1, calls=3, count=5000, timeout_ms=300)
     assert rc == 2 and rep.timeouts >= 1 and rep.timeout_peer == 3 and rep.timeout_rank != 3
